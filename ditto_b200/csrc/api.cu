@@ -1,0 +1,188 @@
+// C ABI of libditto_b200: argument checking, TMA tensor-map construction and
+// kernel launch.  Declarations and the reference interfaces they stand in for
+// are in include/ditto_b200.h.
+#include "../../include/ditto_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "attention_sm100.cuh"
+#include "mlp_sm100.cuh"
+#include "selftest_sm100.cuh"
+
+namespace {
+
+thread_local char g_last_error[256] = "";
+
+void set_error(const char* what, const char* detail) {
+  std::snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, detail ? detail : "");
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The encoder is a host-side driver function; resolve it through the runtime so
+// the library has no link-time dependency on libcuda.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of 16-bit elements, 128-byte swizzled boxes.
+int make_map_2d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint32_t box_cols,
+                uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) {
+    set_error("cuTensorMapEncodeTiled", "entry point not found");
+    return DITTO_ERR_DRIVER;
+  }
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
+    set_error("cuTensorMapEncodeTiled", buf);
+    return DITTO_ERR_CUDA;
+  }
+  return DITTO_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int cuda_fail(const char* what, cudaError_t e) {
+  set_error(what, cudaGetErrorString(e));
+  return DITTO_ERR_CUDA;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void* out, int batch, int M, int N,
+                               int K, int L, int dtype, int k_layout, float scale, int flags, void* workspace,
+                               size_t ws_bytes, int* status_word, void* stream) {
+  (void)workspace;
+  (void)ws_bytes;
+  if (!q || !k || !v || !out) return DITTO_ERR_INVALID_ARG;
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0 || L <= 0) return DITTO_ERR_INVALID_ARG;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return DITTO_ERR_INVALID_ARG;
+  if (!(scale > 0.f) || !std::isfinite(scale)) return DITTO_ERR_INVALID_ARG;
+  if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
+  if (k_layout != 0 && k_layout != 1) return DITTO_ERR_INVALID_ARG;
+  // The reference asserts multiples of 16 (bmm_chain.py:34-38); the tcgen05 path covers 128-row tiles.
+  if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
+  if (N != K || (K != 64 && K != 128)) return DITTO_ERR_UNSUPPORTED;
+  if (M % 128 || L % 128) return DITTO_ERR_UNSUPPORTED;
+  if (batch > 65535) return DITTO_ERR_UNSUPPORTED;
+
+  const bool bf16 = dtype == DITTO_DTYPE_BF16;
+  const int d = K;
+  int nt = (M % 256 == 0 && !(flags & DITTO_FLAG_ONE_TILE)) ? 2 : 1;
+  const bool psmem = (flags & DITTO_FLAG_P_VIA_SMEM) != 0;
+
+  ditto_b200::AttnParams p;
+  std::memset(&p, 0, sizeof(p));
+  int rc = make_map_2d(&p.map_q, bf16, q, d, static_cast<uint64_t>(batch) * M, 64, 128);
+  if (rc) return rc;
+  if (k_layout == 0)
+    rc = make_map_2d(&p.map_k, bf16, k, L, static_cast<uint64_t>(batch) * d, 64, d);
+  else
+    rc = make_map_2d(&p.map_k, bf16, k, d, static_cast<uint64_t>(batch) * L, 64, 128);
+  if (rc) return rc;
+  rc = make_map_2d(&p.map_v, bf16, v, d, static_cast<uint64_t>(batch) * L, 64, 128);
+  if (rc) return rc;
+  p.out = out;
+  p.M = M;
+  p.L = L;
+  p.k_transposed = (k_layout == 0);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status_word;
+  cudaError_t e = ditto_b200::launch_attention(p, batch, d, bf16, nt, psmem, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("bmm_softmax_bmm launch", e);
+  return DITTO_OK;
+}
+
+int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N,
+                              int K, int L, int dtype, int w_layout, int epilogue, void* workspace,
+                              size_t ws_bytes, int* status_word, void* stream) {
+  (void)workspace;
+  (void)ws_bytes;
+  if (!x || !w1 || !w2 || !y) return DITTO_ERR_INVALID_ARG;
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0 || L <= 0) return DITTO_ERR_INVALID_ARG;
+  if (!aligned16(x) || !aligned16(w1) || !aligned16(w2) || !aligned16(y)) return DITTO_ERR_INVALID_ARG;
+  if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
+  if (w_layout != 0 && w_layout != 1) return DITTO_ERR_INVALID_ARG;
+  if (epilogue != 0 && epilogue != 1) return DITTO_ERR_INVALID_ARG;
+  if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
+  return ditto_b200::launch_mlp_chain(x, w1, w2, y, batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, w_layout, epilogue,
+                                      status_word, static_cast<cudaStream_t>(stream));
+}
+
+size_t ditto_b200_workspace_bytes(int op, int batch, int M, int N, int K, int L, int dtype) {
+  (void)op; (void)batch; (void)M; (void)N; (void)K; (void)L; (void)dtype;
+  return 0;  // both chains keep their intermediates on chip
+}
+
+int ditto_b200_selftest_umma(const void* a, const void* b, float* c, int N, int K, int dtype, int b_mn, int a_tmem,
+                             int* status_word, void* stream) {
+  if (!a || !b || !c) return DITTO_ERR_INVALID_ARG;
+  if (N <= 0 || K <= 0 || N % 64 || K % 64 || N > 256 || K > 256) return DITTO_ERR_UNSUPPORTED;
+  if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
+  const bool bf16 = dtype == DITTO_DTYPE_BF16;
+  ditto_b200::SelftestParams p;
+  std::memset(&p, 0, sizeof(p));
+  int rc = make_map_2d(&p.map_a, bf16, a, K, 128, 64, 128);
+  if (rc) return rc;
+  rc = b_mn ? make_map_2d(&p.map_b, bf16, b, N, K, 64, K) : make_map_2d(&p.map_b, bf16, b, K, N, 64, N);
+  if (rc) return rc;
+  p.a_global = a;
+  p.c = c;
+  p.N = N;
+  p.K = K;
+  p.b_mn = b_mn ? 1 : 0;
+  p.a_tmem = a_tmem ? 1 : 0;
+  p.bf16 = bf16 ? 1 : 0;
+  p.status = status_word;
+  cudaError_t e = ditto_b200::launch_umma_selftest(p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("selftest launch", e);
+  return DITTO_OK;
+}
+
+const char* ditto_b200_strerror(int code) {
+  switch (code) {
+    case DITTO_OK: return "ok";
+    case DITTO_ERR_INVALID_ARG: return "invalid argument";
+    case DITTO_ERR_UNSUPPORTED: return "shape, dtype or layout not supported by the sm_100a kernels";
+    case DITTO_ERR_CUDA: return "CUDA error";
+    case DITTO_ERR_TIMEOUT: return "device-side wait timed out";
+    case DITTO_ERR_WORKSPACE: return "workspace too small";
+    case DITTO_ERR_DRIVER: return "driver entry point missing";
+    default: return "unknown error";
+  }
+}
+
+const char* ditto_b200_last_cuda_error(void) { return g_last_error; }
+
+int ditto_b200_version(void) { return 100; }
+
+}  // extern "C"

@@ -1,0 +1,24 @@
+// Host-visible launch interface of the fused bmm -> softmax -> bmm kernel.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace ditto_b200 {
+
+struct AttnParams {
+  CUtensorMap map_q;  // [batch*M, D] row-major, box 64 x 128, 128B swizzle
+  CUtensorMap map_k;  // [batch*L, D] (box 64 x 128) or, transposed, [batch*D, L] (box 64 x D)
+  CUtensorMap map_v;  // [batch*L, D] row-major, box 64 x 128
+  void* out;          // [batch, M, D] fp16 / bf16
+  int M;              // query rows per slice (multiple of 128 * NT)
+  int L;              // key/value rows per slice (multiple of 128)
+  int k_transposed;   // 1: K stored [batch, D, L] (the reference's layout)
+  float scale_log2;   // softmax scale * log2(e)
+  int* status;        // device word receiving a non-zero code if a bounded wait expired; may be null
+};
+
+// d in {64,128}; nt in {1,2} query tiles per CTA; psmem: stage P through shared memory instead of TMEM.
+cudaError_t launch_attention(const AttnParams& p, int batch, int d, bool bf16, int nt, bool psmem,
+                             cudaStream_t stream);
+
+}  // namespace ditto_b200

@@ -1,0 +1,124 @@
+// Single-CTA unit test of the tcgen05 building blocks: C[128, N] = A[128, K] * B
+// with one MMA chain, so that every operand form the fused kernels rely on can be
+// checked in isolation against a CPU product:
+//   b_mn = 0 : B stored [N, K] (K contiguous, "K-major"), as K in S = Q * K^T
+//   b_mn = 1 : B stored [K, N] (N contiguous, "MN-major"), as V in O = P * V
+//   a_tmem = 1 : A is first copied into TMEM (two 16-bit values per column) and
+//               the MMA reads it from there, as P in O = P * V
+#include "selftest_sm100.cuh"
+
+#include "sm100_ptx.cuh"
+
+namespace ditto_b200 {
+
+namespace {
+struct TestBars {
+  uint64_t full;
+  uint64_t done;
+  uint32_t tmem_base;
+  uint32_t abort_word;
+};
+}  // namespace
+
+__global__ void __launch_bounds__(128, 1) umma_selftest_kernel(const __grid_constant__ SelftestParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int a_bytes = 128 * p.K * 2;
+  const int b_bytes = p.N * p.K * 2;
+  uint8_t* sa = smem;
+  uint8_t* sb = smem + a_bytes;
+  TestBars* bar = reinterpret_cast<TestBars*>(sb + b_bytes);
+  volatile uint32_t* abort_word = &bar->abort_word;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->full, 1);
+    mbar_init(&bar->done, 1);
+    bar->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&bar->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bar->tmem_base;
+
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(&bar->full, a_bytes + b_bytes);
+    for (int a = 0; a < p.K / 64; ++a) tma_load_2d(sa + a * (128 * 128), &p.map_a, &bar->full, a * 64, 0);
+    if (p.b_mn) {
+      for (int a = 0; a < p.N / 64; ++a) tma_load_2d(sb + a * (p.K * 128), &p.map_b, &bar->full, a * 64, 0);
+    } else {
+      for (int a = 0; a < p.K / 64; ++a) tma_load_2d(sb + a * (p.N * 128), &p.map_b, &bar->full, a * 64, 0);
+    }
+  }
+  bool ok = mbar_wait(&bar->full, 0, abort_word, 0x10);
+  ok = __syncthreads_and(ok);
+
+  const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+  if (ok && p.a_tmem) {
+    // Row r of A (K 16-bit values) -> TMEM lane r, columns [256, 256 + K/2).
+    const uint32_t* arow = reinterpret_cast<const uint32_t*>(p.a_global) + static_cast<size_t>(threadIdx.x) * (p.K / 2);
+    for (int c = 0; c < p.K / 2; c += 8) {
+      uint32_t r[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r[i] = arow[c + i];
+      tmem_st_x8(lane_base + 256 + c, r);
+    }
+    tmem_wait_st();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  if (ok && threadIdx.x == 0) {
+    const uint32_t idesc = umma_idesc_f16(p.bf16 != 0, 128, p.N, false, p.b_mn != 0);
+    const uint32_t a_addr = smem_u32(sa), b_addr = smem_u32(sb);
+    for (int i = 0; i < p.K / 16; ++i) {
+      uint64_t db;
+      if (p.b_mn)
+        db = umma_desc_sw128(b_addr + i * 2048, p.K * 128, 1024);
+      else
+        db = umma_desc_sw128(b_addr + (i / 4) * (p.N * 128) + (i % 4) * 32, 16, 1024);
+      if (p.a_tmem) {
+        umma_ts(tmem_base, tmem_base + 256 + i * 8, db, idesc, i > 0);
+      } else {
+        const uint64_t da = umma_desc_sw128(a_addr + (i / 4) * (128 * 128) + (i % 4) * 32, 16, 1024);
+        umma_ss(tmem_base, da, db, idesc, i > 0);
+      }
+    }
+    umma_commit(&bar->done);
+  }
+  __syncwarp();
+  if (ok) ok = mbar_wait(&bar->done, 0, abort_word, 0x20);
+  ok = __all_sync(0xffffffffu, ok);
+  if (ok) {
+    tc_fence_after_sync();
+    float* crow = p.c + static_cast<size_t>(threadIdx.x) * p.N;
+    for (int c = 0; c < p.N; c += 8) {
+      uint32_t r[8];
+      tmem_ld_x8_wait(lane_base + c, r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) crow[c + i] = __uint_as_float(r[i]);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tmem_dealloc(tmem_base, 512);
+    if (lane == 0 && bar->abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, static_cast<int>(bar->abort_word));
+  }
+}
+
+cudaError_t launch_umma_selftest(const SelftestParams& p, cudaStream_t stream) {
+  const int smem = 128 * p.K * 2 + p.N * p.K * 2 + 64 + 1024;
+  cudaError_t e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  umma_selftest_kernel<<<1, 128, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace ditto_b200

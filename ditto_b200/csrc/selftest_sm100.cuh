@@ -1,0 +1,20 @@
+// Launch interface of the single-CTA tcgen05 self test.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace ditto_b200 {
+
+struct SelftestParams {
+  CUtensorMap map_a;     // A [128, K], box 64 x 128
+  CUtensorMap map_b;     // B [N, K] (box 64 x N) or [K, N] (box 64 x K)
+  const void* a_global;  // A again, for the TMEM-operand path
+  float* c;              // C [128, N] fp32
+  int N, K;              // multiples of 64, <= 256
+  int b_mn, a_tmem, bf16;
+  int* status;
+};
+
+cudaError_t launch_umma_selftest(const SelftestParams& p, cudaStream_t stream);
+
+}  // namespace ditto_b200

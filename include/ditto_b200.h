@@ -1,0 +1,89 @@
+/* ditto_b200 -- C ABI of the B200 (sm_100a) fused GEMM-chain kernels.
+ *
+ * The reference (KnowingNothing/Ditto) has no C plugin interface of its own: a
+ * fused chain is compiled by TVM into a runtime.Module whose entry
+ * "default_function" is called with positional DLTensor arguments -- inputs,
+ * weights, then outputs, all caller-allocated, compact row-major
+ * (src/runtime/graph_runtime.cc:133-204, python/ditto/auto_compute/graph.py:90-102,
+ * benchmark/chimera/cuda/bmm_softmax_bmm_cuda.py:239-256).  The entry points
+ * below take the place of those generated modules for the two chains; the
+ * shape tuple (batch, M, N, K, L) is the reference's:
+ *     A/query [batch, M, K]   B/key [batch, K, L]   C/value [batch, L, N]   out [batch, M, N]
+ *
+ * Conventions: every pointer is a device pointer owned by the caller; nothing
+ * is allocated per call; launches are asynchronous on `stream` (a
+ * cudaStream_t passed as void*); argument errors are reported synchronously by
+ * the return value; no entry point throws, aborts or traps.  A device-side
+ * bounded wait that expires stores a non-zero code in *status_word (device
+ * memory, optional) -- read it after synchronising the stream.
+ */
+#ifndef DITTO_B200_H_
+#define DITTO_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DITTO_OK 0
+#define DITTO_ERR_INVALID_ARG (-1) /* null pointer, non-positive size, misaligned buffer */
+#define DITTO_ERR_UNSUPPORTED (-2) /* shape / dtype / layout outside what the kernels cover */
+#define DITTO_ERR_CUDA (-3)        /* a CUDA runtime call failed; see ditto_b200_last_cuda_error() */
+#define DITTO_ERR_TIMEOUT (-4)     /* a device-side bounded wait expired */
+#define DITTO_ERR_WORKSPACE (-5)   /* workspace smaller than ditto_b200_workspace_bytes() */
+#define DITTO_ERR_DRIVER (-6)      /* the driver does not export cuTensorMapEncodeTiled */
+
+#define DITTO_DTYPE_FP16 0
+#define DITTO_DTYPE_BF16 1
+
+#define DITTO_OP_BMM_SOFTMAX_BMM 0
+#define DITTO_OP_GEMM_RELU_GEMM 1
+
+/* flags of ditto_b200_bmm_softmax_bmm */
+#define DITTO_FLAG_P_VIA_SMEM 1   /* stage the probabilities through shared memory instead of TMEM */
+#define DITTO_FLAG_ONE_TILE 2     /* one 128-row query tile per CTA (default: two when M % 256 == 0) */
+
+/* Fused attention chain  out = softmax(scale * Q K^T) V, replacing the module TVM builds from
+ * BatchGemmSoftmaxGemmMMA (python/ditto/auto_compute/nn/functional/bmm_chain.py:5-104) under
+ * TensorizeCUDA (src/auto_tensorize/hyper_fusion.cc:1494-1603).
+ *   k_layout 0: key is [batch, K, L] (the reference's pre-transposed layout,
+ *               python/ditto/auto_compute/nn/module/self_attention.py:55-57)
+ *   k_layout 1: key is [batch, L, K]
+ *   scale 1.0 reproduces the reference's exp(QK^T)/sum semantics; the softmax is evaluated in the
+ *   max-subtracted form, which is the same function without the overflow.
+ * Supported: N == K in {64, 128}; M, L multiples of 128; fp16 or bf16 in/out, fp32 accumulate. */
+int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void* out, int batch, int M, int N,
+                               int K, int L, int dtype, int k_layout, float scale, int flags, void* workspace,
+                               size_t ws_bytes, int* status_word, void* stream);
+
+/* Fused MLP chain  y = act(X W1) W2 with the hidden activations kept on chip, replacing the
+ * module built from BatchGemmReluGemm (python_test/auto_tensorize/test_hyper_fusion_cpu.py:24-96,
+ * evaluation/cpu/bmm_relu_bmm.py:56-125) and, with epilogue 0, BatchGemmGemm
+ * (benchmark/chimera/cuda/bmm_bmm_cuda.py:69-150).
+ *   x [batch, M, K]; w1 [batch, K, L]; w2 [batch, L, N]; y [batch, M, N]
+ *   w_layout 0: weights as above ([in, out]); 1: [out, in] as in nn/functional/linear.py:4-41
+ *   epilogue 0: identity between the GEMMs; 1: ReLU */
+int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N,
+                              int K, int L, int dtype, int w_layout, int epilogue, void* workspace,
+                              size_t ws_bytes, int* status_word, void* stream);
+
+/* Scratch bytes the op needs for this shape (0 when none). */
+size_t ditto_b200_workspace_bytes(int op, int batch, int M, int N, int K, int L, int dtype);
+
+/* Single-CTA check of one tcgen05 MMA chain: c[128, N] (fp32) = a[128, K] * b.
+ *   b_mn 0: b is [N, K]; 1: b is [K, N].  a_tmem 1: the A operand is read from tensor memory.
+ * N, K multiples of 64, at most 256.  Exists so the descriptor encodings the fused kernels depend
+ * on can be verified one at a time; it has no counterpart in the reference. */
+int ditto_b200_selftest_umma(const void* a, const void* b, float* c, int N, int K, int dtype, int b_mn,
+                             int a_tmem, int* status_word, void* stream);
+
+const char* ditto_b200_strerror(int code);
+/* Text of the last CUDA / driver error seen by the calling thread ("" if none). */
+const char* ditto_b200_last_cuda_error(void);
+int ditto_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DITTO_B200_H_ */
