@@ -1,0 +1,136 @@
+"""Operators on torch CUDA tensors: thin argument marshalling over the C ABI.
+
+PyTorch supplies device memory and the stream; all arithmetic happens in the hand-written
+sm_100a kernels of libditto_b200.so.  There is no CPU path: tensors must live on a CUDA device.
+"""
+import torch
+
+from . import _lib
+
+_DTYPE_CODE = {torch.float16: _lib.DTYPE_FP16, torch.bfloat16: _lib.DTYPE_BF16}
+_status_words = {}
+
+# number of kernel launches issued through this module (benchmarks report it)
+launch_count = 0
+
+
+def _status_word(device):
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+    return _status_words[key]
+
+
+def device_status(device=None, reset=True):
+    """Synchronise and return the device-side status word (0 = no bounded wait has expired)."""
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    w = _status_word(dev)
+    torch.cuda.synchronize(dev)
+    v = int(w.item())
+    if reset and v:
+        w.zero_()
+    return v
+
+
+def _check_tensor(t, name, dtype=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise TypeError(f"{name} must be a CUDA tensor (ditto_b200 has no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous (compact row-major)")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"{name} has dtype {t.dtype}, expected {dtype}")
+
+
+def bmm_softmax_bmm(query, key, value, out=None, scale=1.0, key_layout="KL", flags=0):
+    """out = softmax(scale * query @ key) @ value, fused in one kernel.
+
+    query [batch, M, K]; key [batch, K, L] when key_layout == "KL" (the reference's layout,
+    bmm_chain.py:30-31) or [batch, L, K] when "LK"; value [batch, L, N]; out [batch, M, N].
+    scale = 1 gives the reference's exp / row-sum semantics.
+    """
+    global launch_count
+    _check_tensor(query, "query")
+    if query.dtype not in _DTYPE_CODE:
+        raise TypeError(f"query dtype {query.dtype} not supported (float16 / bfloat16)")
+    _check_tensor(key, "key", query.dtype)
+    _check_tensor(value, "value", query.dtype)
+    if query.dim() != 3 or key.dim() != 3 or value.dim() != 3:
+        raise ValueError("query, key and value must be 3-D")
+    batch, M, K = query.shape
+    if key_layout == "KL":
+        kb, kK, L = key.shape
+        klay = 0
+    elif key_layout == "LK":
+        kb, L, kK = key.shape
+        klay = 1
+    else:
+        raise ValueError("key_layout must be 'KL' or 'LK'")
+    vb, vL, N = value.shape
+    if not (kb == batch and vb == batch and kK == K and vL == L):
+        raise ValueError(f"inconsistent shapes: {tuple(query.shape)}, {tuple(key.shape)} ({key_layout}), {tuple(value.shape)}")
+    if out is None:
+        out = torch.empty((batch, M, N), dtype=query.dtype, device=query.device)
+    else:
+        _check_tensor(out, "out", query.dtype)
+        if tuple(out.shape) != (batch, M, N):
+            raise ValueError(f"out has shape {tuple(out.shape)}, expected {(batch, M, N)}")
+    lib = _lib.load()
+    with torch.cuda.device(query.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.ditto_b200_bmm_softmax_bmm(query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(),
+                                            batch, M, N, K, L, _DTYPE_CODE[query.dtype], klay, float(scale),
+                                            int(flags), None, 0, _status_word(query.device).data_ptr(), stream)
+    _lib.check(rc, "ditto_b200_bmm_softmax_bmm")
+    launch_count += 1
+    return out
+
+
+def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO"):
+    """out = act(x @ w1) @ w2 with the hidden activations kept on chip.
+
+    x [batch, M, K] or [M, K]; w1 [batch, K, L] / [K, L]; w2 [batch, L, N] / [L, N] when
+    weight_layout == "IO" ([in, out]); "OI" takes the transposed [out, in] weights of
+    nn/functional/linear.py.  activation: "relu" or "identity".
+    """
+    global launch_count
+    _check_tensor(x, "x")
+    if x.dtype not in _DTYPE_CODE:
+        raise TypeError(f"x dtype {x.dtype} not supported (float16 / bfloat16)")
+    squeeze = x.dim() == 2
+    x3 = x.unsqueeze(0) if squeeze else x
+    w13 = w1.unsqueeze(0) if w1.dim() == 2 else w1
+    w23 = w2.unsqueeze(0) if w2.dim() == 2 else w2
+    _check_tensor(w13, "w1", x.dtype)
+    _check_tensor(w23, "w2", x.dtype)
+    batch, M, K = x3.shape
+    if weight_layout == "IO":
+        (b1, K1, L), (b2, L2, N) = w13.shape, w23.shape
+        wl = 0
+    elif weight_layout == "OI":
+        (b1, L, K1), (b2, N, L2) = w13.shape, w23.shape
+        wl = 1
+    else:
+        raise ValueError("weight_layout must be 'IO' or 'OI'")
+    if not (b1 == batch and b2 == batch and K1 == K and L2 == L):
+        raise ValueError(f"inconsistent shapes: {tuple(x.shape)}, {tuple(w1.shape)}, {tuple(w2.shape)}")
+    if activation not in ("relu", "identity"):
+        raise ValueError("activation must be 'relu' or 'identity'")
+    if out is None:
+        out = torch.empty((batch, M, N), dtype=x.dtype, device=x.device)
+        out3 = out
+        if squeeze:
+            out = out[0]
+    else:
+        _check_tensor(out, "out", x.dtype)
+        out3 = out.unsqueeze(0) if out.dim() == 2 else out
+        if tuple(out3.shape) != (batch, M, N):
+            raise ValueError(f"out has shape {tuple(out.shape)}, expected {(batch, M, N)}")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.ditto_b200_gemm_relu_gemm(x3.data_ptr(), w13.data_ptr(), w23.data_ptr(), out3.data_ptr(), batch, M, N,
+                                           K, L, _DTYPE_CODE[x.dtype], wl, 1 if activation == "relu" else 0, None, 0,
+                                           _status_word(x.device).data_ptr(), stream)
+    _lib.check(rc, "ditto_b200_gemm_relu_gemm")
+    launch_count += 1
+    return out

@@ -1,0 +1,81 @@
+"""Write the golden vectors in this folder: oracle outputs on small seeded cases.
+
+    python -m tests.golden.make_golden
+
+The reference cannot be imported or built here (its TVM dependency is absent), so these vectors
+come from the CPU oracle, cross-checked against its numpy/fp64 restatement at generation time.
+They pin the oracle against silent change and give the GPU tests fixed targets; inputs are
+regenerated from seeds (ditto_b200.workloads), only outputs are stored (as float16 / float32).
+"""
+import os
+
+import numpy as np
+
+from ditto_b200 import workloads as W
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+# name -> (kind, batch, M, N, K, L, dtype, scale, dist)
+CASES = {
+    "attn_fp16_d64": ("softmax", 2, 128, 64, 64, 256, "float16", 0.125, "normal"),
+    "attn_bf16_d128": ("softmax", 1, 128, 128, 128, 256, "bfloat16", 128 ** -0.5, "normal"),
+    # U(-0.5, 0.5): keeps exp(QK) inside fp16 range so the reference-literal form stays finite
+    "attn_fp16_reference_semantics": ("softmax", 2, 128, 64, 64, 128, "float16", 1.0, "uniform_half"),
+    "mlp_bf16_relu": ("relu", 1, 128, 128, 128, 256, "bfloat16", 1.0, "normal"),
+    "chain_fp16_identity": ("identity", 2, 128, 64, 64, 128, "float16", 1.0, "uniform"),
+}
+
+
+def workload(case):
+    kind, batch, M, N, K, L, dtype, scale, dist = CASES[case]
+    cfg = 900 + sorted(CASES).index(case)
+    return W.Workload(case, kind, batch, M, N, K, L, dtype, scale, dist, cfg)
+
+
+def inputs(case):
+    """(A [batch, M, K], B [batch, K, L], C [batch, L, N]) -- B already in the reference's [K, L] layout."""
+    w = workload(case)
+    if w.kind == "softmax":
+        q, k, v = W.attention_inputs(w, 0, w.batch)
+        return q, np.ascontiguousarray(k.transpose(0, 2, 1)), v
+    a, b, c = W.chain_inputs(w)
+    if w.dist == "normal":  # variance 1 / fan_in like the MLP weights
+        b = W._round(b * np.float32(w.K ** -0.5), w.dtype)
+        c = W._round(c * np.float32(w.L ** -0.5), w.dtype)
+    return a, b, c
+
+
+def compute(case, oracle):
+    w = workload(case)
+    dt = {"float16": oracle.FP16, "bfloat16": oracle.BF16}[w.dtype]
+    A, B, C = inputs(case)
+    out = {}
+    if w.kind == "softmax":
+        out["stable_fp32"] = oracle.bmm_softmax_bmm(A, B, C, w.scale, dt, wide=False)
+        if w.scale == 1.0:
+            out["literal"] = oracle.bmm_softmax_bmm_literal(A, B, C, dt)
+    else:
+        out["chain_fp32"] = oracle.gemm_act_gemm(A, B, C, 1 if w.kind == "relu" else 0, dt, wide=False)
+    return out
+
+
+def main():
+    from oracle import chain_oracle as oracle
+    for case in CASES:
+        w = workload(case)
+        dt = {"float16": oracle.FP16, "bfloat16": oracle.BF16}[w.dtype]
+        A, B, C = inputs(case)
+        out = compute(case, oracle)
+        # cross-check against the independent numpy / fp64 restatement before committing
+        if w.kind == "softmax":
+            ref = oracle.np_bmm_softmax_bmm(A, B, C, w.scale, dt, wide=True)
+            assert np.abs(out["stable_fp32"] - ref).max() <= 2e-3 * np.abs(ref).max() + 1e-5
+        else:
+            ref = oracle.np_gemm_act_gemm(A, B, C, 1 if w.kind == "relu" else 0, dt, wide=True)
+            assert np.abs(out["chain_fp32"] - ref).max() <= 2e-3 * np.abs(ref).max() + 1e-5
+        np.savez_compressed(os.path.join(HERE, case + ".npz"), **out)
+        print(case, {k: v.shape for k, v in out.items()})
+
+
+if __name__ == "__main__":
+    main()

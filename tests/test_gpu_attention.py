@@ -1,0 +1,223 @@
+"""GPU parity tests of the fused bmm -> softmax -> bmm kernel, through the C ABI, against the CPU
+oracle on the same seeded inputs.  Tolerances: tests/tolerances.py."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from ditto_b200 import _lib, ops
+from ditto_b200 import workloads as W
+from tests.golden import make_golden
+from tests.tolerances import assert_close
+
+pytestmark = pytest.mark.gpu
+
+TDT = {"float16": torch.float16, "bfloat16": torch.bfloat16}
+ODT = {"float16": 0, "bfloat16": 1}
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _dev(a, dtype, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda).to(TDT[dtype])
+
+
+def _run(cuda, q, k, v, dtype, scale, layout="LK", flags=0):
+    """q [b,M,K], k [b,L,K], v [b,L,N] float32 arrays of dtype-rounded values -> float32 result."""
+    dq, dv = _dev(q, dtype, cuda), _dev(v, dtype, cuda)
+    dk = _dev(k.transpose(0, 2, 1), dtype, cuda) if layout == "KL" else _dev(k, dtype, cuda)
+    out = torch.full((q.shape[0], q.shape[1], v.shape[2]), float("nan"), dtype=TDT[dtype], device=cuda)  # poison
+    ops.bmm_softmax_bmm(dq, dk, dv, out=out, scale=scale, key_layout=layout, flags=flags)
+    assert ops.device_status(cuda) == 0
+    return out.float().cpu().numpy()
+
+
+def _oracle(oracle, q, k, v, dtype, scale):
+    return oracle.bmm_softmax_bmm(q, np.ascontiguousarray(k.transpose(0, 2, 1)), v, scale, ODT[dtype], wide=False)
+
+
+def _case(seed, b, M, L, d, dtype, dist="normal"):
+    w = W.Workload("t", "softmax", b, M, d, d, L, dtype, 1.0, dist, seed)
+    return W.attention_inputs(w, 0, b)
+
+
+@pytest.mark.parametrize("b_mn,a_tmem", [(0, 0), (1, 0), (1, 1), (0, 1)])
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_umma_building_blocks(cuda, b_mn, a_tmem, dtype):
+    """One tcgen05 MMA chain per operand form the fused kernels use, against a CPU product."""
+    lib = _lib.load()
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    for N, K in ((64, 64), (128, 64), (64, 128), (128, 128), (256, 256)):
+        rng = np.random.default_rng(N * 1000 + K)
+        a = W._round(rng.standard_normal((128, K)).astype(np.float32), dtype)
+        b = W._round(rng.standard_normal((K, N) if b_mn else (N, K)).astype(np.float32), dtype)
+        c = torch.full((128, N), float("nan"), device=cuda)
+        da, db = _dev(a, dtype, cuda), _dev(b, dtype, cuda)
+        rc = lib.ditto_b200_selftest_umma(da.data_ptr(), db.data_ptr(), c.data_ptr(), N, K, ODT[dtype], b_mn, a_tmem,
+                                          status.data_ptr(), None)
+        torch.cuda.synchronize()
+        assert rc == 0 and int(status.item()) == 0
+        want = a.astype(np.float64) @ (b if b_mn else b.T).astype(np.float64)
+        np.testing.assert_allclose(c.cpu().numpy(), want, rtol=1e-5, atol=2e-4)
+
+
+@pytest.mark.parametrize("dtype,d", [("float16", 64), ("float16", 128), ("bfloat16", 64), ("bfloat16", 128)])
+@pytest.mark.parametrize("layout", ["LK", "KL"])
+@pytest.mark.parametrize("flags", [0, _lib.FLAG_ONE_TILE, _lib.FLAG_P_VIA_SMEM, _lib.FLAG_P_VIA_SMEM | _lib.FLAG_ONE_TILE])
+def test_parity_small(cuda, oracle, dtype, d, layout, flags):
+    """Every kernel variant (dtype x head dim x key layout x tile count x P staging) on small shapes."""
+    for (b, M, L) in ((2, 128, 128), (3, 256, 384), (1, 512, 128)):
+        q, k, v = _case(11, b, M, L, d, dtype)
+        scale = d ** -0.5
+        got = _run(cuda, q, k, v, dtype, scale, layout, flags)
+        assert_close(got, _oracle(oracle, q, k, v, dtype, scale), dtype, f"{dtype} d={d} {layout} flags={flags} {(b, M, L)}")
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_reference_semantics_scale_one(cuda, oracle, dtype):
+    """scale = 1 with U(-0.5,0.5) operands: the reference's exp / ones-column sum / divide chain
+    (bmm_chain.py:64-103) and the kernel's max-subtracted softmax are the same function."""
+    q, k, v = _case(12, 4, 256, 256, 64, dtype, dist="uniform_half")
+    got = _run(cuda, q, k, v, dtype, 1.0, "KL")
+    assert_close(got, _oracle(oracle, q, k, v, dtype, 1.0), dtype, "scale=1 stable")
+    lit = oracle.bmm_softmax_bmm_literal(q, np.ascontiguousarray(k.transpose(0, 2, 1)), v, ODT[dtype])
+    assert_close(got, lit, dtype, "scale=1 literal")
+
+
+def test_large_logits_stay_finite(cuda, oracle):
+    """Unscaled N(0,1) logits at d = 64 have sigma 8: exp() overflows fp16 in the reference's literal
+    form; the online softmax must stay finite and match the stable oracle.  Also exercises the
+    running-max rescale of the accumulator, which small logits never trigger."""
+    q, k, v = _case(13, 2, 256, 512, 64, "float16")
+    got = _run(cuda, q, k, v, "float16", 1.0)
+    assert_close(got, _oracle(oracle, q, k, v, "float16", 1.0), "float16", "scale=1 N(0,1)")
+    # rows whose maximum keeps growing block after block: forces a rescale at every K/V block
+    k2 = k.copy()
+    for j in range(4):
+        k2[:, j * 128:(j + 1) * 128] *= np.float32(0.25 * (j + 1))
+    k2 = W._round(k2, "float16")
+    got = _run(cuda, q, k2, v, "float16", 1.0)
+    assert_close(got, _oracle(oracle, q, k2, v, "float16", 1.0), "float16", "growing max")
+
+
+@pytest.mark.parametrize("case", ["attn_fp16_d64", "attn_bf16_d128", "attn_fp16_reference_semantics"])
+def test_golden_vectors(cuda, case):
+    w = make_golden.workload(case)
+    A, B, C = make_golden.inputs(case)   # B in the reference's [K, L] layout
+    dq, dk, dv = _dev(A, w.dtype, cuda), _dev(B, w.dtype, cuda), _dev(C, w.dtype, cuda)
+    out = ops.bmm_softmax_bmm(dq, dk, dv, scale=w.scale, key_layout="KL")
+    assert ops.device_status(cuda) == 0
+    stored = np.load(os.path.join(GOLDEN, case + ".npz"))
+    for key in stored.files:
+        assert_close(out.float().cpu().numpy(), stored[key], w.dtype, f"{case}:{key}")
+
+
+def test_cfg2_full(cuda, oracle):
+    """BASELINE config 2 at full size: 12 slices, S = 512, d = 64, fp16, scale 1/8, both key layouts."""
+    w = W.WORKLOADS["cfg2"]
+    q, k, v = W.attention_inputs(w, 0, w.batch)
+    want = _oracle(oracle, q, k, v, w.dtype, w.scale)
+    for layout in ("LK", "KL"):
+        got = _run(cuda, q, k, v, w.dtype, w.scale, layout)
+        mabs, mrel = assert_close(got, want, w.dtype, f"cfg2 {layout}")
+        print(f"cfg2 {layout}: max abs {mabs:.3e} max rel {mrel:.3e}")
+
+
+@pytest.mark.parametrize("name,slices", [("cfg3", (0, 1, 255, 256, 510, 511)), ("cfg5", (0, 511, 1023))])
+def test_large_configs_on_sampled_slices(cuda, oracle, name, slices):
+    """Configs 3 and 5: the sampled slices (first, last, shard boundaries) are generated from their
+    seeds, placed at their index inside a full-size launch, and compared with the oracle; the other
+    slices hold unrelated random data, so a slice mix-up shows."""
+    w = W.WORKLOADS[name]
+    tdt = TDT[w.dtype]
+    g = torch.Generator(device=cuda).manual_seed(5)
+    n = w.batch if name == "cfg3" else 64      # cfg5: a 64-slice launch keeps the test quick; indices wrap
+    q = torch.randn(n, w.M, w.K, device=cuda, generator=g).to(tdt)
+    k = torch.randn(n, w.L, w.K, device=cuda, generator=g).to(tdt)
+    v = torch.randn(n, w.L, w.N, device=cuda, generator=g).to(tdt)
+    placed = {}
+    for s in slices:
+        qs, ks, vs = W.attention_slice(w, s)
+        i = s % n
+        q[i], k[i], v[i] = (torch.from_numpy(t).to(cuda).to(tdt) for t in (qs, ks, vs))
+        placed[i] = (qs, ks, vs)
+    out = ops.bmm_softmax_bmm(q, k, v, scale=w.scale, key_layout="LK")
+    assert ops.device_status(cuda) == 0
+    assert torch.isfinite(out.float()).all()
+    for i, (qs, ks, vs) in placed.items():
+        want = _oracle(oracle, qs[None], ks[None], vs[None], w.dtype, w.scale)[0]
+        assert_close(out[i].float().cpu().numpy(), want, w.dtype, f"{name} slice {i}")
+
+
+def test_full_size_properties(cuda):
+    """Size-independent properties at config-3 size (512 slices, S = 512, d = 64):
+    * softmax rows sum to one: with V = all-ones the output is exactly 1 up to rounding;
+    * permuting the K/V rows of a slice leaves the result unchanged;
+    * the result is linear in V;
+    * repeated launches are bitwise identical."""
+    w = W.WORKLOADS["cfg3"]
+    g = torch.Generator(device=cuda).manual_seed(9)
+    q = torch.randn(w.batch, w.M, w.K, device=cuda, generator=g).half()
+    k = torch.randn(w.batch, w.L, w.K, device=cuda, generator=g).half()
+    v = torch.randn(w.batch, w.L, w.N, device=cuda, generator=g).half()
+    ones = ops.bmm_softmax_bmm(q, k, torch.ones_like(v), scale=w.scale, key_layout="LK")
+    assert (ones.float() - 1).abs().max().item() <= 2e-3
+    base = ops.bmm_softmax_bmm(q, k, v, scale=w.scale, key_layout="LK")
+    again = ops.bmm_softmax_bmm(q, k, v, scale=w.scale, key_layout="LK")
+    assert torch.equal(base, again)
+    perm = torch.randperm(w.L, device=cuda, generator=g)
+    permuted = ops.bmm_softmax_bmm(q, k[:, perm].contiguous(), v[:, perm].contiguous(), scale=w.scale, key_layout="LK")
+    assert (permuted.float() - base.float()).abs().max().item() <= 4e-3
+    v2 = torch.randn(w.batch, w.L, w.N, device=cuda, generator=g).half()
+    lin = ops.bmm_softmax_bmm(q, k, (v + 2 * v2).half(), scale=w.scale, key_layout="LK")
+    second = ops.bmm_softmax_bmm(q, k, v2, scale=w.scale, key_layout="LK")
+    assert (lin.float() - (base.float() + 2 * second.float())).abs().max().item() <= 1.5e-2
+    assert ops.device_status(cuda) == 0
+
+
+def test_reference_style_entry_point(cuda, oracle):
+    """The chain built and launched the way the reference's benchmark does it
+    (benchmark/chimera/cuda/bmm_softmax_bmm_cuda.py:158-261): builder -> fusion state ->
+    tensorize_cuda -> build -> func(*inputs, *outputs) with caller-allocated, pre-filled outputs."""
+    import ditto_b200 as ditto
+    from ditto_b200 import auto_compute as ac, auto_tensorize as at, hardware as hw
+    batch, M, N, K, L = 12, 512, 64, 64, 512
+    ins, outs = ac.nn.functional.BatchGemmSoftmaxGemm(batch, M, N, K, L, "float16", "float32")
+    A, B, C = ins
+    (F,) = outs
+    E_frag = F.op.input_tensors[0]
+    exp, C_ext = E_frag.op.input_tensors
+    D_frag = exp.op.input_tensors[0]
+    b, m, n, mi, ni = E_frag.op.axis
+    rlo, rli = E_frag.op.reduce_axis
+    fuse_choice = at.fusion_choice(D_frag.op, E_frag.op, [b, m, n, rlo, mi, ni, rli], 3)
+    p1 = at.cuda_wmma(M=16, N=16, K=16, in_dtype="float16", out_dtype="float32", scope="shared")
+    p2 = at.cuda_wmma(M=16, N=16, K=16, in_dtype="float16", out_dtype="float32", scope="global")
+    mi1 = at.match_info(at.intrinsic_match(D_frag, p1, ["InnerMost", "SameRange"])[0], p1)
+    mi2 = at.match_info(at.intrinsic_match(E_frag, p2, ["InnerMost", "SameRange"])[0], p2)
+    layer = ac.layer([F.op], inputs=[A, B, C])
+    state = at.tensorize_hyper_fusion_state(layer, fuse_choice, {D_frag.op: mi1, E_frag.op: mi2})
+    sch = at.tensorize_cuda(layer, state, hw.query_hw_param("gpu.cuda.B200"), at.cuda_tensorize_param(ty_size=4, tz_size=2))
+    func = ditto.build(sch, layer.schedule_tensors, "cuda")
+    rng = np.random.default_rng(3)
+    a, bb, c = (W._round(rng.uniform(-0.5, 0.5, t.shape).astype(np.float32), "float16") for t in ins)
+    f = torch.from_numpy(rng.uniform(-1, 1, F.shape).astype(np.float32)).to(cuda).half()
+    func(_dev(a, "float16", cuda), _dev(bb, "float16", cuda), _dev(c, "float16", cuda), f)
+    assert ops.device_status(cuda) == 0
+    want = oracle.bmm_softmax_bmm(a, bb, c, 1.0, 0, wide=False)
+    assert_close(f.float().cpu().numpy(), want, "float16", "reference-style entry")
+    cost = func.time_evaluator(func.entry_name, None, min_repeat_ms=50)(_dev(a, "float16", cuda), _dev(bb, "float16", cuda),
+                                                                        _dev(c, "float16", cuda), f).mean
+    assert 0 < cost < 1e-2
+
+
+def test_unsupported_shapes_raise(cuda):
+    q = torch.zeros(1, 144, 64, dtype=torch.float16, device=cuda)
+    kv = torch.zeros(1, 128, 64, dtype=torch.float16, device=cuda)
+    with pytest.raises(_lib.DittoError) as e:
+        ops.bmm_softmax_bmm(q, kv, kv, key_layout="LK")
+    assert e.value.code == _lib.ERR_UNSUPPORTED
+    with pytest.raises(ValueError):
+        ops.bmm_softmax_bmm(kv, kv[:, :, :32].contiguous(), kv, key_layout="LK")
+    with pytest.raises(ValueError):
+        ops.bmm_softmax_bmm(kv, kv.transpose(1, 2), kv, key_layout="KL")   # non-contiguous
