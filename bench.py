@@ -1,0 +1,438 @@
+#!/usr/bin/env python
+"""Benchmark of the fused GEMM-chain path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5] [--impl reference]
+
+One "step" is one pass of the fused chain over this rank's shard of the workload (slices for the
+attention chain, 128-row blocks for the MLP chain; the shards are contiguous and there is no
+collective on the data path).  Rank 0 prints one JSON line:
+
+* value / ms_per_step -- kernel-only throughput, inputs resident in HBM, CUDA events on the
+  launching stream, max over ranks; L2 is flushed between timed steps when a rank's inputs are
+  smaller than twice the L2.
+* e2e -- the same pass through the public operator (ditto_b200.ops) starting from pinned HOST
+  buffers: host->device copies, kernel and device->host copy of the result inside the timed region.
+* roofline -- algorithmic FLOPs per launch / mean launch time against the measured cuBLAS bf16 peak.
+* cpu_baseline -- the CPU port of the reference's fused loop nest timed on the host cores over a
+  bounded sample (rank 0, 1 GPU only).
+
+With --impl reference only the CPU path is timed (the reference itself needs TVM, which cannot be
+installed here); rank 0 prints the line, other ranks exit.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+# DRAM traffic per launch of the dominant kernel from the ncu captures summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum, scaled by the number of units when the capture
+# ran a smaller launch of the same kernel).  None = not captured yet.
+NCU_TRAFFIC_BYTES_PER_UNIT = {}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg5")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--units", type=int, default=0,
+                    help="run only the first N units (slices / 128-row blocks) of the workload: small cases for profiling")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the baseline sample")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"tflops": float(p["bf16_tflops"]), "tflops_sustained": float(p.get("bf16_tflops_sustained", 0.0)),
+                "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+# ---------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    REASONS = {
+        "hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4,
+        "hw_power_brake": 0x80,
+    }
+
+    def __init__(self, index):
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                for name, bit in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ---------------------------------------------------------------------------- the GPU arm
+class GpuRun:
+    """This rank's shard of a workload on its GPU: device inputs, pinned host copies, timed passes."""
+
+    def __init__(self, w, rank, world, device):
+        import torch
+        from ditto_b200 import ops
+        self.torch, self.ops, self.w, self.device = torch, ops, w, device
+        self.lo, self.hi = w.shard(rank, world)
+        self.n = self.hi - self.lo
+        tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[w.dtype]
+        g = torch.Generator(device=device).manual_seed(1234 + rank)
+        rnd = lambda *shape, std=1.0: (torch.randn(*shape, device=device, generator=g) * std).to(tdt)
+        if w.kind == "softmax":
+            self.inputs = [rnd(self.n, w.M, w.K), rnd(self.n, w.L, w.K), rnd(self.n, w.L, w.N)]
+            self.resident = []
+            self.out = torch.empty(self.n, w.M, w.N, dtype=tdt, device=device)
+            self.flops = 2.0 * self.n * w.M * w.L * (w.K + w.N)
+        else:
+            rows = self.n * 128
+            self.inputs = [rnd(rows, w.K)]
+            wg = torch.Generator(device=device).manual_seed(77)   # same weights on every rank
+            self.resident = [(torch.randn(w.K, w.L, device=device, generator=wg) * w.K ** -0.5).to(tdt),
+                             (torch.randn(w.L, w.N, device=device, generator=wg) * w.L ** -0.5).to(tdt)]
+            self.out = torch.empty(rows, w.N, dtype=tdt, device=device)
+            self.flops = 2.0 * rows * w.L * (w.K + w.N)
+        self.in_bytes = sum(t.numel() * t.element_size() for t in self.inputs)
+        self.out_bytes = self.out.numel() * self.out.element_size()
+        self.flush = None
+        if self.in_bytes + sum(t.numel() * 2 for t in self.resident) < 2 * L2_BYTES:
+            self.flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
+
+    def launch(self, inputs=None, out=None):
+        w, ops = self.w, self.ops
+        ins = inputs if inputs is not None else self.inputs
+        out = out if out is not None else self.out
+        if self.n == 0:
+            return
+        if w.kind == "softmax":
+            ops.bmm_softmax_bmm(ins[0], ins[1], ins[2], out=out, scale=w.scale, key_layout="LK")
+        else:
+            ops.gemm_relu_gemm(ins[0], self.resident[0], self.resident[1], out=out,
+                               activation="relu" if w.kind == "relu" else "identity")
+
+    def sanity(self):
+        """Largest deviation of unit 0 from a plain fp32 torch evaluation on the GPU."""
+        torch, w = self.torch, self.w
+        if self.n == 0:
+            return 0.0
+        self.launch()
+        if w.kind == "softmax":
+            q, k, v = (t[0].float() for t in self.inputs)
+            ref = torch.softmax(q @ k.t() * w.scale, -1) @ v
+            got = self.out[0].float()
+        else:
+            x = self.inputs[0][:128].float()
+            h = x @ self.resident[0].float()
+            h = torch.relu(h) if w.kind == "relu" else h
+            ref = h.to(self.out.dtype).float() @ self.resident[1].float()
+            got = self.out[:128].float()
+        return float((got - ref).abs().max().item())
+
+    def time_kernel(self, steps, warmup, barrier):
+        """Sum of the per-step device times of `steps` passes, ms."""
+        torch = self.torch
+        for _ in range(warmup):
+            self.launch()
+            if self.flush is not None:
+                self.flush.zero_()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        torch.cuda.synchronize(self.device)
+        barrier()
+        launches0 = self.ops.launch_count
+        for i in range(steps):
+            starts[i].record()
+            self.launch()
+            stops[i].record()
+            if self.flush is not None:
+                self.flush.zero_()
+        torch.cuda.synchronize(self.device)
+        barrier()
+        launches = self.ops.launch_count - launches0
+        return sum(s.elapsed_time(e) for s, e in zip(starts, stops)), launches
+
+    def time_e2e(self, steps, warmup, barrier, chunks=8):
+        """Host buffers -> device -> host, every step, chunked so copies overlap the kernel. ms total."""
+        torch, w = self.torch, self.w
+        if self.n == 0:
+            torch.cuda.synchronize(self.device)
+            barrier()
+            barrier()
+            return 0.0
+        unit_rows = 1 if w.kind == "softmax" else 128
+        units = self.n
+        chunks = max(1, min(chunks, units))
+        per = -(-units // chunks)
+        spans = [(c * per * unit_rows, min((c + 1) * per, units) * unit_rows) for c in range(chunks)
+                 if c * per < units]
+        host_in = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in self.inputs]
+        for h, d in zip(host_in, self.inputs):
+            h.copy_(d)
+        host_out = torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
+        nbuf = 2
+        max_rows = max(b - a for a, b in spans)
+        dev_in = [[torch.empty((max_rows,) + tuple(t.shape[1:]), dtype=t.dtype, device=self.device) for t in self.inputs]
+                  for _ in range(nbuf)]
+        dev_out = [torch.empty((max_rows,) + tuple(self.out.shape[1:]), dtype=self.out.dtype, device=self.device)
+                   for _ in range(nbuf)]
+        s_in, s_k, s_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        main = torch.cuda.current_stream(self.device)
+
+        def one_step():
+            copied = [None] * nbuf    # event: buffer's inputs landed
+            freed = [None] * nbuf     # event: buffer's outputs copied out (buffer reusable)
+            for ci, (a, b) in enumerate(spans):
+                bi = ci % nbuf
+                with torch.cuda.stream(s_in):
+                    if freed[bi] is not None:
+                        s_in.wait_event(freed[bi])
+                    for h, d in zip(host_in, dev_in[bi]):
+                        d[: b - a].copy_(h[a:b], non_blocking=True)
+                    ev_in = torch.cuda.Event()
+                    ev_in.record(s_in)
+                with torch.cuda.stream(s_k):
+                    s_k.wait_event(ev_in)
+                    self.launch([d[: b - a] for d in dev_in[bi]], dev_out[bi][: b - a])
+                    ev_k = torch.cuda.Event()
+                    ev_k.record(s_k)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_k)
+                    host_out[a:b].copy_(dev_out[bi][: b - a], non_blocking=True)
+                    ev_o = torch.cuda.Event()
+                    ev_o.record(s_out)
+                freed[bi] = ev_o
+            for s in (s_in, s_k, s_out):
+                main.wait_stream(s)
+
+        for _ in range(min(warmup, 2)):
+            for s in (s_in, s_k, s_out):
+                s.wait_stream(main)
+            one_step()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(self.device)
+        barrier()
+        e0.record(main)
+        for _ in range(steps):
+            for s in (s_in, s_k, s_out):
+                s.wait_stream(main)
+            one_step()
+        e1.record(main)
+        torch.cuda.synchronize(self.device)
+        barrier()
+        self.e2e_checksum = float(host_out[:1].float().sum().item())
+        return e0.elapsed_time(e1)
+
+
+# ---------------------------------------------------------------------------- the CPU arm
+def cpu_sample(w, seconds):
+    """Time the CPU port of the reference's fused loop nest (oracle/chain_oracle.c:
+    baseline_chain_fp32) on a bounded sample of the workload.  Returns (TFLOP/s, cores, description)."""
+    import numpy as np
+    from oracle import chain_oracle as co          # the benchmark's CPU-baseline leg may use the oracle
+    from ditto_b200 import workloads as W
+    cores = co.max_threads()
+    kind = {"softmax": 0, "relu": 1, "identity": 2}[w.kind]
+    if w.kind == "softmax":
+        unit_flops = 2.0 * w.M * w.L * (w.K + w.N)
+        q, k, v = W.attention_inputs(w, 0, min(8, w.batch))
+        kt = np.ascontiguousarray(k.transpose(0, 2, 1))
+        run = lambda: co.baseline_chain_fp32(q, kt, v, kind, w.scale)
+        units_per_call, what = q.shape[0], "slices"
+    else:
+        unit_flops = 2.0 * 128 * w.L * (w.K + w.N)
+        blocks = max(1, min(w.units, max(cores // 4, 1)))
+        if w.kind == "identity" or w.batch > 1:
+            a, b, c = W.chain_inputs(w)
+            unit_flops, units_per_call, what = w.flops, 1, "full passes"
+        else:
+            w1, w2 = W.mlp_weights(w)
+            a, b, c = W.mlp_inputs(w, 0, blocks)[None], w1[None], w2[None]
+            units_per_call, what = blocks, "128-row blocks"
+        run = lambda: co.baseline_chain_fp32(a, b, c, kind, 1.0)
+    run()                                           # warm-up, page in
+    t0 = time.perf_counter()
+    calls = 0
+    while True:
+        run()
+        calls += 1
+        el = time.perf_counter() - t0
+        if el >= seconds or calls >= 2000:
+            break
+    tflops = calls * units_per_call * unit_flops / el / 1e12
+    return tflops, cores, f"{calls} calls x {units_per_call} {what} of {w.name} ({el:.1f} s, fp32, AVX2 FMA port)"
+
+
+def reference_arm(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warm = max(args.steps, 1), max(args.warmup, 0)
+    per_step = max(0.5, min(8.0, 60.0 / (steps + warm)))
+    vals = []
+    desc = ""
+    cores = 0
+    for i in range(steps + warm):
+        v, cores, desc = cpu_sample(w, per_step)
+        if i >= warm:
+            vals.append(v)
+    value = sum(vals) / len(vals)
+    line = {
+        "impl": "reference", "metric": "fused GEMM-chain TFLOP/s", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": per_step * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "note": "CPU port of the reference's fused loop nest on the host cores; "
+                   "the reference's own TVM/LLVM build cannot be installed here"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc + " per step"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------- main
+def main():
+    args = parse_args()
+    from ditto_b200 import workloads as W
+    if args.workload not in W.WORKLOADS:
+        raise SystemExit(f"unknown workload {args.workload}; choose from {sorted(W.WORKLOADS)}")
+    w = W.WORKLOADS[args.workload]
+    if args.units:
+        import dataclasses
+        if w.kind == "softmax":
+            w = dataclasses.replace(w, batch=min(args.units, w.batch), name=f"{w.name} [first {args.units} slices]")
+        else:
+            w = dataclasses.replace(w, M=128 * min(args.units, w.units), name=f"{w.name} [first {args.units} row blocks]")
+    if args.impl == "reference":
+        reference_arm(args, w)
+        return
+    if w.dtype == "float32":
+        raise SystemExit("cfg1 is the reference's CPU-only fp32 case; it is covered by the tests, not benchmarked on the GPU")
+
+    world_env = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 and world_env == 1:
+        # convenience: relaunch under torchrun, one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__), *sys.argv[1:]]
+        raise SystemExit(subprocess.call(cmd))
+
+    import torch
+    from ditto_b200 import distributed as D
+    from ditto_b200 import ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the chain kernels have no CPU fallback")
+    rank, world = D.init()
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    barrier = D.barrier
+    peaks = measured_peaks()
+
+    run = GpuRun(w, rank, world, device)
+    err = run.sanity()
+    with ClockSampler(local) as clk:
+        ms_total, launches = run.time_kernel(args.steps, max(args.warmup, 3), barrier)
+    status = ops.device_status(device)
+    ms_total = D.max_over_ranks(ms_total, device)
+    ms_step = ms_total / args.steps
+    value = w.flops / (ms_step * 1e-3) / 1e12
+
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(1, min(args.steps, 10))
+        ms_e2e = D.max_over_ranks(run.time_e2e(e2e_steps, args.warmup, barrier), device) / e2e_steps
+        e2e = {"value": w.flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "steps": e2e_steps,
+               "h2d_bytes_per_step": int(D.sum_over_ranks(run.in_bytes, device)),
+               "d2h_bytes_per_step": int(D.sum_over_ranks(run.out_bytes, device))}
+    err = D.max_over_ranks(err, device)
+    status = int(D.max_over_ranks(status, device))
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        v, cores, desc = cpu_sample(w, args.cpu_seconds)
+        cpu = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc}
+
+    if rank == 0:
+        per_gpu_flops = run.flops                      # rank 0's launch (shards are equal for 1/2/4/8 GPUs)
+        achieved = per_gpu_flops / (ms_step * 1e-3) / 1e12
+        unit_traffic = NCU_TRAFFIC_BYTES_PER_UNIT.get(args.workload)
+        line = {
+            "metric": "fused GEMM-chain TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": {"float16": "fp16", "bfloat16": "bf16"}[w.dtype] + " in, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": w.name, "kind": w.kind, "units": w.units, "units_per_gpu": run.n,
+                       "shape_batch_M_N_K_L": [w.batch, w.M, w.N, w.K, w.L], "scale": w.scale,
+                       "sharding": f"contiguous units over {world} GPU(s), no collective",
+                       "l2": "flushed between timed steps" if run.flush is not None else "inputs larger than L2"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["tflops"],
+                         "traffic": (unit_traffic * run.n) if unit_traffic else None,
+                         "peak_source": peaks["source"] + " cuBLAS bf16 burst",
+                         "frac_of_sustained_peak": achieved / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
+                         "algorithmic_gbs": w.bytes / world / (ms_step * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm_gbs"]},
+            "cpu_baseline": cpu,
+            "e2e": e2e,
+            "gpu_launches": launches,
+            "clocks": clk.summary(),
+            "sanity_max_abs_err_vs_torch_fp32": err,
+            "device_status": status,
+        }
+        print(json.dumps(line), flush=True)
+    barrier()
+    if D.dist.is_initialized():
+        D.dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -60,7 +60,7 @@ def load():
     path = library_path()
     if not os.path.exists(path):
         raise ImportError(
-            f"{path} not found: build it with `python -m ditto_b200.build` (needs nvcc); "
+            f"{path} not found: build it with `python -m ditto_b200.build_lib` (needs nvcc); "
             "ditto_b200 has no CPU fallback")
     lib = ctypes.CDLL(path)
     vp, i, f, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t

@@ -1,7 +1,7 @@
 """Build libditto_b200.so (sm_100a only) in-tree with nvcc.
 
-    python -m ditto_b200.build            # rebuild if a source is newer than the library
-    python -m ditto_b200.build --force
+    python -m ditto_b200.build_lib            # rebuild if a source is newer than the library
+    python -m ditto_b200.build_lib --force
 
 nvcc cross-compiles without a GPU, so this also runs on a CPU-only machine.
 """
