@@ -117,6 +117,9 @@ int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void
   p.k_transposed = (k_layout == 0);
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word;
+#ifdef DITTO_TRACE
+  p.trace = ws_bytes >= 1280 * sizeof(long long) ? static_cast<long long*>(workspace) : nullptr;
+#endif
   cudaError_t e = ditto_b200::launch_attention(p, batch, d, bf16, nt, psmem, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail("bmm_softmax_bmm launch", e);
   return DITTO_OK;

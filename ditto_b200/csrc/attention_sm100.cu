@@ -14,13 +14,16 @@
 // query rows of one slice (batch x head) and streams the slice's K/V in blocks
 // of 128 rows through a TMA-fed ring of 128B-swizzled shared-memory stages.
 //
-// Warp roles (320 threads):
+// Warp roles (NT = 2: 320 threads):
 //   warps 0-3   softmax + epilogue for query tile 0  (thread i <-> row i, TMEM lane i)
 //   warps 4-7   softmax + epilogue for query tile 1
 //   warp  8     TMA producer (one lane issues)
-//   warp  9     MMA issuer   (one lane issues)
+//   warp  9     MMA issuer (one elected lane issues)
 // With two tiles the tensor pipe works on one tile while the other tile's
-// softmax runs, so the exponentials overlap the MMAs.
+// softmax runs, so the exponentials overlap the MMAs.  A single issuing warp
+// serving the tiles alternately is what keeps them half a period apart: with
+// one issuing warp per tile the two softmax phases drift into step, fight for
+// the exponential unit and leave the tensor pipe idle (measured: 18 % slower).
 //
 // TMEM columns (512 allocated): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
 // P (16-bit, two values per 32-bit column) overwrites the first 64 columns of
@@ -33,16 +36,27 @@
 
 #include "sm100_ptx.cuh"
 
+// Optional timeline capture for tuning (compiled in only with -DDITTO_TRACE): CTA (0,0) stores
+// clock64() stamps of its first iterations into the buffer passed as the call's workspace.
+#ifdef DITTO_TRACE
+#define DITTO_STAMP(base, j, k)                                                                   \
+  do {                                                                                            \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (j) < 16)        \
+      p.trace[(base) + (j) * 16 + (k)] = clock64();                                               \
+  } while (0)
+#else
+#define DITTO_STAMP(base, j, k) do {} while (0)
+#endif
+
 namespace ditto_b200 {
 
 namespace {
 
 constexpr int kBM = 128;   // query rows per tile
 constexpr int kBN = 128;   // K/V rows per block
-constexpr int kThreads = 320;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
+constexpr int threads_for(int nt) { return 32 * (4 * nt + 2); }
 constexpr uint32_t kTmemCols = 512;
+constexpr int kSplit = 96;  // K/V rows in the first part of P (the rest follows separately)
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; P stays <= 2^8 with a stale max
 
 template <int D, int NT, bool PSMEM>
@@ -62,7 +76,7 @@ struct Smem {
 struct Barriers {
   uint64_t q_full;
   uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
-  uint64_t s_full[2], p_full[2], o_done[2];
+  uint64_t s_full[2], p_part[2][2], o_done[2];
   uint32_t tmem_base;
   uint32_t abort_word;
 };
@@ -82,7 +96,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }  // namespace
 
 template <bool BF16, int D, int NT, bool PSMEM>
-__global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(threads_for(NT), 1) attention_kernel(const __grid_constant__ AttnParams p) {
   using SM = Smem<D, NT, PSMEM>;
   constexpr int kStages = SM::kStages;
   constexpr int kAtoms = D / 64;  // 64-element (128-byte) chunks along the head dimension
@@ -92,6 +106,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   Barriers* bar = reinterpret_cast<Barriers*>(smem + SM::kOffBar);
   volatile uint32_t* abort_word = &bar->abort_word;
 
+  constexpr int kProducerWarp = 4 * NT;
+  constexpr int kMmaWarp = 4 * NT + 1;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int slice = blockIdx.y;
@@ -108,7 +124,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     }
     for (int t = 0; t < NT; ++t) {
       mbar_init(&bar->s_full[t], 1);
-      mbar_init(&bar->p_full[t], kBM);
+      mbar_init(&bar->p_part[t][0], kBM);
+      mbar_init(&bar->p_part[t][1], kBM);
       mbar_init(&bar->o_done[t], 1);
     }
     bar->abort_word = 0;
@@ -124,7 +141,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   const uint32_t tmem_base = bar->tmem_base;
 
   if (warp == kProducerWarp) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer (one thread)
     if (lane == 0) {
       tma_prefetch_desc(&p.map_q);
       tma_prefetch_desc(&p.map_k);
@@ -134,136 +151,145 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         for (int a = 0; a < kAtoms; ++a)
           tma_load_2d(smem + SM::kOffQ + t * SM::kTileQ + a * (kBM * 128), &p.map_q, &bar->q_full, a * 64,
                       slice * p.M + m0 + t * kBM);
-    }
-    bool ok = true;
-    int armed_k[4] = {-1, -1, -1, -1}, armed_v[4] = {-1, -1, -1, -1};  // parity of the newest armed phase
-    for (int j = 0; j < nkv; ++j) {
-      const int s = j % kStages;
-      const uint32_t ph = (j / kStages) & 1;
-      ok = mbar_wait(&bar->k_empty[s], ph ^ 1, abort_word, 0x100 + j);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (lane == 0) {
-        uint8_t* dst = smem + SM::kOffK + s * SM::kTileKV;
-        mbar_arrive_expect_tx(&bar->k_full[s], SM::kTileKV);
-        armed_k[s] = static_cast<int>(ph);
-        if (p.k_transposed) {
-          // K given as [slice, D, L]: boxes of 64 kv-columns x D rows (MN-major operand)
-          for (int a = 0; a < kBN / 64; ++a)
-            tma_load_2d(dst + a * (D * 128), &p.map_k, &bar->k_full[s], j * kBN + a * 64, slice * D);
-        } else {
+      bool ok = true;
+      int armed_k[4] = {-1, -1, -1, -1}, armed_v[4] = {-1, -1, -1, -1};  // parity of the newest armed phase
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (j / kStages) & 1;
+        ok = mbar_wait(&bar->k_empty[s], ph ^ 1, abort_word, 0x100 + j);
+        if (!ok) break;
+        {
+          uint8_t* dst = smem + SM::kOffK + s * SM::kTileKV;
+          mbar_arrive_expect_tx(&bar->k_full[s], SM::kTileKV);
+          armed_k[s] = static_cast<int>(ph);
+          if (p.k_transposed) {
+            // K given as [slice, D, L]: boxes of 64 kv-columns x D rows (MN-major operand)
+            for (int a = 0; a < kBN / 64; ++a)
+              tma_load_2d(dst + a * (D * 128), &p.map_k, &bar->k_full[s], j * kBN + a * 64, slice * D);
+          } else {
+            for (int a = 0; a < kAtoms; ++a)
+              tma_load_2d(dst + a * (kBN * 128), &p.map_k, &bar->k_full[s], a * 64, slice * p.L + j * kBN);
+          }
+        }
+        ok = mbar_wait(&bar->v_empty[s], ph ^ 1, abort_word, 0x200 + j);
+        if (!ok) break;
+        {
+          uint8_t* dst = smem + SM::kOffV + s * SM::kTileKV;
+          mbar_arrive_expect_tx(&bar->v_full[s], SM::kTileKV);
+          armed_v[s] = static_cast<int>(ph);
           for (int a = 0; a < kAtoms; ++a)
-            tma_load_2d(dst + a * (kBN * 128), &p.map_k, &bar->k_full[s], a * 64, slice * p.L + j * kBN);
+            tma_load_2d(dst + a * (kBN * 128), &p.map_v, &bar->v_full[s], a * 64, slice * p.L + j * kBN);
         }
       }
-      ok = mbar_wait(&bar->v_empty[s], ph ^ 1, abort_word, 0x200 + j);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (lane == 0) {
-        uint8_t* dst = smem + SM::kOffV + s * SM::kTileKV;
-        mbar_arrive_expect_tx(&bar->v_full[s], SM::kTileKV);
-        armed_v[s] = static_cast<int>(ph);
-        for (int a = 0; a < kAtoms; ++a)
-          tma_load_2d(dst + a * (kBN * 128), &p.map_v, &bar->v_full[s], a * 64, slice * p.L + j * kBN);
-      }
-    }
-    if (!ok && lane == 0) {
-      // Drain: let copies that were already issued land before the CTA exits.
-      for (int s = 0; s < kStages; ++s) {
-        if (armed_k[s] >= 0)
-          for (uint32_t spin = 0; spin < (1u << 20) && !mbar_try_wait(&bar->k_full[s], armed_k[s]); ++spin) {}
-        if (armed_v[s] >= 0)
-          for (uint32_t spin = 0; spin < (1u << 20) && !mbar_try_wait(&bar->v_full[s], armed_v[s]); ++spin) {}
+      if (!ok) {
+        // Drain: let copies that were already issued land before the CTA exits.
+        for (int s = 0; s < kStages; ++s) {
+          if (armed_k[s] >= 0)
+            for (uint32_t spin = 0; spin < (1u << 20) && !mbar_try_wait(&bar->k_full[s], armed_k[s]); ++spin) {}
+          if (armed_v[s] >= 0)
+            for (uint32_t spin = 0; spin < (1u << 20) && !mbar_try_wait(&bar->v_full[s], armed_v[s]); ++spin) {}
+        }
       }
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
-    const uint32_t idesc_s = umma_idesc_f16(BF16, kBM, kBN, false, p.k_transposed != 0);
+    // The issuing warp is the serial resource of the CTA.  It stays converged: every lane
+    // evaluates the (warp-uniform) waits and descriptor arithmetic, and one elected lane issues
+    // the MMAs and commits.  Descriptors are built once and advanced by adding precomputed
+    // (byte offset >> 4) constants to their low word.
+    const uint32_t issuer = elect_one();
+    const bool kt = p.k_transposed != 0;
+    const uint32_t idesc_s = umma_idesc_f16(BF16, kBM, kBN, false, kt);
     const uint32_t idesc_o = umma_idesc_f16(BF16, kBM, D, false, true);
-    const uint32_t q_addr = smem_u32(smem + SM::kOffQ);
-    const uint32_t k_addr = smem_u32(smem + SM::kOffK);
-    const uint32_t v_addr = smem_u32(smem + SM::kOffV);
-    const uint32_t p_addr = smem_u32(smem + SM::kOffP);
+    const uint64_t dq0 = umma_desc_sw128(smem_u32(smem + SM::kOffQ), 16, 1024);
+    const uint64_t dk0 = kt ? umma_desc_sw128(smem_u32(smem + SM::kOffK), D * 128, 1024)
+                            : umma_desc_sw128(smem_u32(smem + SM::kOffK), 16, 1024);
+    const uint64_t dv0 = umma_desc_sw128(smem_u32(smem + SM::kOffV), kBN * 128, 1024);
+    const uint64_t dp0 = umma_desc_sw128(smem_u32(smem + SM::kOffP), 16, 1024);
 
     auto issue_s = [&](int t, int stage) {
-      if (lane == 0) {
+      const uint64_t da = dq0 + ((t * SM::kTileQ) >> 4);
+      const uint64_t db = dk0 + ((stage * SM::kTileKV) >> 4);
 #pragma unroll
-        for (int i = 0; i < D / 16; ++i) {
-          const uint64_t da =
-              umma_desc_sw128(q_addr + t * SM::kTileQ + (i / 4) * (kBM * 128) + (i % 4) * 32, 16, 1024);
-          uint64_t db;
-          if (p.k_transposed)
-            db = umma_desc_sw128(k_addr + stage * SM::kTileKV + i * 2048, D * 128, 1024);
-          else
-            db = umma_desc_sw128(k_addr + stage * SM::kTileKV + (i / 4) * (kBN * 128) + (i % 4) * 32, 16, 1024);
-          umma_ss(tmem_base + t * kBN, da, db, idesc_s, i > 0 ? 1u : 0u);
-        }
-        umma_commit(&bar->s_full[t]);
+      for (int i = 0; i < D / 16; ++i) {
+        // K-major operand: 32 bytes per k-step inside a 64-element atom, then the next atom;
+        // MN-major (transposed K): 16 rows of 128 bytes per k-step
+        const uint32_t off_k = ((i / 4) * (kBM * 128) + (i % 4) * 32) >> 4;
+        const uint32_t off_b = kt ? static_cast<uint32_t>((i * 2048) >> 4) : off_k;
+        umma_ss_elected(tmem_base + t * kBN, da + off_k, db + off_b, idesc_s, i > 0 ? 1u : 0u, issuer);
       }
-      __syncwarp();
+      umma_commit_elected(&bar->s_full[t], issuer);
     };
-    auto issue_pv = [&](int t, int stage, bool accumulate) {
-      if (lane == 0) {
+    // P arrives in two parts (the first kSplit K/V rows, then the rest); each part is multiplied
+    // as soon as it is there, so the second part's exponentials overlap the first part's MMAs.
+    auto issue_pv = [&](int t, int stage, int part, uint32_t accumulate) {
+      const uint64_t db = dv0 + ((stage * SM::kTileKV) >> 4);
 #pragma unroll
-        for (int i = 0; i < kBN / 16; ++i) {
-          const uint64_t db = umma_desc_sw128(v_addr + stage * SM::kTileKV + i * 2048, kBN * 128, 1024);
-          const uint32_t acc = (accumulate || i > 0) ? 1u : 0u;
-          if constexpr (PSMEM) {
-            const uint64_t da =
-                umma_desc_sw128(p_addr + t * SM::kTileP + (i / 4) * (kBM * 128) + (i % 4) * 32, 16, 1024);
-            umma_ss(tmem_base + 256 + t * D, da, db, idesc_o, acc);
-          } else {
-            umma_ts(tmem_base + 256 + t * D, tmem_base + t * kBN + i * 8, db, idesc_o, acc);
-          }
+      for (int i = (part == 0 ? 0 : kSplit / 16); i < (part == 0 ? kSplit / 16 : kBN / 16); ++i) {
+        const uint32_t acc = i > 0 ? 1u : accumulate;
+        if constexpr (PSMEM) {
+          const uint64_t da = dp0 + ((t * SM::kTileP + (i / 4) * (kBM * 128) + (i % 4) * 32) >> 4);
+          umma_ss_elected(tmem_base + 256 + t * D, da, db + ((i * 2048) >> 4), idesc_o, acc, issuer);
+        } else {
+          umma_ts_elected(tmem_base + 256 + t * D, tmem_base + t * kBN + i * 8, db + ((i * 2048) >> 4), idesc_o, acc,
+                          issuer);
         }
-        umma_commit(&bar->o_done[t]);
       }
-      __syncwarp();
     };
-    auto commit_to = [&](uint64_t* b) {
-      if (lane == 0) umma_commit(b);
-      __syncwarp();
-    };
-    auto wait_all = [&](uint64_t* b, uint32_t parity, uint32_t code) {
+    auto wait = [&](uint64_t* b, uint32_t parity, uint32_t code) {
       bool ok = mbar_wait(b, parity, abort_word, code);
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after_sync();
       return ok;
     };
 
-    bool ok = wait_all(&bar->q_full, 0, 0x300);
-    ok = ok && wait_all(&bar->k_full[0], 0, 0x301);
+    // With a single K/V stage the release cannot wait for the next iteration's first MMA
+    // (that MMA needs the very load the release unblocks).
+    constexpr bool kDeferRelease = kStages >= 2;
+    bool ok = wait(&bar->q_full, 0, 0x300) && wait(&bar->k_full[0], 0, 0x301);
     if (ok) {
-      issue_s(0, 0);
-      if (NT == 2) issue_s(1, 0);
-      commit_to(&bar->k_empty[0]);
+      for (int t = 0; t < NT; ++t) issue_s(t, 0);
+      umma_commit_elected(&bar->k_empty[0], issuer);
+      // operands of the first iteration; later ones are checked one iteration ahead, off the
+      // critical path (the loads land long before they are needed)
+      ok = wait(&bar->v_full[0], 0, 0x400);
+      if (ok && nkv > 1) ok = wait(&bar->k_full[1 % kStages], (1 / kStages) & 1, 0x600);
     }
     for (int j = 0; j < nkv && ok; ++j) {
       const int sv = j % kStages;
       const int sk = (j + 1) % kStages;
       const bool more = (j + 1 < nkv);
-      ok = wait_all(&bar->v_full[sv], (j / kStages) & 1, 0x400 + j);
-      if (!ok) break;
-      ok = wait_all(&bar->p_full[0], j & 1, 0x500 + j);
-      if (!ok) break;
-      issue_pv(0, sv, j > 0);
-      if (NT == 1) commit_to(&bar->v_empty[sv]);
-      if (more) {
-        ok = wait_all(&bar->k_full[sk], ((j + 1) / kStages) & 1, 0x600 + j);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        ok = wait(&bar->p_part[t][0], j & 1, 0x500 + j);
         if (!ok) break;
-        issue_s(0, sk);
-        if (NT == 1) commit_to(&bar->k_empty[sk]);
-      }
-      if (NT == 2) {
-        ok = wait_all(&bar->p_full[1], j & 1, 0x700 + j);
-        if (!ok) break;
-        issue_pv(1, sv, j > 0);
-        commit_to(&bar->v_empty[sv]);
-        if (more) {
-          issue_s(1, sk);
-          commit_to(&bar->k_empty[sk]);
+        DITTO_STAMP(512, j, 1 + 4 * t);
+        issue_pv(t, sv, 0, j > 0 ? 1u : 0u);
+        if (kDeferRelease && t == 0 && j > 0) {
+          // Release the stages the previous iteration finished with.  Deferred to here so that
+          // the two commits do not sit between "P is ready" and the first MMA that consumes it.
+          umma_commit_elected(&bar->v_empty[(j - 1) % kStages], issuer);
+          umma_commit_elected(&bar->k_empty[sv], issuer);
         }
+        ok = wait(&bar->p_part[t][1], j & 1, 0x580 + j);
+        if (!ok) break;
+        DITTO_STAMP(512, j, 2 + 4 * t);
+        issue_pv(t, sv, 1, 1u);
+        // Same thread, in-order pipe: the next S overwrites the P it follows only after P*V has
+        // read it, and its commit also covers that P*V (a commit tracks every earlier MMA).
+        if (more) issue_s(t, sk); else umma_commit_elected(&bar->o_done[t], issuer);
+        DITTO_STAMP(512, j, 3 + 4 * t);
       }
+      if (!ok) break;
+      if (!kDeferRelease) {
+        umma_commit_elected(&bar->v_empty[sv], issuer);
+        if (more) umma_commit_elected(&bar->k_empty[sk], issuer);
+      }
+      if (more) {
+        ok = wait(&bar->v_full[sk], ((j + 1) / kStages) & 1, 0x400 + j);
+        if (ok && j + 2 < nkv) ok = wait(&bar->k_full[(j + 2) % kStages], ((j + 2) / kStages) & 1, 0x600 + j);
+      }
+      DITTO_STAMP(512, j, 0);
     }
   } else if (warp < 4 * NT) {
     // ------------------------------------------------------------ softmax + epilogue
@@ -281,29 +307,30 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if ((warp & 3) == 0) DITTO_STAMP(t * 256, j, 0); else DITTO_STAMP(t * 256, j, 8 + (warp & 3));
 
       uint32_t sv[kBN];
       tmem_ld_x128_wait(s_col, sv);
+      if ((warp & 3) == 0) DITTO_STAMP(t * 256, j, 1);
 
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      float mx[8];
 #pragma unroll
-      for (int i = 0; i < kBN; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(sv[i + 0]));
-        mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+      for (int u = 0; u < 8; ++u) mx[u] = fmaxf(__uint_as_float(sv[2 * u]), __uint_as_float(sv[2 * u + 1]));
+#pragma unroll
+      for (int i = 16; i < kBN; i += 16) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          mx[u] = max3(mx[u], __uint_as_float(sv[i + 2 * u]), __uint_as_float(sv[i + 2 * u + 1]));
       }
-      const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+      const float m_new = fmaxf(max3(m, mx[0], mx[1]), fmaxf(max3(mx[2], mx[3], mx[4]), max3(mx[5], mx[6], mx[7])));
       // Lazy rescale: keep the stale maximum while the true one is within
       // 2^kRescaleThreshold of it; the final division by l cancels the difference.
       const bool need = (m_new - m) * c > kRescaleThreshold;
       if (__any_sync(0xffffffffu, need)) {
         const float f = ex2_approx((m - m_new) * c);
         if (j > 0) {
-          ok = mbar_wait(&bar->o_done[t], (j - 1) & 1, abort_word, 0x900 + j);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after_sync();
+          // s_full(j) was committed after P*V(j-1) by the same thread and a commit covers every
+          // earlier MMA, so the accumulator is quiescent here.
 #pragma unroll
           for (int cc = 0; cc < D; cc += 32) {
             uint32_t o[32];
@@ -318,39 +345,65 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         m = m_new;
       }
 
+      if ((warp & 3) == 0) DITTO_STAMP(t * 256, j, 2);
       const float mc = m * c;
       float sum0 = 0.f, sum1 = 0.f;
-      uint32_t pk[kBN / 2];
 #pragma unroll
-      for (int i = 0; i < kBN / 2; ++i) {
-        const float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * i]), c, -mc));
-        const float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * i + 1]), c, -mc));
-        sum0 += p0;
-        sum1 += p1;
-        pk[i] = pack2<BF16>(p0, p1);
+      for (int part = 0; part < 2; ++part) {
+        constexpr int kFirst = kSplit / 2;               // packed 32-bit words in part 0
+        const int w0 = part == 0 ? 0 : kFirst;
+        const int w1 = part == 0 ? kFirst : kBN / 2;
+        uint32_t pk[kFirst];
+#pragma unroll
+        for (int i = 0; i < kFirst; ++i) {
+          if (w0 + i < w1) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * (w0 + i)]), c, -mc));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * (w0 + i) + 1]), c, -mc));
+            sum0 += p0;
+            sum1 += p1;
+            pk[i] = pack2<BF16>(p0, p1);
+          }
+        }
+        if (part == 0 && (warp & 3) == 0) DITTO_STAMP(t * 256, j, 3);
+        if constexpr (PSMEM) {
+          // K-major, 128B-swizzled A operand: 64-column atoms of 128 rows x 128 bytes, 16-byte chunks.
+          uint8_t* pt = smem + SM::kOffP + t * SM::kTileP;
+#pragma unroll
+          for (int ch = 0; ch < kFirst / 4; ++ch) {
+            const int gch = w0 / 4 + ch;                  // chunk index within the 128-column row
+            if (gch < w1 / 4) {
+              uint4 v = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+              *reinterpret_cast<uint4*>(pt + (gch >> 3) * (kBM * 128) + row * 128 + (((gch & 7) ^ (row & 7)) << 4)) = v;
+            }
+          }
+          fence_proxy_async_smem();
+        } else {
+          if (part == 0) {
+            uint32_t lo[32], hi[16];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) lo[i] = pk[i];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) hi[i] = pk[32 + i];
+            tmem_st_x32(s_col, lo);
+            tmem_st_x16(s_col + 32, hi);
+          } else {
+            uint32_t lo[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) lo[i] = pk[i];
+            tmem_st_x16(s_col + kFirst, lo);
+          }
+          tmem_wait_st();
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&bar->p_part[t][part]);
+        if (part == 0 && (warp & 3) == 0) DITTO_STAMP(t * 256, j, 4);
       }
       l += sum0 + sum1;
-
-      if constexpr (PSMEM) {
-        // K-major, 128B-swizzled A operand: two 64-column atoms of 128 rows x 128 bytes.
-        uint8_t* pt = smem + SM::kOffP + t * SM::kTileP;
-#pragma unroll
-        for (int ch = 0; ch < 16; ++ch) {
-          const int atom = ch >> 3, cidx = ch & 7;
-          uint4 v = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-          *reinterpret_cast<uint4*>(pt + atom * (kBM * 128) + row * 128 + ((cidx ^ (row & 7)) << 4)) = v;
-        }
-        fence_proxy_async_smem();
-      } else {
-        tmem_st_x64(s_col, pk);
-        tmem_wait_st();
-      }
-      tc_fence_before_sync();
-      mbar_arrive(&bar->p_full[t]);
+      if ((warp & 3) == 0) DITTO_STAMP(t * 256, j, 5); else DITTO_STAMP(t * 256, j, 5 + (warp & 3));
     }
 
     if (ok) {
-      ok = mbar_wait(&bar->o_done[t], (nkv - 1) & 1, abort_word, 0xA00);
+      ok = mbar_wait(&bar->o_done[t], 0, abort_word, 0xA00);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
@@ -389,7 +442,7 @@ static cudaError_t launch_one(const AttnParams& p, int batch, cudaStream_t strea
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kBytes);
   if (e != cudaSuccess) return e;
   dim3 grid(p.M / (NT * kBM), batch, 1);
-  kern<<<grid, kThreads, SM::kBytes, stream>>>(p);
+  kern<<<grid, threads_for(NT), SM::kBytes, stream>>>(p);
   return cudaGetLastError();
 }
 

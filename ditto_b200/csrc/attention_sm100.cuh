@@ -15,6 +15,7 @@ struct AttnParams {
   int k_transposed;   // 1: K stored [batch, D, L] (the reference's layout)
   float scale_log2;   // softmax scale * log2(e)
   int* status;        // device word receiving a non-zero code if a bounded wait expired; may be null
+  long long* trace;   // timeline buffer of -DDITTO_TRACE builds (null otherwise)
 };
 
 // d in {64,128}; nt in {1,2} query tiles per CTA; psmem: stage P through shared memory instead of TMEM.

@@ -150,6 +150,49 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       : "memory");
 }
 
+// Converged-warp issue.  tcgen05.mma / commit are single-thread instructions, but a warp that
+// stays converged and predicates them on an elect.sync lane keeps descriptors and addresses in
+// uniform registers; measured on B200 this sustains one 128 x 128 x 16 MMA per 64 clocks (and a
+// 128 x 64 x 16 one per 32), whereas a divergent `if (lane == 0)` loop around computed
+// descriptors does not.  `issuer` is the value returned by elect_one() for the calling lane.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t is_elected;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(is_elected));
+  return is_elected;
+}
+__device__ __forceinline__ void umma_ss_elected(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate, uint32_t issuer) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(issuer)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_elected(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate, uint32_t issuer) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(issuer)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_elected(uint64_t* bar, uint32_t issuer) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(issuer)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor for 128-byte-swizzled tiles (what a TMA box
 // with CU_TENSOR_MAP_SWIZZLE_128B and a 128-byte inner extent produces).
 //   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4
@@ -180,6 +223,11 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(bool bf16, uint32_t m, uin
 }
 
 // ---------------------------------------------------------------- math
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
