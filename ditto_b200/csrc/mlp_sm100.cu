@@ -1,12 +1,461 @@
+// Fused GEMM -> activation -> GEMM for sm_100a:  Y = act(X W1) W2, hidden activations on chip.
+//
+// Replaces what the reference would build from BatchGemmReluGemm / BatchGemmGemm
+// (python_test/auto_tensorize/test_hyper_fusion_cpu.py:24-96, benchmark/chimera/cuda/
+// bmm_bmm_cuda.py:69-150): first GEMM, element-wise stage cast to the input type, second GEMM.
+//
+// Why a cluster.  One 128-row block of Y with N up to 1024 fp32 columns does not fit the 512
+// TMEM columns of an SM, and its hidden row block (128 x L 16-bit) does not fit shared memory.
+// So four CTAs (a cluster, one SM each) share a row block:
+//   * CTA q owns the Y columns [q N/4, (q+1) N/4) -- N/4 <= 256 TMEM columns, resident for the
+//     whole kernel -- and every fourth 128-wide chunk of the hidden dimension;
+//   * for its own chunks it runs GEMM1 (X block x W1 chunk -> 128 x 128 fp32 in TMEM), applies
+//     the activation, rounds to the 16-bit type, writes the tile into its shared memory in the
+//     K-major 128B-swizzled operand layout, and pushes a copy to the three peers with a
+//     shared::cta -> shared::cluster bulk copy that signals the peer's mbarrier;
+//   * for every chunk (its own and the peers') it runs GEMM2 (H chunk x its W2 slice) into Y.
+// The hidden activations therefore exist only in TMEM and (distributed) shared memory.
+// No TMA load in this file uses cluster multicast; every CTA fetches its own operands.
+//
+// Warp roles (224 threads): warps 0-3 epilogue (thread r <-> row r / TMEM lane r), warp 4 TMA
+// producer, warp 5 MMA issuer (converged, one elected lane issues), warp 6 relay (tells all four
+// CTAs when this CTA has finished reading a round of hidden chunks).
+//
+// Per round i (four chunks, one per CTA) on each CTA's tensor pipe:
+//   GEMM1(own chunk of round i+1)  |  GEMM2(4 chunks of round i)
+// and the epilogue warps drain GEMM1's accumulator (two TMEM buffers, ping-pong) while GEMM2 runs.
 #include "mlp_sm100.cuh"
 
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstring>
+
 #include "../../include/ditto_b200.h"
+#include "sm100_ptx.cuh"
 
 namespace ditto_b200 {
 
-int launch_mlp_chain(const void*, const void*, const void*, void*, int, int, int, int, int, bool, int, int, int*,
-                     cudaStream_t) {
-  return DITTO_ERR_UNSUPPORTED;
+namespace {
+
+constexpr int kCluster = 4;
+constexpr int kRows = 128;            // rows of X / Y per cluster
+constexpr int kChunk = 128;           // hidden columns per chunk
+constexpr int kStageBytes = 32 * 1024;
+constexpr int kStages = 3;
+constexpr int kSlotBytes = kRows * kChunk * 2;   // one hidden chunk, 16-bit: 32 KB
+constexpr int kThreads = 224;
+constexpr int kOffSlots = 0;
+constexpr int kOffRing = kOffSlots + kCluster * kSlotBytes;
+constexpr int kOffBar = kOffRing + kStages * kStageBytes;
+constexpr int kSmemBytes = kOffBar + 256 + 1024;
+
+struct MlpParams {
+  CUtensorMap map_x;   // X  [batch*M, K], box 64 x 128
+  CUtensorMap map_w1;  // IO: W1 [batch*K, L], box 64 x 64;  OI: W1 [batch*L, K], box 64 x 128
+  CUtensorMap map_w2;  // IO: W2 [batch*L, N], box 64 x 64;  OI: W2 [batch*N, L], box 64 x N/4
+  void* y;             // Y  [batch, M, N]
+  int M, N, K, L;
+  int w_oi;            // 1: weights stored [out, in] (K-major B operands)
+  int relu;
+  int* status;
+};
+
+struct Bars {
+  uint64_t full[kStages], empty[kStages];
+  uint64_t h_tmem_full[2], h_tmem_empty[2];
+  uint64_t h_ready;      // this round's four hidden chunks are in this CTA's slots
+  uint64_t g2_done;      // this CTA's GEMM2 of the round has finished reading the slots
+  uint64_t slots_free;   // all four CTAs have (count 4, remote arrivals)
+  uint64_t y_done;
+  uint64_t epi_sync;     // the 128 epilogue threads, once per round (bounded, unlike bar.sync)
+  uint32_t tmem_base;
+  uint32_t abort_word;
+};
+static_assert(sizeof(Bars) <= 256, "barrier block too large");
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t cta) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta));
+  return remote;
+}
+// Bulk copy from this CTA's shared memory into a peer's; completion (bytes) on the peer's mbarrier.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, const void* src, uint32_t bytes,
+                                                  uint32_t mbar_cluster_addr) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster_addr), "r"(smem_u32(src)), "r"(bytes), "r"(mbar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word,
+                                                  uint32_t code) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (*abort_word != 0u) return false;
+    if (spin > 4096u) __nanosleep(64);
+  }
+  atomicCAS(const_cast<uint32_t*>(abort_word), 0u, code);
+  return false;
+}
+
+}  // namespace
+
+template <bool BF16>
+__global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
+    mlp_chain_kernel(const __grid_constant__ MlpParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // Every CTA of the cluster rounds its dynamic shared memory up by the same amount (the base
+  // offset is identical across CTAs of a launch), so slot and barrier offsets match across peers.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Bars* bar = reinterpret_cast<Bars*>(smem + kOffBar);
+  volatile uint32_t* abort_word = &bar->abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t q = cluster_ctarank();
+  const int row0 = (blockIdx.x / kCluster) * kRows;
+  const int b = blockIdx.y;
+  const int NS = p.N / kCluster;          // this CTA's Y columns
+  const int rounds = p.L / (kCluster * kChunk);
+  const int ksteps1 = p.K / 64;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bar->full[s], 1);
+      mbar_init(&bar->empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar->h_tmem_full[i], 1);
+      mbar_init(&bar->h_tmem_empty[i], kRows);
+    }
+    mbar_init(&bar->h_ready, 1);
+    mbar_init(&bar->g2_done, 1);
+    mbar_init(&bar->slots_free, kCluster);
+    mbar_init(&bar->y_done, 1);
+    mbar_init(&bar->epi_sync, kRows);
+    bar->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&bar->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                     // peers' barriers exist before anyone signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bar->tmem_base;
+  const uint32_t tmem_y = tmem_base;
+  const uint32_t tmem_h = tmem_base + 256;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer (one thread)
+    if (lane == 0) {
+      tma_prefetch_desc(&p.map_x);
+      tma_prefetch_desc(&p.map_w1);
+      tma_prefetch_desc(&p.map_w2);
+      int ps = 0;
+      uint32_t pph = 0;
+      bool ok = true;
+      auto acquire = [&](uint32_t bytes, uint32_t code) -> uint8_t* {
+        ok = mbar_wait(&bar->empty[ps], pph ^ 1, abort_word, code);
+        if (!ok) return nullptr;
+        mbar_arrive_expect_tx(&bar->full[ps], bytes);
+        return smem + kOffRing + ps * kStageBytes;
+      };
+      auto advance = [&]() {
+        if (++ps == kStages) { ps = 0; pph ^= 1; }
+      };
+      auto load_g1 = [&](int i) {         // operands of GEMM1 for this CTA's chunk of round i
+        const int g = i * kCluster + static_cast<int>(q);
+        for (int ks = 0; ks < ksteps1 && ok; ++ks) {
+          uint8_t* dst = acquire(2 * 16384, 0x100 + i);
+          if (!ok) break;
+          tma_load_2d(dst, &p.map_x, &bar->full[ps], ks * 64, b * p.M + row0);
+          if (p.w_oi) {
+            tma_load_2d(dst + 16384, &p.map_w1, &bar->full[ps], ks * 64, b * p.L + g * kChunk);
+          } else {
+            tma_load_2d(dst + 16384, &p.map_w1, &bar->full[ps], g * kChunk, b * p.K + ks * 64);
+            tma_load_2d(dst + 16384 + 8192, &p.map_w1, &bar->full[ps], g * kChunk + 64, b * p.K + ks * 64);
+          }
+          advance();
+        }
+      };
+      auto load_g2 = [&](int i) {         // this CTA's W2 slice for the four chunks of round i
+        for (int c = 0; c < kCluster && ok; ++c) {
+          const int g = i * kCluster + c;
+          for (int kk = 0; kk < 2 && ok; ++kk) {
+            uint8_t* dst = acquire(64 * NS * 2, 0x200 + i);
+            if (!ok) break;
+            if (p.w_oi) {
+              tma_load_2d(dst, &p.map_w2, &bar->full[ps], g * kChunk + kk * 64, b * p.N + q * NS);
+            } else {
+              for (int a = 0; a < NS / 64; ++a)
+                tma_load_2d(dst + a * 8192, &p.map_w2, &bar->full[ps], q * NS + a * 64, b * p.L + g * kChunk + kk * 64);
+            }
+            advance();
+          }
+        }
+      };
+      load_g1(0);
+      if (rounds > 1) load_g1(1);
+      for (int i = 0; i < rounds && ok; ++i) {
+        load_g2(i);
+        if (i + 2 < rounds) load_g1(i + 2);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ MMA issuer (converged warp)
+    const uint32_t issuer = elect_one();
+    const uint32_t idesc1 = umma_idesc_f16(BF16, kRows, kChunk, false, p.w_oi == 0);
+    const uint32_t idesc2 = umma_idesc_f16(BF16, kRows, NS, false, p.w_oi == 0);
+    const uint32_t ring = smem_u32(smem + kOffRing);
+    const uint32_t slots = smem_u32(smem + kOffSlots);
+    int cs = 0;
+    uint32_t cph = 0;
+    bool ok = true;
+    auto wait = [&](uint64_t* bp, uint32_t parity, uint32_t code) {
+      bool r = mbar_wait(bp, parity, abort_word, code);
+      r = __all_sync(0xffffffffu, r);
+      tc_fence_after_sync();
+      return r;
+    };
+    auto advance = [&]() {
+      if (++cs == kStages) { cs = 0; cph ^= 1; }
+    };
+    auto g1 = [&](int i) {
+      const int hb = i & 1;
+      if (i >= 2) ok = wait(&bar->h_tmem_empty[hb], ((i >> 1) - 1) & 1, 0x300 + i);
+      for (int ks = 0; ks < ksteps1 && ok; ++ks) {
+        ok = wait(&bar->full[cs], cph, 0x310 + i);
+        if (!ok) break;
+        const uint32_t st = ring + cs * kStageBytes;
+        const uint64_t da = umma_desc_sw128(st, 16, 1024);
+        const uint64_t db = p.w_oi ? umma_desc_sw128(st + 16384, 16, 1024) : umma_desc_sw128(st + 16384, 8192, 1024);
+#pragma unroll
+        for (int s4 = 0; s4 < 4; ++s4) {
+          const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
+          umma_ss_elected(tmem_h + hb * kChunk, da + ((s4 * 32) >> 4), db + offb, idesc1, (ks | s4) ? 1u : 0u, issuer);
+        }
+        umma_commit_elected(&bar->empty[cs], issuer);
+        advance();
+      }
+      if (ok) umma_commit_elected(&bar->h_tmem_full[hb], issuer);
+    };
+    auto g2 = [&](int i) {
+      ok = wait(&bar->h_ready, i & 1, 0x400 + i);
+      for (int c = 0; c < kCluster && ok; ++c) {
+        for (int kk = 0; kk < 2 && ok; ++kk) {
+          ok = wait(&bar->full[cs], cph, 0x410 + i);
+          if (!ok) break;
+          const uint32_t st = ring + cs * kStageBytes;
+          const uint64_t da = umma_desc_sw128(slots + c * kSlotBytes + kk * 16384, 16, 1024);
+          const uint64_t db = p.w_oi ? umma_desc_sw128(st, 16, 1024) : umma_desc_sw128(st, 8192, 1024);
+#pragma unroll
+          for (int s4 = 0; s4 < 4; ++s4) {
+            const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
+            umma_ss_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (i | c | kk | s4) ? 1u : 0u, issuer);
+          }
+          umma_commit_elected(&bar->empty[cs], issuer);
+          advance();
+        }
+      }
+      if (ok) umma_commit_elected(&bar->g2_done, issuer);
+    };
+    g1(0);
+    if (rounds > 1 && ok) g1(1);
+    for (int i = 0; i < rounds && ok; ++i) {
+      g2(i);
+      if (i + 2 < rounds && ok) g1(i + 2);
+    }
+    if (ok) umma_commit_elected(&bar->y_done, issuer);
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ relay (one thread)
+    if (lane == 0) {
+      for (int i = 0; i < rounds; ++i) {
+        if (!mbar_wait(&bar->g2_done, i & 1, abort_word, 0x500 + i)) break;
+        for (uint32_t c = 0; c < kCluster; ++c) mbar_arrive_cluster(&bar->slots_free, c);
+      }
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------------------ epilogue
+    const int row = warp * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    uint8_t* my_slot = smem + kOffSlots + q * kSlotBytes;
+    bool ok = true;
+    for (int i = 0; i < rounds; ++i) {
+      const int hb = i & 1;
+      ok = mbar_wait(&bar->h_tmem_full[hb], (i >> 1) & 1, abort_word, 0x600 + i);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t h[kChunk];
+      tmem_ld_x128_wait(tmem_h + hb * kChunk + lane_base, h);
+      tc_fence_before_sync();
+      mbar_arrive(&bar->h_tmem_empty[hb]);
+      uint32_t pk[kChunk / 2];
+#pragma unroll
+      for (int j = 0; j < kChunk / 2; ++j) {
+        float v0 = __uint_as_float(h[2 * j]), v1 = __uint_as_float(h[2 * j + 1]);
+        if (p.relu) {
+          v0 = v0 > 0.f ? v0 : 0.f;       // if_then_else(D > 0, D, 0) as in the reference
+          v1 = v1 > 0.f ? v1 : 0.f;
+        }
+        pk[j] = pack2<BF16>(v0, v1);
+      }
+      if (i > 0) {
+        // every CTA of the cluster has finished GEMM2 of the previous round: slots may be overwritten
+        ok = mbar_wait_cluster(&bar->slots_free, (i - 1) & 1, abort_word, 0x700 + i);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        const uint4 v = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+        *reinterpret_cast<uint4*>(my_slot + (ch >> 3) * 16384 + row * 128 + (((ch & 7) ^ (row & 7)) << 4)) = v;
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&bar->epi_sync);                        // all 128 rows of the chunk are written
+      ok = mbar_wait(&bar->epi_sync, i & 1, abort_word, 0x780 + i);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (threadIdx.x == 0) {
+        const uint32_t slot_addr = smem_u32(my_slot);
+        const uint32_t bar_addr = smem_u32(&bar->h_ready);
+        for (uint32_t c = 0; c < kCluster; ++c)
+          if (c != q) bulk_copy_to_peer(map_to_cta(slot_addr, c), my_slot, kSlotBytes, map_to_cta(bar_addr, c));
+        // the local chunk is in place; the expected bytes are the three chunks the peers push
+        mbar_arrive_expect_tx(&bar->h_ready, (kCluster - 1) * kSlotBytes);
+      }
+    }
+    if (ok) {
+      ok = mbar_wait(&bar->y_done, 0, abort_word, 0x800);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) +
+                      ((static_cast<size_t>(b) * p.M + row0 + row) * p.N + static_cast<size_t>(q) * NS) * 2;
+      for (int cc = 0; cc < NS; cc += 32) {
+        uint32_t o[32];
+        tmem_ld_x32_wait(tmem_y + lane_base + cc, o);
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) w[j] = pack2<BF16>(__uint_as_float(o[2 * j]), __uint_as_float(o[2 * j + 1]));
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(yrow + cc * 2 + j * 16) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                     // no CTA leaves while a peer may still write to it
+  if (warp == 0) {
+    tmem_dealloc(tmem_base, 512);
+    if (lane == 0 && bar->abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, static_cast<int>(bar->abort_word));
+  }
+}
+
+// ------------------------------------------------------------------ host side
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+bool make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint32_t box_cols,
+              uint32_t box_rows) {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return false;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
+                     bool bf16, int w_layout, int epilogue, int* status, cudaStream_t stream) {
+  // Coverage of the cluster kernel: 128-row blocks; hidden size a multiple of 4 chunks of 128;
+  // N/4 Y columns per CTA (<= 256 TMEM columns, whole 64-column swizzle atoms); K in 64-wide steps.
+  if (M % kRows || L % (kCluster * kChunk) || K % 64) return DITTO_ERR_UNSUPPORTED;
+  if (N % (kCluster * 64) || N > kCluster * 256) return DITTO_ERR_UNSUPPORTED;
+  if (batch > 65535) return DITTO_ERR_UNSUPPORTED;
+  const int NS = N / kCluster;
+  MlpParams p;
+  std::memset(&p, 0, sizeof(p));
+  bool ok = make_map(&p.map_x, bf16, x, K, static_cast<uint64_t>(batch) * M, 64, 128);
+  if (w_layout == 1) {
+    ok = ok && make_map(&p.map_w1, bf16, w1, K, static_cast<uint64_t>(batch) * L, 64, 128);
+    ok = ok && make_map(&p.map_w2, bf16, w2, L, static_cast<uint64_t>(batch) * N, 64, NS);
+  } else {
+    ok = ok && make_map(&p.map_w1, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, 64);
+    ok = ok && make_map(&p.map_w2, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, 64);
+  }
+  if (!ok) return DITTO_ERR_DRIVER;
+  p.y = y;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.L = L;
+  p.w_oi = w_layout == 1;
+  p.relu = epilogue == 1;
+  p.status = status;
+  dim3 grid(kCluster * (M / kRows), batch, 1);
+  cudaError_t e;
+  if (bf16) {
+    e = cudaFuncSetAttribute(mlp_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess) mlp_chain_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  } else {
+    e = cudaFuncSetAttribute(mlp_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess) mlp_chain_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  }
+  if (e == cudaSuccess) e = cudaGetLastError();
+  return e == cudaSuccess ? DITTO_OK : DITTO_ERR_CUDA;
 }
 
 }  // namespace ditto_b200

@@ -21,7 +21,7 @@ CASES = {
     "attn_bf16_d128": ("softmax", 1, 128, 128, 128, 256, "bfloat16", 128 ** -0.5, "normal"),
     # U(-0.5, 0.5): keeps exp(QK) inside fp16 range so the reference-literal form stays finite
     "attn_fp16_reference_semantics": ("softmax", 2, 128, 64, 64, 128, "float16", 1.0, "uniform_half"),
-    "mlp_bf16_relu": ("relu", 1, 128, 128, 128, 256, "bfloat16", 1.0, "normal"),
+    "mlp_bf16_relu": ("relu", 1, 128, 256, 128, 512, "bfloat16", 1.0, "normal"),
     "chain_fp16_identity": ("identity", 2, 128, 64, 64, 128, "float16", 1.0, "uniform"),
 }
 

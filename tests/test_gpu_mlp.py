@@ -1,0 +1,117 @@
+"""GPU parity tests of the fused GEMM -> activation -> GEMM kernel, through the C ABI, against the
+CPU oracle on the same seeded inputs.  Tolerances: tests/tolerances.py (the absolute floor is scaled
+by the magnitude of the result, which grows with the hidden size)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from ditto_b200 import _lib, ops
+from ditto_b200 import workloads as W
+from tests.golden import make_golden
+from tests.tolerances import assert_close
+
+pytestmark = pytest.mark.gpu
+
+TDT = {"float16": torch.float16, "bfloat16": torch.bfloat16}
+ODT = {"float16": 0, "bfloat16": 1}
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _dev(a, dtype, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda).to(TDT[dtype])
+
+
+def _inputs(seed, batch, M, N, K, L, dtype):
+    rng = np.random.default_rng(seed)
+    x = W._round(rng.standard_normal((batch, M, K)).astype(np.float32), dtype)
+    w1 = W._round((rng.standard_normal((batch, K, L)) * K ** -0.5).astype(np.float32), dtype)
+    w2 = W._round((rng.standard_normal((batch, L, N)) * L ** -0.5).astype(np.float32), dtype)
+    return x, w1, w2
+
+
+def _run(cuda, x, w1, w2, dtype, act, layout="IO"):
+    dx = _dev(x, dtype, cuda)
+    if layout == "OI":
+        d1, d2 = _dev(w1.transpose(0, 2, 1), dtype, cuda), _dev(w2.transpose(0, 2, 1), dtype, cuda)
+    else:
+        d1, d2 = _dev(w1, dtype, cuda), _dev(w2, dtype, cuda)
+    out = torch.full((x.shape[0], x.shape[1], w2.shape[2]), float("nan"), dtype=TDT[dtype], device=cuda)  # poison
+    ops.gemm_relu_gemm(dx, d1, d2, out=out, activation=act, weight_layout=layout)
+    assert ops.device_status(cuda) == 0
+    return out.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("act", ["relu", "identity"])
+@pytest.mark.parametrize("layout", ["IO", "OI"])
+def test_parity_small(cuda, oracle, dtype, act, layout):
+    for (batch, M, N, K, L) in ((1, 128, 256, 64, 512), (2, 256, 512, 128, 1024), (1, 128, 1024, 192, 512)):
+        x, w1, w2 = _inputs(21, batch, M, N, K, L, dtype)
+        got = _run(cuda, x, w1, w2, dtype, act, layout)
+        want = oracle.gemm_act_gemm(x, w1, w2, 1 if act == "relu" else 0, ODT[dtype], wide=False)
+        assert_close(got, want, dtype, f"{dtype} {act} {layout} {(batch, M, N, K, L)}")
+
+
+def test_golden_vector(cuda):
+    case = "mlp_bf16_relu"
+    w = make_golden.workload(case)
+    A, B, C = make_golden.inputs(case)
+    out = ops.gemm_relu_gemm(_dev(A, w.dtype, cuda), _dev(B, w.dtype, cuda), _dev(C, w.dtype, cuda), activation="relu")
+    assert ops.device_status(cuda) == 0
+    stored = np.load(os.path.join(GOLDEN, case + ".npz"))
+    assert_close(out.float().cpu().numpy(), stored["chain_fp32"], w.dtype, case)
+
+
+def test_cfg4_sampled_row_blocks(cuda, oracle):
+    """BASELINE config 4 at full size (X[16384,1024], W1[1024,4096], W2[4096,1024], bf16): seeded
+    row blocks (first, last and the shard boundaries of 2/4/8 GPUs) are placed at their index, the
+    rest of X is unrelated random data, and those blocks are compared with the oracle."""
+    w = W.WORKLOADS["cfg4"]
+    w1, w2 = W.mlp_weights(w)
+    g = torch.Generator(device=cuda).manual_seed(3)
+    x = torch.randn(w.M, w.K, device=cuda, generator=g).bfloat16()
+    blocks = (0, 15, 16, 63, 64, 127)
+    rows = {}
+    for blk in blocks:
+        r = W.mlp_rows(w, blk)
+        x[blk * 128:(blk + 1) * 128] = torch.from_numpy(r).to(cuda).bfloat16()
+        rows[blk] = r
+    out = ops.gemm_relu_gemm(x, _dev(w1, w.dtype, cuda), _dev(w2, w.dtype, cuda), activation="relu")
+    assert ops.device_status(cuda) == 0
+    assert torch.isfinite(out.float()).all()
+    for blk, r in rows.items():
+        want = oracle.gemm_act_gemm(r[None], w1[None], w2[None], 1, oracle.BF16, wide=False)[0]
+        assert_close(out[blk * 128:(blk + 1) * 128].float().cpu().numpy(), want, w.dtype, f"cfg4 row block {blk}")
+
+
+def test_full_size_properties(cuda):
+    """Size-independent checks at config-4 size: rows are independent (permuting row blocks
+    permutes the result), the identity chain is linear in X, ReLU of a non-negative hidden layer
+    equals the identity chain, and repeated launches are bitwise identical."""
+    w = W.WORKLOADS["cfg4"]
+    g = torch.Generator(device=cuda).manual_seed(4)
+    x = torch.randn(w.M, w.K, device=cuda, generator=g).bfloat16()
+    w1 = (torch.randn(w.K, w.L, device=cuda, generator=g) * w.K ** -0.5).bfloat16()
+    w2 = (torch.randn(w.L, w.N, device=cuda, generator=g) * w.L ** -0.5).bfloat16()
+    base = ops.gemm_relu_gemm(x, w1, w2, activation="relu")
+    assert torch.equal(base, ops.gemm_relu_gemm(x, w1, w2, activation="relu"))
+    perm = torch.randperm(w.M // 128, device=cuda, generator=g)
+    xp = x.view(-1, 128, w.K)[perm].reshape(w.M, w.K).contiguous()
+    assert torch.equal(ops.gemm_relu_gemm(xp, w1, w2, activation="relu"), base.view(-1, 128, w.N)[perm].reshape(w.M, w.N))
+    lin = ops.gemm_relu_gemm((2 * x).bfloat16(), w1, w2, activation="identity").float()
+    one = ops.gemm_relu_gemm(x, w1, w2, activation="identity").float()
+    assert (lin - 2 * one).abs().max().item() <= 2e-2 * one.abs().max().item()
+    pos = ops.gemm_relu_gemm(x.abs(), w1.abs(), w2, activation="relu")
+    assert torch.equal(pos, ops.gemm_relu_gemm(x.abs(), w1.abs(), w2, activation="identity"))
+    assert ops.device_status(cuda) == 0
+
+
+def test_unsupported_shapes_raise(cuda):
+    x = torch.zeros(128, 64, dtype=torch.bfloat16, device=cuda)
+    w1 = torch.zeros(64, 256, dtype=torch.bfloat16, device=cuda)   # hidden 256 is not a multiple of 512
+    w2 = torch.zeros(256, 256, dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(_lib.DittoError) as e:
+        ops.gemm_relu_gemm(x, w1, w2)
+    assert e.value.code == _lib.ERR_UNSUPPORTED
