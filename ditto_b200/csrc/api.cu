@@ -137,8 +137,12 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
   if (w_layout != 0 && w_layout != 1) return DITTO_ERR_INVALID_ARG;
   if (epilogue != 0 && epilogue != 1) return DITTO_ERR_INVALID_ARG;
   if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
+  long long* trace = nullptr;
+#ifdef DITTO_TRACE
+  if (ws_bytes >= 128 * sizeof(long long)) trace = static_cast<long long*>(workspace);
+#endif
   return ditto_b200::launch_mlp_chain(x, w1, w2, y, batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, w_layout, epilogue,
-                                      status_word, static_cast<cudaStream_t>(stream));
+                                      status_word, static_cast<cudaStream_t>(stream), trace);
 }
 
 size_t ditto_b200_workspace_bytes(int op, int batch, int M, int N, int K, int L, int dtype) {

@@ -35,6 +35,17 @@
 #include "../../include/ditto_b200.h"
 #include "sm100_ptx.cuh"
 
+// Optional timeline capture for tuning (compiled in only with -DDITTO_TRACE): the first CTA stores
+// clock64() stamps of its rounds into the buffer passed as the call's workspace.
+#ifdef DITTO_TRACE
+#define DITTO_STAMP(i, k)                                                                   \
+  do {                                                                                      \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (i) < 8) p.trace[(i) * 16 + (k)] = clock64(); \
+  } while (0)
+#else
+#define DITTO_STAMP(i, k) do {} while (0)
+#endif
+
 namespace ditto_b200 {
 
 namespace {
@@ -60,6 +71,7 @@ struct MlpParams {
   int w_oi;            // 1: weights stored [out, in] (K-major B operands)
   int relu;
   int* status;
+  long long* trace;    // timeline buffer of -DDITTO_TRACE builds (null otherwise)
 };
 
 struct Bars {
@@ -256,6 +268,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     auto g1 = [&](int i) {
       const int hb = i & 1;
       if (i >= 2) ok = wait(&bar->h_tmem_empty[hb], ((i >> 1) - 1) & 1, 0x300 + i);
+      if (lane == 0) DITTO_STAMP(i, 0);
       for (int ks = 0; ks < ksteps1 && ok; ++ks) {
         ok = wait(&bar->full[cs], cph, 0x310 + i);
         if (!ok) break;
@@ -271,9 +284,12 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         advance();
       }
       if (ok) umma_commit_elected(&bar->h_tmem_full[hb], issuer);
+      if (lane == 0) DITTO_STAMP(i, 1);
     };
     auto g2 = [&](int i) {
+      if (lane == 0) DITTO_STAMP(i, 2);
       ok = wait(&bar->h_ready, i & 1, 0x400 + i);
+      if (lane == 0) DITTO_STAMP(i, 3);
       for (int c = 0; c < kCluster && ok; ++c) {
         for (int kk = 0; kk < 2 && ok; ++kk) {
           ok = wait(&bar->full[cs], cph, 0x410 + i);
@@ -291,6 +307,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         }
       }
       if (ok) umma_commit_elected(&bar->g2_done, issuer);
+      if (lane == 0) DITTO_STAMP(i, 4);
     };
     g1(0);
     if (rounds > 1 && ok) g1(1);
@@ -304,6 +321,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       for (int i = 0; i < rounds; ++i) {
         if (!mbar_wait(&bar->g2_done, i & 1, abort_word, 0x500 + i)) break;
+        DITTO_STAMP(i, 5);
         for (uint32_t c = 0; c < kCluster; ++c) mbar_arrive_cluster(&bar->slots_free, c);
       }
     }
@@ -319,6 +337,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (threadIdx.x == 0) DITTO_STAMP(i, 6);
       uint32_t h[kChunk];
       tmem_ld_x128_wait(tmem_h + hb * kChunk + lane_base, h);
       tc_fence_before_sync();
@@ -339,6 +358,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
+      if (threadIdx.x == 0) DITTO_STAMP(i, 7);
 #pragma unroll
       for (int ch = 0; ch < 16; ++ch) {
         const uint4 v = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
@@ -356,6 +376,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           if (c != q) bulk_copy_to_peer(map_to_cta(slot_addr, c), my_slot, kSlotBytes, map_to_cta(bar_addr, c));
         // the local chunk is in place; the expected bytes are the three chunks the peers push
         mbar_arrive_expect_tx(&bar->h_ready, (kCluster - 1) * kSlotBytes);
+        DITTO_STAMP(i, 8);
       }
     }
     if (ok) {
@@ -419,7 +440,7 @@ bool make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint
 }  // namespace
 
 int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
-                     bool bf16, int w_layout, int epilogue, int* status, cudaStream_t stream) {
+                     bool bf16, int w_layout, int epilogue, int* status, cudaStream_t stream, long long* trace) {
   // Coverage of the cluster kernel: 128-row blocks; hidden size a multiple of 4 chunks of 128;
   // N/4 Y columns per CTA (<= 256 TMEM columns, whole 64-column swizzle atoms); K in 64-wide steps.
   if (M % kRows || L % (kCluster * kChunk) || K % 64) return DITTO_ERR_UNSUPPORTED;
@@ -445,6 +466,7 @@ int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int
   p.w_oi = w_layout == 1;
   p.relu = epilogue == 1;
   p.status = status;
+  p.trace = trace;
   dim3 grid(kCluster * (M / kRows), batch, 1);
   cudaError_t e;
   if (bf16) {
