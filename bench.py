@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--units", type=int, default=0,
                     help="run only the first N units (slices / 128-row blocks) of the workload: small cases for profiling")
+    ap.add_argument("--also", default="cfg4,cfg3,cfg2",
+                    help="at 1 GPU, also time these workloads kernel-only and list them under other_workloads ('' = none)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the baseline sample")
     return ap.parse_args()
 
@@ -395,6 +397,28 @@ def main():
                "d2h_bytes_per_step": int(D.sum_over_ranks(run.out_bytes, device))}
     err = D.max_over_ranks(err, device)
     status = int(D.max_over_ranks(status, device))
+    run_flops, run_n, run_flushed = run.flops, run.n, run.flush is not None
+
+    others = []
+    if world == 1 and args.also and not args.units:
+        run = None
+        torch.cuda.empty_cache()
+        for name in [n for n in args.also.split(",") if n and n != args.workload and n in W.WORKLOADS]:
+            ow = W.WORKLOADS[name]
+            if ow.dtype == "float32":
+                continue
+            orun = GpuRun(ow, 0, 1, device)
+            oerr = orun.sanity()
+            oms, _ = orun.time_kernel(10, 3, barrier)
+            oms /= 10
+            otf = ow.flops / (oms * 1e-3) / 1e12
+            others.append({"workload": ow.name, "value": otf, "unit": "TFLOP/s", "ms_per_step": oms,
+                           "frac_of_tensor_peak": otf / peaks["tflops"],
+                           "algorithmic_gbs": ow.bytes / (oms * 1e-3) / 1e9,
+                           "frac_of_hbm_peak": ow.bytes / (oms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                           "sanity_max_abs_err_vs_torch_fp32": oerr, "device_status": ops.device_status(device)})
+            del orun
+            torch.cuda.empty_cache()
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -402,7 +426,7 @@ def main():
         cpu = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc}
 
     if rank == 0:
-        per_gpu_flops = run.flops                      # rank 0's launch (shards are equal for 1/2/4/8 GPUs)
+        per_gpu_flops = run_flops                      # rank 0's launch (shards are equal for 1/2/4/8 GPUs)
         achieved = per_gpu_flops / (ms_step * 1e-3) / 1e12
         unit_traffic = NCU_TRAFFIC_BYTES_PER_UNIT.get(args.workload)
         line = {
@@ -411,18 +435,19 @@ def main():
             "scaling": "strong", "vs_baseline": None,
             "dtype": {"float16": "fp16", "bfloat16": "bf16"}[w.dtype] + " in, f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": w.name, "kind": w.kind, "units": w.units, "units_per_gpu": run.n,
+            "config": {"workload": w.name, "kind": w.kind, "units": w.units, "units_per_gpu": run_n,
                        "shape_batch_M_N_K_L": [w.batch, w.M, w.N, w.K, w.L], "scale": w.scale,
                        "sharding": f"contiguous units over {world} GPU(s), no collective",
-                       "l2": "flushed between timed steps" if run.flush is not None else "inputs larger than L2"},
+                       "l2": "flushed between timed steps" if run_flushed else "inputs larger than L2"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"],
-                         "traffic": (unit_traffic * run.n) if unit_traffic else None,
+                         "traffic": (unit_traffic * run_n) if unit_traffic else None,
                          "peak_source": peaks["source"] + " cuBLAS bf16 burst",
                          "frac_of_sustained_peak": achieved / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
                          "algorithmic_gbs": w.bytes / world / (ms_step * 1e-3) / 1e9, "hbm_peak_gbs": peaks["hbm_gbs"]},
             "cpu_baseline": cpu,
             "e2e": e2e,
+            "other_workloads": others,
             "gpu_launches": launches,
             "clocks": clk.summary(),
             "sanity_max_abs_err_vs_torch_fp32": err,
