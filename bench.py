@@ -34,7 +34,11 @@ L2_BYTES = 126 * 1024 * 1024
 # DRAM traffic per launch of the dominant kernel from the ncu captures summarised under profiles/
 # (dram__bytes_read.sum + dram__bytes_write.sum, scaled by the number of units when the capture
 # ran a smaller launch of the same kernel).  None = not captured yet.
-NCU_TRAFFIC_BYTES_PER_UNIT = {}
+NCU_TRAFFIC_BYTES_PER_UNIT = {
+    "cfg5": (201.455e6 + 45.604e6) / 128,   # profiles/attention_bf16_d128_cfg5.md: 128-slice capture
+    "cfg3": (100.812e6 + 16.190e6) / 512,   # profiles/attention_fp16_d64_cfg3.md: full launch
+    "cfg4": (50.420e6 + 3.081e6) / 128,     # profiles/mlp_bf16_cfg4.md: full launch (128 row blocks)
+}
 
 
 def parse_args():
@@ -282,13 +286,15 @@ def cpu_sample(w, seconds):
     import numpy as np
     from oracle import chain_oracle as co          # the benchmark's CPU-baseline leg may use the oracle
     from ditto_b200 import workloads as W
-    cores = co.max_threads()
+    # all host cores this process may use; torchrun exports OMP_NUM_THREADS=1, which is not what a
+    # CPU baseline "on the box's host cores" means, so the thread count is set explicitly
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     kind = {"softmax": 0, "relu": 1, "identity": 2}[w.kind]
     if w.kind == "softmax":
         unit_flops = 2.0 * w.M * w.L * (w.K + w.N)
         q, k, v = W.attention_inputs(w, 0, min(8, w.batch))
         kt = np.ascontiguousarray(k.transpose(0, 2, 1))
-        run = lambda: co.baseline_chain_fp32(q, kt, v, kind, w.scale)
+        run = lambda: co.baseline_chain_fp32(q, kt, v, kind, w.scale, threads=cores)
         units_per_call, what = q.shape[0], "slices"
     else:
         unit_flops = 2.0 * 128 * w.L * (w.K + w.N)
@@ -300,7 +306,7 @@ def cpu_sample(w, seconds):
             w1, w2 = W.mlp_weights(w)
             a, b, c = W.mlp_inputs(w, 0, blocks)[None], w1[None], w2[None]
             units_per_call, what = blocks, "128-row blocks"
-        run = lambda: co.baseline_chain_fp32(a, b, c, kind, 1.0)
+        run = lambda: co.baseline_chain_fp32(a, b, c, kind, 1.0, threads=cores)
     run()                                           # warm-up, page in
     t0 = time.perf_counter()
     calls = 0
@@ -372,10 +378,10 @@ def main():
     from ditto_b200 import ops
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the chain kernels have no CPU fallback")
-    rank, world = D.init()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    rank, world = D.init(device=device)
     barrier = D.barrier
     peaks = measured_peaks()
 

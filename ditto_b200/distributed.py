@@ -11,14 +11,16 @@ def env_rank_world():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 
 
-def init(backend=None):
-    """Join the process group described by the torchrun environment (no-op for one process)."""
+def init(backend=None, device=None):
+    """Join the process group described by the torchrun environment (no-op for one process).
+    `device` (a CUDA device) binds the NCCL communicator to this rank's GPU."""
     rank, world = env_rank_world()
     if world > 1 and not dist.is_initialized():
         backend = backend or ("nccl" if torch.cuda.is_available() else "gloo")
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29500")
-        dist.init_process_group(backend=backend, rank=rank, world_size=world)
+        kwargs = {"device_id": device} if (backend == "nccl" and device is not None) else {}
+        dist.init_process_group(backend=backend, rank=rank, world_size=world, **kwargs)
     return rank, world
 
 
