@@ -22,6 +22,7 @@ OP_BMM_SOFTMAX_BMM = 0
 OP_GEMM_RELU_GEMM = 1
 FLAG_P_VIA_SMEM = 1
 FLAG_ONE_TILE = 2
+FLAG_TWO_TILES = 4
 
 EXPORTS = (
     "ditto_b200_bmm_softmax_bmm",

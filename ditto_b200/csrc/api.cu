@@ -98,6 +98,8 @@ int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void
   const bool bf16 = dtype == DITTO_DTYPE_BF16;
   const int d = K;
   int nt = (M % 256 == 0 && !(flags & DITTO_FLAG_ONE_TILE)) ? 2 : 1;
+  // d = 64: one tile per CTA with separate S / P columns, two CTAs per SM (see attention_sm100.cu)
+  if (d == 64 && !(flags & (DITTO_FLAG_TWO_TILES | DITTO_FLAG_P_VIA_SMEM))) nt = 1;
   const bool psmem = (flags & DITTO_FLAG_P_VIA_SMEM) != 0;
 
   ditto_b200::AttnParams p;

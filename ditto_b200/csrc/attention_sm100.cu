@@ -55,16 +55,23 @@ namespace {
 constexpr int kBM = 128;   // query rows per tile
 constexpr int kBN = 128;   // K/V rows per block
 constexpr int threads_for(int nt) { return 32 * (4 * nt + 2); }
-constexpr uint32_t kTmemCols = 512;
 constexpr int kSplit = 96;  // K/V rows in the first part of P (the rest follows separately)
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; P stays <= 2^8 with a stale max
+
+// "Separate-P" variant (one 128-row tile per CTA, D = 64, P through TMEM): S, O and P each get
+// their own TMEM columns (128 + 64 + 64 = 256), so the next S MMA no longer has to wait for the
+// P*V that reads P and runs while the softmax of the current block is still computing; with 256
+// TMEM columns and 80 KB of shared memory two such CTAs share an SM and hide each other's
+// prologue and epilogue.
+template <int D, int NT, bool PSMEM>
+constexpr bool kSeparateP = (NT == 1 && D == 64 && !PSMEM);
 
 template <int D, int NT, bool PSMEM>
 struct Smem {
   static constexpr int kTileQ = kBM * D * 2;
   static constexpr int kTileKV = kBN * D * 2;
   static constexpr int kTileP = kBM * kBN * 2;
-  static constexpr int kStages = PSMEM ? (D == 64 ? 3 : 1) : (D == 64 ? 4 : 2);
+  static constexpr int kStages = kSeparateP<D, NT, PSMEM> ? 2 : PSMEM ? (D == 64 ? 3 : 1) : (D == 64 ? 4 : 2);
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = kOffQ + NT * kTileQ;
   static constexpr int kOffV = kOffK + kStages * kTileKV;
@@ -77,6 +84,7 @@ struct Barriers {
   uint64_t q_full;
   uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
   uint64_t s_full[2], p_part[2][2], o_done[2];
+  uint64_t s_taken[2];   // separate-P variant: the softmax warps hold S in registers
   uint32_t tmem_base;
   uint32_t abort_word;
 };
@@ -96,8 +104,13 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }  // namespace
 
 template <bool BF16, int D, int NT, bool PSMEM>
-__global__ void __launch_bounds__(threads_for(NT), 1) attention_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 : 1)
+    attention_kernel(const __grid_constant__ AttnParams p) {
   using SM = Smem<D, NT, PSMEM>;
+  constexpr bool kSep = kSeparateP<D, NT, PSMEM>;
+  constexpr uint32_t kTmemCols = kSep ? 256 : 512;
+  constexpr uint32_t kColO = kSep ? 128 : 256;       // first accumulator column
+  constexpr uint32_t kColP = 192;                    // separate-P variant only
   constexpr int kStages = SM::kStages;
   constexpr int kAtoms = D / 64;  // 64-element (128-byte) chunks along the head dimension
 
@@ -127,6 +140,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) attention_kernel(const __g
       mbar_init(&bar->p_part[t][0], kBM);
       mbar_init(&bar->p_part[t][1], kBM);
       mbar_init(&bar->o_done[t], 1);
+      mbar_init(&bar->s_taken[t], kBM);
     }
     bar->abort_word = 0;
     fence_mbar_init();
@@ -229,10 +243,10 @@ __global__ void __launch_bounds__(threads_for(NT), 1) attention_kernel(const __g
         const uint32_t acc = i > 0 ? 1u : accumulate;
         if constexpr (PSMEM) {
           const uint64_t da = dp0 + ((t * SM::kTileP + (i / 4) * (kBM * 128) + (i % 4) * 32) >> 4);
-          umma_ss_elected(tmem_base + 256 + t * D, da, db + ((i * 2048) >> 4), idesc_o, acc, issuer);
+          umma_ss_elected(tmem_base + kColO + t * D, da, db + ((i * 2048) >> 4), idesc_o, acc, issuer);
         } else {
-          umma_ts_elected(tmem_base + 256 + t * D, tmem_base + t * kBN + i * 8, db + ((i * 2048) >> 4), idesc_o, acc,
-                          issuer);
+          umma_ts_elected(tmem_base + kColO + t * D, tmem_base + (kSep ? kColP : t * kBN) + i * 8,
+                          db + ((i * 2048) >> 4), idesc_o, acc, issuer);
         }
       }
     };
@@ -255,7 +269,36 @@ __global__ void __launch_bounds__(threads_for(NT), 1) attention_kernel(const __g
       ok = wait(&bar->v_full[0], 0, 0x400);
       if (ok && nkv > 1) ok = wait(&bar->k_full[1 % kStages], (1 / kStages) & 1, 0x600);
     }
-    for (int j = 0; j < nkv && ok; ++j) {
+    if constexpr (kSep) {
+      // S(j+1) is issued as soon as the softmax warps have taken S(j) out of TMEM, ahead of
+      // P*V(j): the tensor pipe computes the next scores while the exponentials run.
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int sv = j % kStages;
+        const int sk = (j + 1) % kStages;
+        const bool more = (j + 1 < nkv);
+        if (more) {
+          ok = wait(&bar->s_taken[0], j & 1, 0x480 + j);
+          if (!ok) break;
+          issue_s(0, sk);
+          umma_commit_elected(&bar->k_empty[sk], issuer);
+        }
+        ok = wait(&bar->p_part[0][0], j & 1, 0x500 + j);
+        if (!ok) break;
+        issue_pv(0, sv, 0, j > 0 ? 1u : 0u);
+        ok = wait(&bar->p_part[0][1], j & 1, 0x580 + j);
+        if (!ok) break;
+        issue_pv(0, sv, 1, 1u);
+        // v_empty doubles as "P*V(j) has finished" for the softmax warps (they overwrite P and may
+        // rescale O in the next iteration)
+        umma_commit_elected(&bar->v_empty[sv], issuer);
+        if (!more) umma_commit_elected(&bar->o_done[0], issuer);
+        if (more) {
+          ok = wait(&bar->v_full[sk], ((j + 1) / kStages) & 1, 0x400 + j);
+          if (ok && j + 2 < nkv) ok = wait(&bar->k_full[(j + 2) % kStages], ((j + 2) / kStages) & 1, 0x600 + j);
+        }
+      }
+    }
+    for (int j = 0; j < (kSep ? 0 : nkv) && ok; ++j) {
       const int sv = j % kStages;
       const int sk = (j + 1) % kStages;
       const bool more = (j + 1 < nkv);
@@ -297,7 +340,8 @@ __global__ void __launch_bounds__(threads_for(NT), 1) attention_kernel(const __g
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const uint32_t s_col = lane_base + t * kBN;
-    const uint32_t o_col = lane_base + 256 + t * D;
+    const uint32_t o_col = lane_base + kColO + t * D;
+    const uint32_t p_col = kSep ? lane_base + kColP : s_col;   // P overwrites S unless it has its own columns
     const float c = p.scale_log2;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
@@ -311,6 +355,10 @@ __global__ void __launch_bounds__(threads_for(NT), 1) attention_kernel(const __g
 
       uint32_t sv[kBN];
       tmem_ld_x128_wait(s_col, sv);
+      if constexpr (kSep) {
+        tc_fence_before_sync();
+        mbar_arrive(&bar->s_taken[t]);             // the S columns may be overwritten by S(j+1)
+      }
       if ((warp & 3) == 0) DITTO_STAMP(t * 256, j, 1);
 
       float mx[8];
@@ -323,6 +371,16 @@ __global__ void __launch_bounds__(threads_for(NT), 1) attention_kernel(const __g
           mx[u] = max3(mx[u], __uint_as_float(sv[i + 2 * u]), __uint_as_float(sv[i + 2 * u + 1]));
       }
       const float m_new = fmaxf(max3(m, mx[0], mx[1]), fmaxf(max3(mx[2], mx[3], mx[4]), max3(mx[5], mx[6], mx[7])));
+      if constexpr (kSep) {
+        if (j > 0) {
+          // P*V(j-1) must have finished before P is overwritten or O is rescaled; here S(j) was
+          // issued ahead of it, so s_full does not imply it.  Normally long complete.
+          ok = mbar_wait(&bar->v_empty[(j - 1) % kStages], ((j - 1) / kStages) & 1, abort_word, 0x900 + j);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+        }
+      }
       // Lazy rescale: keep the stale maximum while the true one is within
       // 2^kRescaleThreshold of it; the final division by l cancels the difference.
       const bool need = (m_new - m) * c > kRescaleThreshold;
@@ -384,13 +442,13 @@ __global__ void __launch_bounds__(threads_for(NT), 1) attention_kernel(const __g
             for (int i = 0; i < 32; ++i) lo[i] = pk[i];
 #pragma unroll
             for (int i = 0; i < 16; ++i) hi[i] = pk[32 + i];
-            tmem_st_x32(s_col, lo);
-            tmem_st_x16(s_col + 32, hi);
+            tmem_st_x32(p_col, lo);
+            tmem_st_x16(p_col + 32, hi);
           } else {
             uint32_t lo[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) lo[i] = pk[i];
-            tmem_st_x16(s_col + kFirst, lo);
+            tmem_st_x16(p_col + kFirst, lo);
           }
           tmem_wait_st();
         }
@@ -440,6 +498,8 @@ static cudaError_t launch_one(const AttnParams& p, int batch, cudaStream_t strea
   using SM = Smem<D, NT, PSMEM>;
   auto kern = attention_kernel<BF16, D, NT, PSMEM>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kBytes);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return e;
   dim3 grid(p.M / (NT * kBM), batch, 1);
   kern<<<grid, threads_for(NT), SM::kBytes, stream>>>(p);

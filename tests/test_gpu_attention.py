@@ -63,7 +63,8 @@ def test_umma_building_blocks(cuda, b_mn, a_tmem, dtype):
 
 @pytest.mark.parametrize("dtype,d", [("float16", 64), ("float16", 128), ("bfloat16", 64), ("bfloat16", 128)])
 @pytest.mark.parametrize("layout", ["LK", "KL"])
-@pytest.mark.parametrize("flags", [0, _lib.FLAG_ONE_TILE, _lib.FLAG_P_VIA_SMEM, _lib.FLAG_P_VIA_SMEM | _lib.FLAG_ONE_TILE])
+@pytest.mark.parametrize("flags", [0, _lib.FLAG_ONE_TILE, _lib.FLAG_TWO_TILES, _lib.FLAG_P_VIA_SMEM,
+                                   _lib.FLAG_P_VIA_SMEM | _lib.FLAG_ONE_TILE])
 def test_parity_small(cuda, oracle, dtype, d, layout, flags):
     """Every kernel variant (dtype x head dim x key layout x tile count x P staging) on small shapes."""
     for (b, M, L) in ((2, 128, 128), (3, 256, 384), (1, 512, 128)):
