@@ -122,7 +122,7 @@ int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void
 #ifdef DITTO_TRACE
   p.trace = ws_bytes >= 1280 * sizeof(long long) ? static_cast<long long*>(workspace) : nullptr;
 #endif
-  cudaError_t e = ditto_b200::launch_attention(p, batch, d, bf16, nt, psmem, static_cast<cudaStream_t>(stream));
+  cudaError_t e = ditto_b200::launch_attention(p, batch, d, bf16, nt, psmem, 0, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail("bmm_softmax_bmm launch", e);
   return DITTO_OK;
 }
@@ -139,6 +139,33 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
   if (w_layout != 0 && w_layout != 1) return DITTO_ERR_INVALID_ARG;
   if (epilogue != 0 && epilogue != 1) return DITTO_ERR_INVALID_ARG;
   if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
+  if (N == K && (K == 64 || K == 128)) {
+    // Small-N chains (the reference's shape family: N = K = 64, L = 512 ...): the result tile
+    // [128, N] fits TMEM next to the intermediate, so the chain runs on the attention kernel with
+    // the activation in place of the softmax: A = x, B = w1, C = w2.
+    if (M % 128 || L % 128 || batch > 65535) return DITTO_ERR_UNSUPPORTED;
+    if (w_layout != 0) return DITTO_ERR_UNSUPPORTED;   // w2 as [N, L] is not an operand form of that kernel
+    const bool bf16 = dtype == DITTO_DTYPE_BF16;
+    ditto_b200::AttnParams p;
+    std::memset(&p, 0, sizeof(p));
+    int rc = make_map_2d(&p.map_q, bf16, x, K, static_cast<uint64_t>(batch) * M, 64, 128);
+    if (rc) return rc;
+    rc = make_map_2d(&p.map_k, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, K);
+    if (rc) return rc;
+    rc = make_map_2d(&p.map_v, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, 128);
+    if (rc) return rc;
+    p.out = y;
+    p.M = M;
+    p.L = L;
+    p.k_transposed = 1;
+    p.scale_log2 = 1.0f;
+    p.status = status_word;
+    const int nt = (K == 64 || M % 256) ? 1 : 2;
+    cudaError_t e = ditto_b200::launch_attention(p, batch, K, bf16, nt, false, epilogue == 1 ? 1 : 2,
+                                                 static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail("gemm_relu_gemm launch", e);
+    return DITTO_OK;
+  }
   long long* trace = nullptr;
 #ifdef DITTO_TRACE
   if (ws_bytes >= 128 * sizeof(long long)) trace = static_cast<long long*>(workspace);

@@ -55,6 +55,7 @@ namespace {
 constexpr int kBM = 128;   // query rows per tile
 constexpr int kBN = 128;   // K/V rows per block
 constexpr int threads_for(int nt) { return 32 * (4 * nt + 2); }
+constexpr int kModeSoftmax = 0, kModeRelu = 1, kModeIdentity = 2;
 constexpr int kSplit = 96;  // K/V rows in the first part of P (the rest follows separately)
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; P stays <= 2^8 with a stale max
 
@@ -103,7 +104,10 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 }  // namespace
 
-template <bool BF16, int D, int NT, bool PSMEM>
+// MODE selects the element-wise stage between the two GEMMs: kModeSoftmax (online softmax and final
+// normalisation), kModeRelu / kModeIdentity (P = act(S) rounded to the input type, no scale, no
+// normalisation) -- the small-N form of the GEMM -> ReLU -> GEMM and plain GEMM -> GEMM chains.
+template <bool BF16, int D, int NT, bool PSMEM, int MODE>
 __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 : 1)
     attention_kernel(const __grid_constant__ AttnParams p) {
   using SM = Smem<D, NT, PSMEM>;
@@ -361,16 +365,19 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
       }
       if ((warp & 3) == 0) DITTO_STAMP(t * 256, j, 1);
 
-      float mx[8];
+      float m_new = m;
+      if constexpr (MODE == kModeSoftmax) {
+        float mx[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) mx[u] = fmaxf(__uint_as_float(sv[2 * u]), __uint_as_float(sv[2 * u + 1]));
+        for (int u = 0; u < 8; ++u) mx[u] = fmaxf(__uint_as_float(sv[2 * u]), __uint_as_float(sv[2 * u + 1]));
 #pragma unroll
-      for (int i = 16; i < kBN; i += 16) {
+        for (int i = 16; i < kBN; i += 16) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
-          mx[u] = max3(mx[u], __uint_as_float(sv[i + 2 * u]), __uint_as_float(sv[i + 2 * u + 1]));
+          for (int u = 0; u < 8; ++u)
+            mx[u] = max3(mx[u], __uint_as_float(sv[i + 2 * u]), __uint_as_float(sv[i + 2 * u + 1]));
+        }
+        m_new = fmaxf(max3(m, mx[0], mx[1]), fmaxf(max3(mx[2], mx[3], mx[4]), max3(mx[5], mx[6], mx[7])));
       }
-      const float m_new = fmaxf(max3(m, mx[0], mx[1]), fmaxf(max3(mx[2], mx[3], mx[4]), max3(mx[5], mx[6], mx[7])));
       if constexpr (kSep) {
         if (j > 0) {
           // P*V(j-1) must have finished before P is overwritten or O is rescaled; here S(j) was
@@ -383,8 +390,8 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
       }
       // Lazy rescale: keep the stale maximum while the true one is within
       // 2^kRescaleThreshold of it; the final division by l cancels the difference.
-      const bool need = (m_new - m) * c > kRescaleThreshold;
-      if (__any_sync(0xffffffffu, need)) {
+      const bool need = MODE == kModeSoftmax && (m_new - m) * c > kRescaleThreshold;
+      if (MODE == kModeSoftmax && __any_sync(0xffffffffu, need)) {
         const float f = ex2_approx((m - m_new) * c);
         if (j > 0) {
           // s_full(j) was committed after P*V(j-1) by the same thread and a commit covers every
@@ -415,8 +422,14 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
 #pragma unroll
         for (int i = 0; i < kFirst; ++i) {
           if (w0 + i < w1) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * (w0 + i)]), c, -mc));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * (w0 + i) + 1]), c, -mc));
+            float p0 = __uint_as_float(sv[2 * (w0 + i)]), p1 = __uint_as_float(sv[2 * (w0 + i) + 1]);
+            if constexpr (MODE == kModeSoftmax) {
+              p0 = ex2_approx(fmaf(p0, c, -mc));
+              p1 = ex2_approx(fmaf(p1, c, -mc));
+            } else if constexpr (MODE == kModeRelu) {
+              p0 = p0 > 0.f ? p0 : 0.f;                  // if_then_else(D > 0, D, 0) as in the reference
+              p1 = p1 > 0.f ? p1 : 0.f;
+            }
             sum0 += p0;
             sum1 += p1;
             pk[i] = pack2<BF16>(p0, p1);
@@ -466,7 +479,7 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
     }
     if (ok) {
       tc_fence_after_sync();
-      const float inv = 1.0f / l;
+      const float inv = MODE == kModeSoftmax ? 1.0f / l : 1.0f;
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
                       (static_cast<size_t>(slice) * p.M + m0 + t * kBM + row) * (D * 2);
 #pragma unroll
@@ -493,10 +506,10 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
 }
 
 // ------------------------------------------------------------------ launcher
-template <bool BF16, int D, int NT, bool PSMEM>
+template <bool BF16, int D, int NT, bool PSMEM, int MODE>
 static cudaError_t launch_one(const AttnParams& p, int batch, cudaStream_t stream) {
   using SM = Smem<D, NT, PSMEM>;
-  auto kern = attention_kernel<BF16, D, NT, PSMEM>;
+  auto kern = attention_kernel<BF16, D, NT, PSMEM, MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kBytes);
   if (e != cudaSuccess) return e;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
@@ -506,26 +519,25 @@ static cudaError_t launch_one(const AttnParams& p, int batch, cudaStream_t strea
   return cudaGetLastError();
 }
 
-cudaError_t launch_attention(const AttnParams& p, int batch, int d, bool bf16, int nt, bool psmem,
+cudaError_t launch_attention(const AttnParams& p, int batch, int d, bool bf16, int nt, bool psmem, int mode,
                              cudaStream_t stream) {
-#define DITTO_DISPATCH(BF, DD, NN, PS) \
-  if (bf16 == BF && d == DD && nt == NN && psmem == PS) return launch_one<BF, DD, NN, PS>(p, batch, stream);
-  DITTO_DISPATCH(false, 64, 1, false)
-  DITTO_DISPATCH(false, 64, 2, false)
-  DITTO_DISPATCH(false, 128, 1, false)
-  DITTO_DISPATCH(false, 128, 2, false)
-  DITTO_DISPATCH(true, 64, 1, false)
-  DITTO_DISPATCH(true, 64, 2, false)
-  DITTO_DISPATCH(true, 128, 1, false)
-  DITTO_DISPATCH(true, 128, 2, false)
-  DITTO_DISPATCH(false, 64, 1, true)
-  DITTO_DISPATCH(false, 64, 2, true)
-  DITTO_DISPATCH(false, 128, 1, true)
-  DITTO_DISPATCH(false, 128, 2, true)
-  DITTO_DISPATCH(true, 64, 1, true)
-  DITTO_DISPATCH(true, 64, 2, true)
-  DITTO_DISPATCH(true, 128, 1, true)
-  DITTO_DISPATCH(true, 128, 2, true)
+#define DITTO_DISPATCH(BF, DD, NN, PS, MO) \
+  if (bf16 == BF && d == DD && nt == NN && psmem == PS && mode == MO) \
+    return launch_one<BF, DD, NN, PS, MO>(p, batch, stream);
+#define DITTO_DISPATCH_SHAPES(PS, MO)  \
+  DITTO_DISPATCH(false, 64, 1, PS, MO) \
+  DITTO_DISPATCH(false, 64, 2, PS, MO) \
+  DITTO_DISPATCH(false, 128, 1, PS, MO) \
+  DITTO_DISPATCH(false, 128, 2, PS, MO) \
+  DITTO_DISPATCH(true, 64, 1, PS, MO)  \
+  DITTO_DISPATCH(true, 64, 2, PS, MO)  \
+  DITTO_DISPATCH(true, 128, 1, PS, MO) \
+  DITTO_DISPATCH(true, 128, 2, PS, MO)
+  DITTO_DISPATCH_SHAPES(false, kModeSoftmax)
+  DITTO_DISPATCH_SHAPES(true, kModeSoftmax)
+  DITTO_DISPATCH_SHAPES(false, kModeRelu)
+  DITTO_DISPATCH_SHAPES(false, kModeIdentity)
+#undef DITTO_DISPATCH_SHAPES
 #undef DITTO_DISPATCH
   return cudaErrorInvalidValue;
 }

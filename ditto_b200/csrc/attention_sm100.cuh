@@ -18,8 +18,9 @@ struct AttnParams {
   long long* trace;   // timeline buffer of -DDITTO_TRACE builds (null otherwise)
 };
 
-// d in {64,128}; nt in {1,2} query tiles per CTA; psmem: stage P through shared memory instead of TMEM.
-cudaError_t launch_attention(const AttnParams& p, int batch, int d, bool bf16, int nt, bool psmem,
+// d in {64,128}; nt in {1,2} query tiles per CTA; psmem: stage P through shared memory instead of TMEM
+// (softmax mode only); mode 0 softmax, 1 ReLU, 2 identity between the two GEMMs.
+cudaError_t launch_attention(const AttnParams& p, int batch, int d, bool bf16, int nt, bool psmem, int mode,
                              cudaStream_t stream);
 
 }  // namespace ditto_b200

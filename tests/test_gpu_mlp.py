@@ -115,3 +115,37 @@ def test_unsupported_shapes_raise(cuda):
     with pytest.raises(_lib.DittoError) as e:
         ops.gemm_relu_gemm(x, w1, w2)
     assert e.value.code == _lib.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("act", ["relu", "identity"])
+@pytest.mark.parametrize("d", [64, 128])
+def test_small_n_chains(cuda, oracle, dtype, act, d):
+    """N = K in {64, 128}: the reference's own shape family (benchmark/chimera/cuda/bmm_bmm_cuda.py
+    shapes table, python_test/auto_tensorize/test_hyper_fusion_cpu.py) -- batched, per-slice weights."""
+    for (batch, M, L) in ((2, 128, 128), (3, 256, 384), (8, 512, 512)):
+        rng = np.random.default_rng(31)
+        a = W._round(rng.uniform(-1, 1, (batch, M, d)).astype(np.float32), dtype)
+        b = W._round(rng.uniform(-1, 1, (batch, d, L)).astype(np.float32), dtype)
+        c = W._round(rng.uniform(-1, 1, (batch, L, d)).astype(np.float32), dtype)
+        got = _run(cuda, a, b, c, dtype, act, "IO")
+        want = oracle.gemm_act_gemm(a, b, c, 1 if act == "relu" else 0, ODT[dtype], wide=False)
+        # |result| grows like sqrt(K L) for U(-1,1) operands: scale the absolute floor with it
+        assert_close(got, want, dtype, f"{dtype} {act} d={d} {(batch, M, L)}", scale=float(np.abs(want).max()))
+
+
+def test_small_n_golden_and_cfg1_shape(cuda, oracle):
+    case = "chain_fp16_identity"
+    w = make_golden.workload(case)
+    A, B, C = make_golden.inputs(case)
+    out = ops.gemm_relu_gemm(_dev(A, w.dtype, cuda), _dev(B, w.dtype, cuda), _dev(C, w.dtype, cuda), activation="identity")
+    assert ops.device_status(cuda) == 0
+    stored = np.load(os.path.join(GOLDEN, case + ".npz"))["chain_fp32"]
+    assert_close(out.float().cpu().numpy(), stored, w.dtype, case, scale=float(np.abs(stored).max()))
+    # BASELINE config 1's shape (A[8,512,64] B[8,64,512] D[8,512,64], U(-1,1)) in fp16 on the GPU; the
+    # fp32 CPU case itself is checked in tests/test_oracle.py
+    cfg1 = W.WORKLOADS["cfg1"]
+    a, b, c = (W._round(t, "float16") for t in W.chain_inputs(cfg1))
+    got = _run(cuda, a, b, c, "float16", "identity", "IO")
+    want = oracle.gemm_act_gemm(a, b, c, 0, oracle.FP16, wide=False)
+    assert_close(got, want, "float16", "cfg1 shape fp16", scale=float(np.abs(want).max()))
