@@ -242,10 +242,35 @@ class ChainSchedule:
     scale: float
     device: HardwareParam
     param: CUDATensorizeParam
+    heads: int = 1     # "mha": heads folded into the packed [batch, M, 3 * heads * K] input
 
 
-def tensorize_cuda(layer: Layer, state: TensorizeHyperFusionState, cuda_param: HardwareParam,
+def _schedule_self_attention(layer: Layer, cuda_param, tensorize_param) -> ChainSchedule:
+    """The packed multi-head layer of nn/module/self_attention.py: one input [batch, M, 3 * hidden]."""
+    first, second, inter = validate(layer)
+    attrs = getattr(layer, "attention_attrs", None)
+    if attrs is None or len(layer.inputs) != 1:
+        raise FusionError("not a packed multi-head attention layer")
+    (src,) = layer.inputs
+    batch, M, k3 = src.shape
+    heads, d = attrs["num_heads"], attrs["head_dim"]
+    if k3 != 3 * heads * d:
+        raise FusionError(f"packed input has {k3} columns, expected {3 * heads * d}")
+    if src.dtype not in ("float16", "bfloat16"):
+        raise FusionError(f"the sm_100a kernels take float16 or bfloat16 operands, got {src.dtype}")
+    scale = 1.0
+    for op in inter:
+        scale = float(op.attrs.get("scale", scale))
+    return ChainSchedule(layer, "mha", batch, M, heads * d, d, M, src.dtype, scale, cuda_param,
+                         tensorize_param or CUDATensorizeParam(), heads)
+
+
+def tensorize_cuda(layer: Layer, state: TensorizeHyperFusionState = None, cuda_param: HardwareParam = None,
                    tensorize_param: CUDATensorizeParam = None) -> ChainSchedule:
+    if layer.name == "multi_head_attention_mma_layer":
+        return _schedule_self_attention(layer, cuda_param, tensorize_param)
+    if state is None:
+        raise FusionError("tensorize_cuda needs the TensorizeHyperFusionState of the chain")
     kind = state.chain_kind
     A, B, C = (layer.schedule_tensors + [None] * 3)[:3]
     ph = [t for t in layer.schedule_tensors[:-1]]

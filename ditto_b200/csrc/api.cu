@@ -117,6 +117,8 @@ int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void
   p.M = M;
   p.L = L;
   p.k_transposed = (k_layout == 0);
+  p.heads = 1;
+  p.out_ld = d;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word;
 #ifdef DITTO_TRACE
@@ -124,6 +126,44 @@ int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void
 #endif
   cudaError_t e = ditto_b200::launch_attention(p, batch, d, bf16, nt, psmem, 0, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail("bmm_softmax_bmm launch", e);
+  return DITTO_OK;
+}
+
+int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M, int heads, int head_dim, int dtype,
+                                    float scale, int flags, int* status_word, void* stream) {
+  if (!qkv || !out) return DITTO_ERR_INVALID_ARG;
+  if (batch <= 0 || M <= 0 || heads <= 0 || head_dim <= 0) return DITTO_ERR_INVALID_ARG;
+  if (!aligned16(qkv) || !aligned16(out)) return DITTO_ERR_INVALID_ARG;
+  if (!(scale > 0.f) || !std::isfinite(scale)) return DITTO_ERR_INVALID_ARG;
+  if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
+  if (head_dim != 64 && head_dim != 128) return DITTO_ERR_UNSUPPORTED;
+  if (M % 128) return DITTO_ERR_UNSUPPORTED;
+  if (static_cast<long long>(batch) * heads > 65535) return DITTO_ERR_UNSUPPORTED;
+  const bool bf16 = dtype == DITTO_DTYPE_BF16;
+  const int d = head_dim, hidden = heads * head_dim;
+  int nt = (M % 256 == 0 && !(flags & DITTO_FLAG_ONE_TILE)) ? 2 : 1;
+  if (d == 64 && !(flags & DITTO_FLAG_TWO_TILES)) nt = 1;
+  ditto_b200::AttnParams p;
+  std::memset(&p, 0, sizeof(p));
+  // one tensor map over the packed [batch*M, 3*hidden] matrix serves Q, K and V: the head split and
+  // the [b, M, h, d] -> [b*h, M, d] permutes become TMA coordinates
+  int rc = make_map_2d(&p.map_q, bf16, qkv, 3ull * hidden, static_cast<uint64_t>(batch) * M, 64, 128);
+  if (rc) return rc;
+  p.map_k = p.map_q;
+  p.map_v = p.map_q;
+  p.out = out;
+  p.M = M;
+  p.L = M;
+  p.k_transposed = 0;
+  p.heads = heads;
+  p.q_col0 = 0;
+  p.k_col0 = hidden;
+  p.v_col0 = 2 * hidden;
+  p.out_ld = hidden;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status_word;
+  cudaError_t e = ditto_b200::launch_attention(p, batch * heads, d, bf16, nt, false, 0, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("multi_head_attention launch", e);
   return DITTO_OK;
 }
 
@@ -158,6 +198,8 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
     p.M = M;
     p.L = L;
     p.k_transposed = 1;
+    p.heads = 1;
+    p.out_ld = N;
     p.scale_log2 = 1.0f;
     p.status = status_word;
     const int nt = (K == 64 || M % 256) ? 1 : 2;

@@ -128,6 +128,10 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int slice = blockIdx.y;
+  // Packed multi-head input: slice = (sequence, head); rows come from the sequence, columns from
+  // the head.  Plain batched input has heads == 1 and zero column offsets.
+  const int seq = slice / p.heads;
+  const int head_col = (slice % p.heads) * D;
   const int m0 = blockIdx.x * (NT * kBM);
   const int nkv = p.L / kBN;
 
@@ -167,8 +171,8 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
       mbar_arrive_expect_tx(&bar->q_full, NT * SM::kTileQ);
       for (int t = 0; t < NT; ++t)
         for (int a = 0; a < kAtoms; ++a)
-          tma_load_2d(smem + SM::kOffQ + t * SM::kTileQ + a * (kBM * 128), &p.map_q, &bar->q_full, a * 64,
-                      slice * p.M + m0 + t * kBM);
+          tma_load_2d(smem + SM::kOffQ + t * SM::kTileQ + a * (kBM * 128), &p.map_q, &bar->q_full,
+                      p.q_col0 + head_col + a * 64, seq * p.M + m0 + t * kBM);
       bool ok = true;
       int armed_k[4] = {-1, -1, -1, -1}, armed_v[4] = {-1, -1, -1, -1};  // parity of the newest armed phase
       for (int j = 0; j < nkv; ++j) {
@@ -186,7 +190,8 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
               tma_load_2d(dst + a * (D * 128), &p.map_k, &bar->k_full[s], j * kBN + a * 64, slice * D);
           } else {
             for (int a = 0; a < kAtoms; ++a)
-              tma_load_2d(dst + a * (kBN * 128), &p.map_k, &bar->k_full[s], a * 64, slice * p.L + j * kBN);
+              tma_load_2d(dst + a * (kBN * 128), &p.map_k, &bar->k_full[s], p.k_col0 + head_col + a * 64,
+                          seq * p.L + j * kBN);
           }
         }
         ok = mbar_wait(&bar->v_empty[s], ph ^ 1, abort_word, 0x200 + j);
@@ -196,7 +201,8 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
           mbar_arrive_expect_tx(&bar->v_full[s], SM::kTileKV);
           armed_v[s] = static_cast<int>(ph);
           for (int a = 0; a < kAtoms; ++a)
-            tma_load_2d(dst + a * (kBN * 128), &p.map_v, &bar->v_full[s], a * 64, slice * p.L + j * kBN);
+            tma_load_2d(dst + a * (kBN * 128), &p.map_v, &bar->v_full[s], p.v_col0 + head_col + a * 64,
+                        seq * p.L + j * kBN);
         }
       }
       if (!ok) {
@@ -481,7 +487,7 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
       tc_fence_after_sync();
       const float inv = MODE == kModeSoftmax ? 1.0f / l : 1.0f;
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
-                      (static_cast<size_t>(slice) * p.M + m0 + t * kBM + row) * (D * 2);
+                      ((static_cast<size_t>(seq) * p.M + m0 + t * kBM + row) * p.out_ld + head_col) * 2;
 #pragma unroll
       for (int cc = 0; cc < D; cc += 32) {
         uint32_t o[32];

@@ -85,6 +85,35 @@ def bmm_softmax_bmm(query, key, value, out=None, scale=1.0, key_layout="KL", fla
     return out
 
 
+def multi_head_attention(qkv, num_heads, out=None, scale=1.0, flags=0):
+    """Self-attention over a packed tensor: qkv [batch, M, 3 * hidden] = [Q | K | V] per row,
+    hidden = num_heads * head_dim; returns [batch, M, hidden].  The head split / merge of
+    nn/module/self_attention.py:46-73 is folded into the kernel's addressing (no reshape passes)."""
+    global launch_count
+    _check_tensor(qkv, "qkv")
+    if qkv.dtype not in _DTYPE_CODE:
+        raise TypeError(f"qkv dtype {qkv.dtype} not supported (float16 / bfloat16)")
+    if qkv.dim() != 3 or qkv.shape[2] % (3 * num_heads):
+        raise ValueError(f"qkv must be [batch, M, 3 * hidden] with hidden divisible by num_heads, got {tuple(qkv.shape)}")
+    batch, M, k3 = qkv.shape
+    hidden = k3 // 3
+    if out is None:
+        out = torch.empty((batch, M, hidden), dtype=qkv.dtype, device=qkv.device)
+    else:
+        _check_tensor(out, "out", qkv.dtype)
+        if tuple(out.shape) != (batch, M, hidden):
+            raise ValueError(f"out has shape {tuple(out.shape)}, expected {(batch, M, hidden)}")
+    lib = _lib.load()
+    with torch.cuda.device(qkv.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.ditto_b200_multi_head_attention(qkv.data_ptr(), out.data_ptr(), batch, M, num_heads, hidden // num_heads,
+                                                 _DTYPE_CODE[qkv.dtype], float(scale), int(flags),
+                                                 _status_word(qkv.device).data_ptr(), stream)
+    _lib.check(rc, "ditto_b200_multi_head_attention")
+    launch_count += 1
+    return out
+
+
 def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO"):
     """out = act(x @ w1) @ w2 with the hidden activations kept on chip.
 

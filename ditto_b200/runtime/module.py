@@ -31,6 +31,16 @@ class ChainModule:
 
     def _check(self, tensors):
         s = self.schedule
+        if s.kind == "mha":
+            if len(tensors) != 2:
+                raise TypeError(f"{self.entry_name} takes 1 input and 1 output, got {len(tensors)} tensors")
+            want = [(s.batch, s.M, 3 * s.N), (s.batch, s.M, s.N)]
+            for t, shp, nm in zip(tensors, want, ("qkv", "out")):
+                if tuple(t.shape) != shp:
+                    raise ValueError(f"{nm}: shape {tuple(t.shape)} does not match the compiled shape {shp}")
+                if t.dtype != _TORCH_DTYPE[s.dtype]:
+                    raise TypeError(f"{nm}: dtype {t.dtype} does not match the compiled dtype {s.dtype}")
+            return
         if len(tensors) != 4:
             raise TypeError(f"{self.entry_name} takes 3 inputs and 1 output, got {len(tensors)} tensors")
         want = [(s.batch, s.M, s.K), (s.batch, s.K, s.L), (s.batch, s.L, s.N), (s.batch, s.M, s.N)]
@@ -42,8 +52,11 @@ class ChainModule:
 
     def __call__(self, *tensors):
         self._check(tensors)
-        a, b, c, f = tensors
         s = self.schedule
+        if s.kind == "mha":
+            ops.multi_head_attention(tensors[0], s.heads, out=tensors[1], scale=s.scale)
+            return
+        a, b, c, f = tensors
         if s.kind == "softmax":
             ops.bmm_softmax_bmm(a, b, c, out=f, scale=s.scale, key_layout="KL")
         else:

@@ -58,6 +58,15 @@ int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void
                                int K, int L, int dtype, int k_layout, float scale, int flags, void* workspace,
                                size_t ws_bytes, int* status_word, void* stream);
 
+/* Multi-head self-attention over a packed tensor, replacing the layer "multi_head_attention_mma_layer"
+ * that MultiHeadAttentionMMA builds (python/ditto/auto_compute/nn/module/self_attention.py:15-82):
+ *   qkv [batch, M, 3 * heads * head_dim] = [Q | K | V] per row; out [batch, M, heads * head_dim].
+ * The reference splits, reshapes to [batch*heads, M, d], transposes K and reshapes the result back in
+ * six extra passes; here the head split is done by the TMA coordinates and the result is written in
+ * place.  scale 1.0 = the reference's semantics.  head_dim in {64, 128}; M a multiple of 128. */
+int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M, int heads, int head_dim, int dtype,
+                                    float scale, int flags, int* status_word, void* stream);
+
 /* Fused MLP chain  y = act(X W1) W2 with the hidden activations kept on chip, replacing the
  * module built from BatchGemmReluGemm (python_test/auto_tensorize/test_hyper_fusion_cpu.py:24-96,
  * evaluation/cpu/bmm_relu_bmm.py:56-125) and, with epilogue 0, BatchGemmGemm

@@ -165,3 +165,12 @@ def test_seeded_inputs_do_not_depend_on_the_shard():
     assert abs(float(q_all.std()) - 1.0) < 0.02
     import numpy as np
     assert (q2.astype(np.float16).astype(np.float32) == q2).all()  # already representable in fp16
+
+
+def test_self_attention_layer_schedules_without_a_fusion_state():
+    mha = ac.nn.module.MultiHeadAttentionMMA(12, 768, in_dtype="float16")
+    y = mha(ac.layer_tensor([4, 512, 2304], dtype="float16"))
+    sch = at.tensorize_cuda(y.layer, None, hw.query_hw_param("gpu.cuda.B200"))
+    assert (sch.kind, sch.batch, sch.M, sch.N, sch.K, sch.L, sch.heads) == ("mha", 4, 512, 768, 64, 512, 12)
+    func = ditto.build(sch, y.layer.schedule_tensors, "cuda")
+    assert func.entry_name == "default_function"
