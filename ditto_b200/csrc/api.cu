@@ -246,6 +246,30 @@ int ditto_b200_selftest_umma(const void* a, const void* b, float* c, int N, int 
   return DITTO_OK;
 }
 
+int ditto_b200_selftest_umma_pair(const void* a, const void* b, float* c, int N, int K, int dtype, int b_mn,
+                                  int* status_word, void* stream) {
+  if (!a || !b || !c) return DITTO_ERR_INVALID_ARG;
+  if (N <= 0 || K <= 0 || N % 128 || K % 64 || N > 256 || K > 256) return DITTO_ERR_UNSUPPORTED;
+  if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
+  const bool bf16 = dtype == DITTO_DTYPE_BF16;
+  ditto_b200::SelftestParams p;
+  std::memset(&p, 0, sizeof(p));
+  int rc = make_map_2d(&p.map_a, bf16, a, K, 256, 64, 128);
+  if (rc) return rc;
+  rc = b_mn ? make_map_2d(&p.map_b, bf16, b, N, K, 64, K) : make_map_2d(&p.map_b, bf16, b, K, N, 64, N / 2);
+  if (rc) return rc;
+  p.a_global = a;
+  p.c = c;
+  p.N = N;
+  p.K = K;
+  p.b_mn = b_mn ? 1 : 0;
+  p.bf16 = bf16 ? 1 : 0;
+  p.status = status_word;
+  cudaError_t e = ditto_b200::launch_umma_pair_selftest(p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("pair selftest launch", e);
+  return DITTO_OK;
+}
+
 const char* ditto_b200_strerror(int code) {
   switch (code) {
     case DITTO_OK: return "ok";

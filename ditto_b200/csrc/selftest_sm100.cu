@@ -122,3 +122,104 @@ cudaError_t launch_umma_selftest(const SelftestParams& p, cudaStream_t stream) {
 }
 
 }  // namespace ditto_b200
+
+// ------------------------------------------------------------------ CTA-pair self test
+// C[256, N] = A[256, K] * B with one cta_group::2 MMA chain: cluster of two CTAs, each holding its
+// 128 rows of A and half of B's N extent, the leader (rank 0) issuing.  Checks the pair mechanics
+// (2-CTA TMEM allocation, TMA byte counts reported to the leader's barrier, operand split,
+// completion signalled to both CTAs) in isolation.
+namespace ditto_b200 {
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
+    umma_pair_selftest_kernel(const __grid_constant__ SelftestParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int half_n = p.N / 2;
+  const int a_bytes = 128 * p.K * 2;
+  const int b_bytes = half_n * p.K * 2;
+  uint8_t* sa = smem;
+  uint8_t* sb = smem + a_bytes;
+  TestBars* bar = reinterpret_cast<TestBars*>(sb + b_bytes);
+  volatile uint32_t* abort_word = &bar->abort_word;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->full, 1);
+    mbar_init(&bar->done, 1);
+    bar->abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc_pair(&bar->tmem_base, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bar->tmem_base;
+
+  if (threadIdx.x == 0) {
+    const uint32_t leader_full = map_to_cta(smem_u32(&bar->full), 0);
+    if (rank == 0) mbar_arrive_expect_tx(&bar->full, 2 * (a_bytes + b_bytes));
+    for (int a = 0; a < p.K / 64; ++a)
+      tma_load_2d_pair(sa + a * (128 * 128), &p.map_a, leader_full, a * 64, static_cast<int>(rank) * 128);
+    if (p.b_mn) {
+      for (int a = 0; a < half_n / 64; ++a)
+        tma_load_2d_pair(sb + a * (p.K * 128), &p.map_b, leader_full, static_cast<int>(rank) * half_n + a * 64, 0);
+    } else {
+      for (int a = 0; a < p.K / 64; ++a)
+        tma_load_2d_pair(sb + a * (half_n * 128), &p.map_b, leader_full, a * 64, static_cast<int>(rank) * half_n);
+    }
+  }
+  bool ok = true;
+  if (warp == 0 && rank == 0) {
+    const uint32_t issuer = elect_one();
+    ok = mbar_wait(&bar->full, 0, abort_word, 0x10);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after_sync();
+    if (ok) {
+      const uint32_t idesc = umma_idesc_f16(p.bf16 != 0, 256, p.N, false, p.b_mn != 0);
+      const uint32_t a_addr = smem_u32(sa), b_addr = smem_u32(sb);
+      for (int i = 0; i < p.K / 16; ++i) {
+        const uint64_t da = umma_desc_sw128(a_addr + (i / 4) * (128 * 128) + (i % 4) * 32, 16, 1024);
+        const uint64_t db = p.b_mn ? umma_desc_sw128(b_addr + i * 2048, p.K * 128, 1024)
+                                   : umma_desc_sw128(b_addr + (i / 4) * (half_n * 128) + (i % 4) * 32, 16, 1024);
+        umma_ss_pair_elected(tmem_base, da, db, idesc, i > 0, issuer);
+      }
+      umma_commit_pair_elected(&bar->done, 0x3, issuer);
+    }
+  }
+  __syncwarp();
+  ok = mbar_wait(&bar->done, 0, abort_word, 0x20);
+  ok = __all_sync(0xffffffffu, ok);
+  if (ok) {
+    tc_fence_after_sync();
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    float* crow = p.c + (static_cast<size_t>(rank) * 128 + threadIdx.x) * p.N;
+    for (int c = 0; c < p.N; c += 8) {
+      uint32_t r[8];
+      tmem_ld_x8_wait(lane_base + c, r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) crow[c + i] = __uint_as_float(r[i]);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 0) {
+    tmem_dealloc_pair(tmem_base, 512);
+    if (lane == 0 && bar->abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, static_cast<int>(bar->abort_word));
+  }
+}
+
+cudaError_t launch_umma_pair_selftest(const SelftestParams& p, cudaStream_t stream) {
+  const int smem = 128 * p.K * 2 + (p.N / 2) * p.K * 2 + 64 + 1024;
+  cudaError_t e = cudaFuncSetAttribute(umma_pair_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  umma_pair_selftest_kernel<<<2, 128, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace ditto_b200

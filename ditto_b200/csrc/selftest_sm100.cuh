@@ -16,5 +16,7 @@ struct SelftestParams {
 };
 
 cudaError_t launch_umma_selftest(const SelftestParams& p, cudaStream_t stream);
+// CTA-pair variant: A has 256 rows (box 64 x 128 per CTA), B boxes cover half of N.
+cudaError_t launch_umma_pair_selftest(const SelftestParams& p, cudaStream_t stream);
 
 }  // namespace ditto_b200

@@ -193,6 +193,67 @@ __device__ __forceinline__ void umma_commit_elected(uint64_t* bar, uint32_t issu
       : "memory");
 }
 
+// ---------------------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs with consecutive cluster ranks (even = leader) execute one MMA of M = 256: each holds
+// its 128 rows of A and half of B's N extent in its own shared memory (same offsets in both) and
+// receives its 128 rows of D in its own TMEM.  Only the leader issues; completion is signalled to
+// barriers at the same offset in both CTAs.  No load here is multicast: each CTA fetches its own
+// operands, and its TMA loads report their bytes to the leader's barrier.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t cta) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta));
+  return remote;
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// 2-D tiled load into this CTA's shared memory whose byte count is reported to `bar_cluster_addr`,
+// a shared::cluster address that may lie in the pair's leader CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ss_pair_elected(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                     uint32_t accumulate, uint32_t issuer) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(issuer)
+      : "memory");
+}
+// Arrive (once) on the barrier at this offset in every CTA named by `cta_mask` when all MMAs issued
+// so far by this thread have retired.
+__device__ __forceinline__ void umma_commit_pair_elected(uint64_t* bar, uint32_t cta_mask, uint32_t issuer) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t.reg .b16 lo, hi;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "mov.b32 {lo, hi}, %1;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], lo;\n\t}"
+      ::"r"(smem_u32(bar)), "r"(cta_mask), "r"(issuer)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor for 128-byte-swizzled tiles (what a TMA box
 // with CU_TENSOR_MAP_SWIZZLE_128B and a 128-byte inner extent produces).
 //   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4

@@ -88,6 +88,11 @@ size_t ditto_b200_workspace_bytes(int op, int batch, int M, int N, int K, int L,
 int ditto_b200_selftest_umma(const void* a, const void* b, float* c, int N, int K, int dtype, int b_mn,
                              int a_tmem, int* status_word, void* stream);
 
+/* The same check for a CTA pair (cta_group::2): c[256, N] = a[256, K] * b, N in {128, 256}.
+ * No counterpart in the reference. */
+int ditto_b200_selftest_umma_pair(const void* a, const void* b, float* c, int N, int K, int dtype, int b_mn,
+                                  int* status_word, void* stream);
+
 const char* ditto_b200_strerror(int code);
 /* Text of the last CUDA / driver error seen by the calling thread ("" if none). */
 const char* ditto_b200_last_cuda_error(void);

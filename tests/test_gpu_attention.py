@@ -222,3 +222,25 @@ def test_unsupported_shapes_raise(cuda):
         ops.bmm_softmax_bmm(kv, kv[:, :, :32].contiguous(), kv, key_layout="LK")
     with pytest.raises(ValueError):
         ops.bmm_softmax_bmm(kv, kv.transpose(1, 2), kv, key_layout="KL")   # non-contiguous
+
+
+@pytest.mark.parametrize("b_mn", [0, 1])
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_umma_pair_building_block(cuda, b_mn, dtype):
+    """One cta_group::2 MMA chain (two CTAs, M = 256) against a CPU product: 2-CTA TMEM allocation,
+    TMA byte counts reported to the leader's barrier, the split of B between the CTAs and the
+    completion signal to both."""
+    lib = _lib.load()
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    for N, K in ((128, 64), (256, 64), (128, 256), (256, 256)):
+        rng = np.random.default_rng(N * 1000 + K + 7)
+        a = W._round(rng.standard_normal((256, K)).astype(np.float32), dtype)
+        b = W._round(rng.standard_normal((K, N) if b_mn else (N, K)).astype(np.float32), dtype)
+        c = torch.full((256, N), float("nan"), device=cuda)
+        da, db = _dev(a, dtype, cuda), _dev(b, dtype, cuda)
+        rc = lib.ditto_b200_selftest_umma_pair(da.data_ptr(), db.data_ptr(), c.data_ptr(), N, K, ODT[dtype], b_mn,
+                                               status.data_ptr(), None)
+        torch.cuda.synchronize()
+        assert rc == 0 and int(status.item()) == 0
+        want = a.astype(np.float64) @ (b if b_mn else b.T).astype(np.float64)
+        np.testing.assert_allclose(c.cpu().numpy(), want, rtol=1e-5, atol=2e-4)
