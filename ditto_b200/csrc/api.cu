@@ -177,7 +177,7 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
   if (!aligned16(x) || !aligned16(w1) || !aligned16(w2) || !aligned16(y)) return DITTO_ERR_INVALID_ARG;
   if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
   if (w_layout != 0 && w_layout != 1) return DITTO_ERR_INVALID_ARG;
-  if (epilogue != 0 && epilogue != 1) return DITTO_ERR_INVALID_ARG;
+  if ((epilogue & ~0x200) != 0 && (epilogue & ~0x200) != 1) return DITTO_ERR_INVALID_ARG;
   if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
   if (N == K && (K == 64 || K == 128)) {
     // Small-N chains (the reference's shape family: N = K = 64, L = 512 ...): the result tile
@@ -203,7 +203,7 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
     p.scale_log2 = 1.0f;
     p.status = status_word;
     const int nt = (K == 64 || M % 256) ? 1 : 2;
-    cudaError_t e = ditto_b200::launch_attention(p, batch, K, bf16, nt, false, epilogue == 1 ? 1 : 2,
+    cudaError_t e = ditto_b200::launch_attention(p, batch, K, bf16, nt, false, (epilogue & 0xff) == 1 ? 1 : 2,
                                                  static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail("gemm_relu_gemm launch", e);
     return DITTO_OK;

@@ -33,6 +33,7 @@
 #include <cstring>
 
 #include "../../include/ditto_b200.h"
+#include "mlp_common.cuh"
 #include "sm100_ptx.cuh"
 
 // Optional timeline capture for tuning (compiled in only with -DDITTO_TRACE): the first CTA stores
@@ -86,46 +87,6 @@ struct Bars {
   uint32_t abort_word;
 };
 static_assert(sizeof(Bars) <= 256, "barrier block too large");
-
-template <bool BF16>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  if constexpr (BF16) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  } else {
-    __half2 v = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-}
-
-// Bulk copy from this CTA's shared memory into a peer's; completion (bytes) on the peer's mbarrier.
-__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, const void* src, uint32_t bytes,
-                                                  uint32_t mbar_cluster_addr) {
-  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst_cluster_addr), "r"(smem_u32(src)), "r"(bytes), "r"(mbar_cluster_addr)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word,
-                                                  uint32_t code) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if (*abort_word != 0u) return false;
-    if (spin > 4096u) __nanosleep(64);
-  }
-  atomicCAS(const_cast<uint32_t*>(abort_word), 0u, code);
-  return false;
-}
 
 }  // namespace
 
@@ -359,8 +320,10 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       if (threadIdx.x == 0) {
         const uint32_t slot_addr = smem_u32(my_slot);
         const uint32_t bar_addr = smem_u32(&bar->h_ready);
-        for (uint32_t c = 0; c < kCluster; ++c)
-          if (c != q) bulk_copy_to_peer(map_to_cta(slot_addr, c), my_slot, kSlotBytes, map_to_cta(bar_addr, c));
+        for (uint32_t d = 1; d < kCluster; ++d) {
+          const uint32_t c = (q + d) % kCluster;   // rotated: senders do not all hit the same destination first
+          bulk_copy_to_peer(map_to_cta(slot_addr, c), my_slot, kSlotBytes, map_to_cta(bar_addr, c));
+        }
         // the local chunk is in place; the expected bytes are the three chunks the peers push
         mbar_arrive_expect_tx(&bar->h_ready, (kCluster - 1) * kSlotBytes);
         DITTO_STAMP(i, 8);
@@ -403,8 +366,10 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-bool make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint32_t box_cols,
-              uint32_t box_rows) {
+}  // namespace
+
+bool mlp_make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint32_t box_cols,
+                  uint32_t box_rows) {
   static EncodeTiledFn fn = nullptr;
   if (fn == nullptr) {
     void* ptr = nullptr;
@@ -424,10 +389,17 @@ bool make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-}  // namespace
 
 int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
                      bool bf16, int w_layout, int epilogue, int* status, cudaStream_t stream, long long* trace) {
+  // CTA-pair kernel (2-SM MMAs, a third fewer operand bytes per CTA) on request.  It is correct
+  // but, as measured, slower than this kernel: its rounds are paced by the exchange of hidden chunks
+  // among eight CTAs instead of by the operand feed.
+  if (epilogue & 0x200) {
+    if (!mlp_pair_supported(M, N, K, L)) return DITTO_ERR_UNSUPPORTED;
+    return launch_mlp_pair(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, epilogue & 0xff, status, stream, trace);
+  }
+  epilogue &= 0xff;
   // Coverage of the cluster kernel: 128-row blocks; hidden size a multiple of 4 chunks of 128;
   // N/4 Y columns per CTA (<= 256 TMEM columns, whole 64-column swizzle atoms); K in 64-wide steps.
   if (M % kRows || L % (kCluster * kChunk) || K % 64) return DITTO_ERR_UNSUPPORTED;
@@ -436,13 +408,13 @@ int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int
   const int NS = N / kCluster;
   MlpParams p;
   std::memset(&p, 0, sizeof(p));
-  bool ok = make_map(&p.map_x, bf16, x, K, static_cast<uint64_t>(batch) * M, 64, 128);
+  bool ok = mlp_make_map(&p.map_x, bf16, x, K, static_cast<uint64_t>(batch) * M, 64, 128);
   if (w_layout == 1) {
-    ok = ok && make_map(&p.map_w1, bf16, w1, K, static_cast<uint64_t>(batch) * L, 64, 128);
-    ok = ok && make_map(&p.map_w2, bf16, w2, L, static_cast<uint64_t>(batch) * N, 64, NS);
+    ok = ok && mlp_make_map(&p.map_w1, bf16, w1, K, static_cast<uint64_t>(batch) * L, 64, 128);
+    ok = ok && mlp_make_map(&p.map_w2, bf16, w2, L, static_cast<uint64_t>(batch) * N, 64, NS);
   } else {
-    ok = ok && make_map(&p.map_w1, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, 64);
-    ok = ok && make_map(&p.map_w2, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, 64);
+    ok = ok && mlp_make_map(&p.map_w1, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, 64);
+    ok = ok && mlp_make_map(&p.map_w2, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, 64);
   }
   if (!ok) return DITTO_ERR_DRIVER;
   p.y = y;

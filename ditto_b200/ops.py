@@ -114,12 +114,13 @@ def multi_head_attention(qkv, num_heads, out=None, scale=1.0, flags=0):
     return out
 
 
-def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO"):
+def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO", pair_mma=False):
     """out = act(x @ w1) @ w2 with the hidden activations kept on chip.
 
     x [batch, M, K] or [M, K]; w1 [batch, K, L] / [K, L]; w2 [batch, L, N] / [L, N] when
     weight_layout == "IO" ([in, out]); "OI" takes the transposed [out, in] weights of
-    nn/functional/linear.py.  activation: "relu" or "identity".
+    nn/functional/linear.py.  activation: "relu" or "identity".  pair_mma selects the kernel
+    variant built on 2-SM MMAs (M % 256 == 0, N in {512, 1024}).
     """
     global launch_count
     _check_tensor(x, "x")
@@ -158,7 +159,8 @@ def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO"):
     with torch.cuda.device(x.device):
         stream = torch.cuda.current_stream().cuda_stream
         rc = lib.ditto_b200_gemm_relu_gemm(x3.data_ptr(), w13.data_ptr(), w23.data_ptr(), out3.data_ptr(), batch, M, N,
-                                           K, L, _DTYPE_CODE[x.dtype], wl, 1 if activation == "relu" else 0, None, 0,
+                                           K, L, _DTYPE_CODE[x.dtype], wl,
+                                           (1 if activation == "relu" else 0) | (0x200 if pair_mma else 0), None, 0,
                                            _status_word(x.device).data_ptr(), stream)
     _lib.check(rc, "ditto_b200_gemm_relu_gemm")
     launch_count += 1

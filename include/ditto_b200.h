@@ -37,6 +37,8 @@ extern "C" {
 #define DITTO_DTYPE_FP16 0
 #define DITTO_DTYPE_BF16 1
 
+#define DITTO_EPILOGUE_PAIR_MMA 0x200
+
 #define DITTO_OP_BMM_SOFTMAX_BMM 0
 #define DITTO_OP_GEMM_RELU_GEMM 1
 
@@ -73,7 +75,8 @@ int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M
  * (benchmark/chimera/cuda/bmm_bmm_cuda.py:69-150).
  *   x [batch, M, K]; w1 [batch, K, L]; w2 [batch, L, N]; y [batch, M, N]
  *   w_layout 0: weights as above ([in, out]); 1: [out, in] as in nn/functional/linear.py:4-41
- *   epilogue 0: identity between the GEMMs; 1: ReLU */
+ *   epilogue 0: identity between the GEMMs; 1: ReLU; | DITTO_EPILOGUE_PAIR_MMA selects the variant built on
+ *   2-SM MMAs over CTA pairs (M % 256 == 0, N in {512, 1024}; same results, currently slower) */
 int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N,
                               int K, int L, int dtype, int w_layout, int epilogue, void* workspace,
                               size_t ws_bytes, int* status_word, void* stream);

@@ -31,14 +31,14 @@ def _inputs(seed, batch, M, N, K, L, dtype):
     return x, w1, w2
 
 
-def _run(cuda, x, w1, w2, dtype, act, layout="IO"):
+def _run(cuda, x, w1, w2, dtype, act, layout="IO", pair=False):
     dx = _dev(x, dtype, cuda)
     if layout == "OI":
         d1, d2 = _dev(w1.transpose(0, 2, 1), dtype, cuda), _dev(w2.transpose(0, 2, 1), dtype, cuda)
     else:
         d1, d2 = _dev(w1, dtype, cuda), _dev(w2, dtype, cuda)
     out = torch.full((x.shape[0], x.shape[1], w2.shape[2]), float("nan"), dtype=TDT[dtype], device=cuda)  # poison
-    ops.gemm_relu_gemm(dx, d1, d2, out=out, activation=act, weight_layout=layout)
+    ops.gemm_relu_gemm(dx, d1, d2, out=out, activation=act, weight_layout=layout, pair_mma=pair)
     assert ops.device_status(cuda) == 0
     return out.float().cpu().numpy()
 
@@ -46,12 +46,18 @@ def _run(cuda, x, w1, w2, dtype, act, layout="IO"):
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 @pytest.mark.parametrize("act", ["relu", "identity"])
 @pytest.mark.parametrize("layout", ["IO", "OI"])
-def test_parity_small(cuda, oracle, dtype, act, layout):
-    for (batch, M, N, K, L) in ((1, 128, 256, 64, 512), (2, 256, 512, 128, 1024), (1, 128, 1024, 192, 512)):
+@pytest.mark.parametrize("pair", [False, True])
+def test_parity_small(cuda, oracle, dtype, act, layout, pair):
+    """Both kernel variants: single-CTA MMAs (default) and 2-SM MMAs over CTA pairs (M % 256 == 0 and
+    N in {512, 1024} only)."""
+    shapes = ((2, 256, 512, 128, 1024), (1, 512, 1024, 256, 1536))
+    if not pair:
+        shapes += ((1, 128, 256, 64, 512), (1, 128, 1024, 192, 512))
+    for (batch, M, N, K, L) in shapes:
         x, w1, w2 = _inputs(21, batch, M, N, K, L, dtype)
-        got = _run(cuda, x, w1, w2, dtype, act, layout)
+        got = _run(cuda, x, w1, w2, dtype, act, layout, pair)
         want = oracle.gemm_act_gemm(x, w1, w2, 1 if act == "relu" else 0, ODT[dtype], wide=False)
-        assert_close(got, want, dtype, f"{dtype} {act} {layout} {(batch, M, N, K, L)}")
+        assert_close(got, want, dtype, f"{dtype} {act} {layout} pair={pair} {(batch, M, N, K, L)}")
 
 
 def test_golden_vector(cuda):
