@@ -47,10 +47,11 @@ constexpr int kRows = 128;            // rows per CTA (256 per pair / cluster)
 constexpr int kChunk = 128;           // hidden columns per chunk
 constexpr int kStageBytes = 24 * 1024;
 constexpr int kStages = 4;
-constexpr int kSlotBytes = kRows * kChunk * 2;
+constexpr int kSets = 2;              // a chunk is exchanged and consumed as two 64-column halves
+constexpr int kSlotBytes = kRows * (kChunk / kSets) * 2;   // one half chunk: a 128-row x 128-byte atom, 16 KB
 constexpr int kThreads = 224;
 constexpr int kOffSlots = 0;
-constexpr int kOffRing = kOffSlots + kPairs * kSlotBytes;
+constexpr int kOffRing = kOffSlots + kSets * kPairs * kSlotBytes;
 constexpr int kOffBar = kOffRing + kStages * kStageBytes;
 constexpr int kSmemBytes = kOffBar + 256 + 1024;
 
@@ -71,10 +72,11 @@ struct PairBars {
   uint64_t empty[kStages];     // each CTA: the pair's MMAs have finished with the stage
   uint64_t h_tmem_full[2];     // each CTA: GEMM1 of the chunk is in TMEM
   uint64_t h_tmem_empty[2];    // leader: both CTAs' epilogues have read the TMEM buffer (8 warp arrivals)
-  uint64_t h_ready;            // each CTA: the round's four chunks are in this CTA's slots
-  uint64_t h_pair;             // leader: ... in both CTAs' slots (2 arrivals)
-  uint64_t g2_done;            // each CTA: the pair's GEMM2 of the round has finished
-  uint64_t slots_free;         // each CTA: all four pairs have (4 arrivals)
+  // one of each per half-chunk set: the exchange of one set overlaps GEMM2 on the other
+  uint64_t h_ready[kSets];     // each CTA: the round's four half chunks are in this CTA's slots
+  uint64_t h_pair[kSets];      // leader: ... in both CTAs' slots (2 arrivals)
+  uint64_t g2_done[kSets];     // each CTA: the pair's GEMM2 over the set has finished
+  uint64_t slots_free[kSets];  // each CTA: all four pairs have (4 arrivals)
   uint64_t y_done;
   uint64_t epi_sync;
   uint32_t tmem_base;
@@ -114,10 +116,12 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       mbar_init(&bar->h_tmem_full[i], 1);
       mbar_init(&bar->h_tmem_empty[i], 8);
     }
-    mbar_init(&bar->h_ready, 1);
-    mbar_init(&bar->h_pair, 2);
-    mbar_init(&bar->g2_done, 1);
-    mbar_init(&bar->slots_free, kPairs);
+    for (int x = 0; x < kSets; ++x) {
+      mbar_init(&bar->h_ready[x], 1);
+      mbar_init(&bar->h_pair[x], 2);
+      mbar_init(&bar->g2_done[x], 1);
+      mbar_init(&bar->slots_free[x], kPairs);
+    }
     mbar_init(&bar->y_done, 1);
     mbar_init(&bar->epi_sync, kRows);
     bar->abort_word = 0;
@@ -169,10 +173,10 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           advance();
         }
       };
-      auto load_g2 = [&](int i) {         // this CTA's half of the pair's W2 slice, four chunks
-        for (int c = 0; c < kPairs && ok; ++c) {
-          const int g = i * kPairs + c;
-          for (int kk = 0; kk < 2 && ok; ++kk) {
+      auto load_g2 = [&](int i) {         // this CTA's half of the pair's W2 slice: set by set, four chunks each
+        for (int kk = 0; kk < kSets && ok; ++kk) {
+          for (int c = 0; c < kPairs && ok; ++c) {
+            const int g = i * kPairs + c;
             uint8_t* dst = acquire(2 * 64 * NH * 2, 0x200 + i);
             if (!ok) break;
             if (p.w_oi) {
@@ -243,28 +247,28 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         if (lane == 0) DITTO_STAMP(i, 1);
       };
       auto g2 = [&](int i) {
-        if (lane == 0) DITTO_STAMP(i, 2);
-        ok = wait_cluster(&bar->h_pair, i & 1, 0x400 + i);
-        if (lane == 0) DITTO_STAMP(i, 3);
-        for (int c = 0; c < kPairs && ok; ++c) {
-          for (int kk = 0; kk < 2 && ok; ++kk) {
+        for (int x = 0; x < kSets && ok; ++x) {
+          if (lane == 0) DITTO_STAMP(i, 2 + 8 * x);
+          ok = wait_cluster(&bar->h_pair[x], i & 1, 0x400 + i);
+          if (lane == 0) DITTO_STAMP(i, 3 + 8 * x);
+          for (int c = 0; c < kPairs && ok; ++c) {
             ok = wait(&bar->full[cs], cph, 0x410 + i);
             if (!ok) break;
             const uint32_t st = ring + cs * kStageBytes;
-            const uint64_t da = umma_desc_sw128(slots + c * kSlotBytes + kk * 16384, 16, 1024);
+            const uint64_t da = umma_desc_sw128(slots + (x * kPairs + c) * kSlotBytes, 16, 1024);
             const uint64_t db = p.w_oi ? umma_desc_sw128(st, 16, 1024) : umma_desc_sw128(st, 8192, 1024);
 #pragma unroll
             for (int s4 = 0; s4 < 4; ++s4) {
               const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
-              umma_ss_pair_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (i | c | kk | s4) ? 1u : 0u,
+              umma_ss_pair_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (i | x | c | s4) ? 1u : 0u,
                                    issuer);
             }
             umma_commit_pair_elected(&bar->empty[cs], pair_mask, issuer);
             advance();
           }
+          if (ok) umma_commit_pair_elected(&bar->g2_done[x], pair_mask, issuer);
+          if (lane == 0) DITTO_STAMP(i, 4 + 8 * x);
         }
-        if (ok) umma_commit_pair_elected(&bar->g2_done, pair_mask, issuer);
-        if (lane == 0) DITTO_STAMP(i, 4);
       };
       g1(0);
       if (rounds > 1 && ok) g1(1);
@@ -275,24 +279,23 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       if (ok) umma_commit_pair_elected(&bar->y_done, pair_mask, issuer);
     }
   } else if (warp == 6) {
-    // ------------------------------------------------------------ relay (one thread)
-    if (lane == 0) {
+    // ------------------------------------------------------------ relay (one thread per set)
+    if (lane < kSets) {
+      const int x = lane;
       for (int i = 0; i < rounds; ++i) {
-        // this CTA holds the round's four chunks -> tell the pair leader
-        if (!mbar_wait_cluster(&bar->h_ready, i & 1, abort_word, 0x500 + i)) break;
-        DITTO_STAMP(i, 9);
-        mbar_arrive_cluster(&bar->h_pair, leader);
-        // the pair has finished reading the round's slots -> tell the four CTAs of this half
-        if (!mbar_wait(&bar->g2_done, i & 1, abort_word, 0x580 + i)) break;
-        DITTO_STAMP(i, 5);
-        for (uint32_t c = 0; c < kPairs; ++c) mbar_arrive_cluster(&bar->slots_free, 2 * c + half);
+        // this CTA holds the round's four half chunks of the set -> tell the pair leader
+        if (!mbar_wait_cluster(&bar->h_ready[x], i & 1, abort_word, 0x500 + i)) break;
+        mbar_arrive_cluster(&bar->h_pair[x], leader);
+        // the pair has finished reading the set's slots -> tell the four CTAs of this half
+        if (!mbar_wait(&bar->g2_done[x], i & 1, abort_word, 0x580 + i)) break;
+        if (x == 0) DITTO_STAMP(i, 5);
+        for (uint32_t c = 0; c < kPairs; ++c) mbar_arrive_cluster(&bar->slots_free[x], 2 * c + half);
       }
     }
   } else if (warp < 4) {
     // ------------------------------------------------------------ epilogue
     const int row = warp * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    uint8_t* my_slot = smem + kOffSlots + pair * kSlotBytes;
     bool ok = true;
     for (int i = 0; i < rounds; ++i) {
       const int hb = i & 1;
@@ -316,33 +319,40 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         }
         pk[j] = pack2<BF16>(v0, v1);
       }
-      if (i > 0) {
-        ok = mbar_wait_cluster(&bar->slots_free, (i - 1) & 1, abort_word, 0x700 + i);
+#pragma unroll
+      for (int x = 0; x < kSets; ++x) {
+        if (i > 0) {
+          // every pair has finished GEMM2 over this set in the previous round: its slots may be overwritten
+          ok = mbar_wait_cluster(&bar->slots_free[x], (i - 1) & 1, abort_word, 0x700 + i);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        if (threadIdx.x == 0 && x == 0) DITTO_STAMP(i, 7);
+        uint8_t* slot = smem + kOffSlots + (x * kPairs + pair) * kSlotBytes;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const int w = x * 32 + 4 * ch;
+          const uint4 v = make_uint4(pk[w], pk[w + 1], pk[w + 2], pk[w + 3]);
+          *reinterpret_cast<uint4*>(slot + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bar->epi_sync);
+        ok = mbar_wait(&bar->epi_sync, (2 * i + x) & 1, abort_word, 0x780 + i);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-      }
-      if (threadIdx.x == 0) DITTO_STAMP(i, 7);
-#pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        const uint4 v = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-        *reinterpret_cast<uint4*>(my_slot + (ch >> 3) * 16384 + row * 128 + (((ch & 7) ^ (row & 7)) << 4)) = v;
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(&bar->epi_sync);
-      ok = mbar_wait(&bar->epi_sync, i & 1, abort_word, 0x780 + i);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (threadIdx.x == 0) {
-        const uint32_t slot_addr = smem_u32(my_slot);
-        const uint32_t bar_addr = smem_u32(&bar->h_ready);
-        for (uint32_t d = 1; d < kPairs; ++d) {
-          // same rows, other pairs; rotated so the senders do not all hit the same destination first
-          const uint32_t peer = 2 * ((pair + d) % kPairs) + half;
-          bulk_copy_to_peer(map_to_cta(slot_addr, peer), my_slot, kSlotBytes, map_to_cta(bar_addr, peer));
+        if (threadIdx.x == 0) {
+          const uint32_t slot_addr = smem_u32(slot);
+          const uint32_t bar_addr = smem_u32(&bar->h_ready[x]);
+          for (uint32_t d = 1; d < kPairs; ++d) {
+            // same rows, other pairs; rotated so the senders do not all hit the same destination first
+            const uint32_t peer = 2 * ((pair + d) % kPairs) + half;
+            bulk_copy_to_peer(map_to_cta(slot_addr, peer), slot, kSlotBytes, map_to_cta(bar_addr, peer));
+          }
+          mbar_arrive_expect_tx(&bar->h_ready[x], (kPairs - 1) * kSlotBytes);
+          if (x == 0) DITTO_STAMP(i, 8);
         }
-        mbar_arrive_expect_tx(&bar->h_ready, (kPairs - 1) * kSlotBytes);
-        DITTO_STAMP(i, 8);
       }
+      if (!ok) break;
     }
     if (ok) {
       ok = mbar_wait(&bar->y_done, 0, abort_word, 0x800);
