@@ -217,6 +217,9 @@ class GpuRun:
             return 0.0
         unit_rows = 1 if w.kind == "softmax" else 128
         units = self.n
+        if w.kind != "softmax":
+            # a chunk of the MLP chain should still fill the GPU: 37 four-CTA clusters per wave
+            chunks = min(chunks, max(1, units // 37))
         chunks = max(1, min(chunks, units))
         per = -(-units // chunks)
         spans = [(c * per * unit_rows, min((c + 1) * per, units) * unit_rows) for c in range(chunks)
@@ -225,7 +228,7 @@ class GpuRun:
         for h, d in zip(host_in, self.inputs):
             h.copy_(d)
         host_out = torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
-        nbuf = 2
+        nbuf = 3
         max_rows = max(b - a for a, b in spans)
         dev_in = [[torch.empty((max_rows,) + tuple(t.shape[1:]), dtype=t.dtype, device=self.device) for t in self.inputs]
                   for _ in range(nbuf)]
@@ -234,11 +237,16 @@ class GpuRun:
         s_in, s_k, s_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
         main = torch.cuda.current_stream(self.device)
 
+        freed = [None] * nbuf         # event: buffer's outputs copied out (buffer reusable); kept across steps
+        counter = [0]
+
         def one_step():
-            copied = [None] * nbuf    # event: buffer's inputs landed
-            freed = [None] * nbuf     # event: buffer's outputs copied out (buffer reusable)
-            for ci, (a, b) in enumerate(spans):
-                bi = ci % nbuf
+            # Steps are pipelined like a serving loop would run them: step n+1's host->device copies
+            # may overlap step n's kernel and device->host copies; every step still moves all of its
+            # inputs and outputs, and the timed region ends when the last step's result is on the host.
+            for (a, b) in spans:
+                bi = counter[0] % nbuf
+                counter[0] += 1
                 with torch.cuda.stream(s_in):
                     if freed[bi] is not None:
                         s_in.wait_event(freed[bi])
@@ -257,21 +265,21 @@ class GpuRun:
                     ev_o = torch.cuda.Event()
                     ev_o.record(s_out)
                 freed[bi] = ev_o
-            for s in (s_in, s_k, s_out):
-                main.wait_stream(s)
 
+        for s in (s_in, s_k, s_out):
+            s.wait_stream(main)
         for _ in range(min(warmup, 2)):
-            for s in (s_in, s_k, s_out):
-                s.wait_stream(main)
             one_step()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize(self.device)
         barrier()
         e0.record(main)
+        for s in (s_in, s_k, s_out):
+            s.wait_stream(main)
         for _ in range(steps):
-            for s in (s_in, s_k, s_out):
-                s.wait_stream(main)
             one_step()
+        for s in (s_in, s_k, s_out):
+            main.wait_stream(s)
         e1.record(main)
         torch.cuda.synchronize(self.device)
         barrier()
