@@ -67,6 +67,32 @@ int make_map_2d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, ui
   return DITTO_OK;
 }
 
+// 3-D tensor [slices, rows, cols] of 16-bit elements: coordinates (col, row, slice), boxes of
+// box_cols x box_rows x 1.  Rows beyond `rows` inside a slice are out of bounds and read as zero,
+// which is what makes partial tiles at the end of a sequence safe.
+int make_map_3d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint64_t slices,
+                uint64_t row_stride_elems, uint64_t slice_stride_elems, uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) {
+    set_error("cuTensorMapEncodeTiled", "entry point not found");
+    return DITTO_ERR_DRIVER;
+  }
+  const cuuint64_t dims[3] = {cols, rows, slices};
+  const cuuint64_t strides[2] = {row_stride_elems * 2, slice_stride_elems * 2};
+  const cuuint32_t box[3] = {box_cols, box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
+    set_error("cuTensorMapEncodeTiled", buf);
+    return DITTO_ERR_CUDA;
+  }
+  return DITTO_OK;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int cuda_fail(const char* what, cudaError_t e) {
@@ -89,36 +115,38 @@ int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void
   if (!(scale > 0.f) || !std::isfinite(scale)) return DITTO_ERR_INVALID_ARG;
   if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
   if (k_layout != 0 && k_layout != 1) return DITTO_ERR_INVALID_ARG;
-  // The reference asserts multiples of 16 (bmm_chain.py:34-38); the tcgen05 path covers 128-row tiles.
+  // The reference asserts multiples of 16 (bmm_chain.py:34-38); so does this entry point.  Partial
+  // 128-row tiles are handled by TMA zero fill, masked scores and predicated stores.
   if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
-  if (N != K || (K != 64 && K != 128)) return DITTO_ERR_UNSUPPORTED;
-  if (M % 128 || L % 128) return DITTO_ERR_UNSUPPORTED;
+  if (N != K || K > 128) return DITTO_ERR_UNSUPPORTED;
   if (batch > 65535) return DITTO_ERR_UNSUPPORTED;
 
   const bool bf16 = dtype == DITTO_DTYPE_BF16;
-  const int d = K;
-  int nt = (M % 256 == 0 && !(flags & DITTO_FLAG_ONE_TILE)) ? 2 : 1;
-  // d = 64: one tile per CTA with separate S / P columns, two CTAs per SM (see attention_sm100.cu)
+  const int d = K <= 64 ? 64 : 128;             // kernel variant; K itself may be any multiple of 16 below it
+  int nt = (M > 128 && !(flags & DITTO_FLAG_ONE_TILE)) ? 2 : 1;
+  // d <= 64: one tile per CTA with separate S / P columns, two CTAs per SM (see attention_sm100.cu)
   if (d == 64 && !(flags & (DITTO_FLAG_TWO_TILES | DITTO_FLAG_P_VIA_SMEM))) nt = 1;
   const bool psmem = (flags & DITTO_FLAG_P_VIA_SMEM) != 0;
 
   ditto_b200::AttnParams p;
   std::memset(&p, 0, sizeof(p));
-  int rc = make_map_2d(&p.map_q, bf16, q, d, static_cast<uint64_t>(batch) * M, 64, 128);
+  const uint64_t uK = K, uM = M, uL = L, ub = batch;
+  int rc = make_map_3d(&p.map_q, bf16, q, uK, uM, ub, uK, uM * uK, 64, 128);
   if (rc) return rc;
   if (k_layout == 0)
-    rc = make_map_2d(&p.map_k, bf16, k, L, static_cast<uint64_t>(batch) * d, 64, d);
+    rc = make_map_3d(&p.map_k, bf16, k, uL, uK, ub, uL, uK * uL, 64, d);
   else
-    rc = make_map_2d(&p.map_k, bf16, k, d, static_cast<uint64_t>(batch) * L, 64, 128);
+    rc = make_map_3d(&p.map_k, bf16, k, uK, uL, ub, uK, uL * uK, 64, 128);
   if (rc) return rc;
-  rc = make_map_2d(&p.map_v, bf16, v, d, static_cast<uint64_t>(batch) * L, 64, 128);
+  rc = make_map_3d(&p.map_v, bf16, v, uK, uL, ub, uK, uL * uK, 64, 128);
   if (rc) return rc;
   p.out = out;
   p.M = M;
   p.L = L;
   p.k_transposed = (k_layout == 0);
+  p.d = K;
   p.heads = 1;
-  p.out_ld = d;
+  p.out_ld = K;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word;
 #ifdef DITTO_TRACE
@@ -136,18 +164,17 @@ int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M
   if (!aligned16(qkv) || !aligned16(out)) return DITTO_ERR_INVALID_ARG;
   if (!(scale > 0.f) || !std::isfinite(scale)) return DITTO_ERR_INVALID_ARG;
   if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
-  if (head_dim != 64 && head_dim != 128) return DITTO_ERR_UNSUPPORTED;
-  if (M % 128) return DITTO_ERR_UNSUPPORTED;
+  if (head_dim % 16 || head_dim > 128 || M % 16) return DITTO_ERR_UNSUPPORTED;
   if (static_cast<long long>(batch) * heads > 65535) return DITTO_ERR_UNSUPPORTED;
   const bool bf16 = dtype == DITTO_DTYPE_BF16;
-  const int d = head_dim, hidden = heads * head_dim;
-  int nt = (M % 256 == 0 && !(flags & DITTO_FLAG_ONE_TILE)) ? 2 : 1;
+  const int d = head_dim <= 64 ? 64 : 128, hidden = heads * head_dim;
+  int nt = (M > 128 && !(flags & DITTO_FLAG_ONE_TILE)) ? 2 : 1;
   if (d == 64 && !(flags & DITTO_FLAG_TWO_TILES)) nt = 1;
   ditto_b200::AttnParams p;
   std::memset(&p, 0, sizeof(p));
   // one tensor map over the packed [batch*M, 3*hidden] matrix serves Q, K and V: the head split and
   // the [b, M, h, d] -> [b*h, M, d] permutes become TMA coordinates
-  int rc = make_map_2d(&p.map_q, bf16, qkv, 3ull * hidden, static_cast<uint64_t>(batch) * M, 64, 128);
+  int rc = make_map_3d(&p.map_q, bf16, qkv, 3ull * hidden, M, batch, 3ull * hidden, 3ull * hidden * M, 64, 128);
   if (rc) return rc;
   p.map_k = p.map_q;
   p.map_v = p.map_q;
@@ -155,6 +182,7 @@ int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M
   p.M = M;
   p.L = M;
   p.k_transposed = 0;
+  p.d = head_dim;
   p.heads = heads;
   p.q_col0 = 0;
   p.k_col0 = hidden;
@@ -179,31 +207,34 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
   if (w_layout != 0 && w_layout != 1) return DITTO_ERR_INVALID_ARG;
   if ((epilogue & ~0x200) != 0 && (epilogue & ~0x200) != 1) return DITTO_ERR_INVALID_ARG;
   if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
-  if (N == K && (K == 64 || K == 128)) {
+  if (N == K && K <= 128) {
     // Small-N chains (the reference's shape family: N = K = 64, L = 512 ...): the result tile
     // [128, N] fits TMEM next to the intermediate, so the chain runs on the attention kernel with
     // the activation in place of the softmax: A = x, B = w1, C = w2.
-    if (M % 128 || L % 128 || batch > 65535) return DITTO_ERR_UNSUPPORTED;
+    if (batch > 65535) return DITTO_ERR_UNSUPPORTED;
     if (w_layout != 0) return DITTO_ERR_UNSUPPORTED;   // w2 as [N, L] is not an operand form of that kernel
     const bool bf16 = dtype == DITTO_DTYPE_BF16;
+    const int dk = K <= 64 ? 64 : 128;
     ditto_b200::AttnParams p;
     std::memset(&p, 0, sizeof(p));
-    int rc = make_map_2d(&p.map_q, bf16, x, K, static_cast<uint64_t>(batch) * M, 64, 128);
+    const uint64_t uK = K, uM = M, uL = L, ub = batch;
+    int rc = make_map_3d(&p.map_q, bf16, x, uK, uM, ub, uK, uM * uK, 64, 128);
     if (rc) return rc;
-    rc = make_map_2d(&p.map_k, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, K);
+    rc = make_map_3d(&p.map_k, bf16, w1, uL, uK, ub, uL, uK * uL, 64, dk);
     if (rc) return rc;
-    rc = make_map_2d(&p.map_v, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, 128);
+    rc = make_map_3d(&p.map_v, bf16, w2, uK, uL, ub, uK, uL * uK, 64, 128);
     if (rc) return rc;
     p.out = y;
     p.M = M;
     p.L = L;
     p.k_transposed = 1;
+    p.d = K;
     p.heads = 1;
     p.out_ld = N;
     p.scale_log2 = 1.0f;
     p.status = status_word;
-    const int nt = (K == 64 || M % 256) ? 1 : 2;
-    cudaError_t e = ditto_b200::launch_attention(p, batch, K, bf16, nt, false, (epilogue & 0xff) == 1 ? 1 : 2,
+    const int nt = (dk == 64 || M <= 128) ? 1 : 2;
+    cudaError_t e = ditto_b200::launch_attention(p, batch, dk, bf16, nt, false, (epilogue & 0xff) == 1 ? 1 : 2,
                                                  static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail("gemm_relu_gemm launch", e);
     return DITTO_OK;

@@ -131,9 +131,10 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
   // Packed multi-head input: slice = (sequence, head); rows come from the sequence, columns from
   // the head.  Plain batched input has heads == 1 and zero column offsets.
   const int seq = slice / p.heads;
-  const int head_col = (slice % p.heads) * D;
+  const int head_col = (slice % p.heads) * p.d;
   const int m0 = blockIdx.x * (NT * kBM);
-  const int nkv = p.L / kBN;
+  const int nkv = (p.L + kBN - 1) / kBN;        // the last block may be partial: TMA zero-fills rows >= L
+  const int ksteps_d = p.d / 16;                // head dimension actually used by S = Q K^T (<= D / 16)
 
   if (threadIdx.x == 0) {
     mbar_init(&bar->q_full, 1);
@@ -171,8 +172,8 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
       mbar_arrive_expect_tx(&bar->q_full, NT * SM::kTileQ);
       for (int t = 0; t < NT; ++t)
         for (int a = 0; a < kAtoms; ++a)
-          tma_load_2d(smem + SM::kOffQ + t * SM::kTileQ + a * (kBM * 128), &p.map_q, &bar->q_full,
-                      p.q_col0 + head_col + a * 64, seq * p.M + m0 + t * kBM);
+          tma_load_3d(smem + SM::kOffQ + t * SM::kTileQ + a * (kBM * 128), &p.map_q, &bar->q_full,
+                      p.q_col0 + head_col + a * 64, m0 + t * kBM, seq);
       bool ok = true;
       int armed_k[4] = {-1, -1, -1, -1}, armed_v[4] = {-1, -1, -1, -1};  // parity of the newest armed phase
       for (int j = 0; j < nkv; ++j) {
@@ -187,11 +188,11 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
           if (p.k_transposed) {
             // K given as [slice, D, L]: boxes of 64 kv-columns x D rows (MN-major operand)
             for (int a = 0; a < kBN / 64; ++a)
-              tma_load_2d(dst + a * (D * 128), &p.map_k, &bar->k_full[s], j * kBN + a * 64, slice * D);
+              tma_load_3d(dst + a * (D * 128), &p.map_k, &bar->k_full[s], j * kBN + a * 64, 0, slice);
           } else {
             for (int a = 0; a < kAtoms; ++a)
-              tma_load_2d(dst + a * (kBN * 128), &p.map_k, &bar->k_full[s], p.k_col0 + head_col + a * 64,
-                          seq * p.L + j * kBN);
+              tma_load_3d(dst + a * (kBN * 128), &p.map_k, &bar->k_full[s], p.k_col0 + head_col + a * 64,
+                          j * kBN, seq);
           }
         }
         ok = mbar_wait(&bar->v_empty[s], ph ^ 1, abort_word, 0x200 + j);
@@ -201,8 +202,8 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
           mbar_arrive_expect_tx(&bar->v_full[s], SM::kTileKV);
           armed_v[s] = static_cast<int>(ph);
           for (int a = 0; a < kAtoms; ++a)
-            tma_load_2d(dst + a * (kBN * 128), &p.map_v, &bar->v_full[s], p.v_col0 + head_col + a * 64,
-                        seq * p.L + j * kBN);
+            tma_load_3d(dst + a * (kBN * 128), &p.map_v, &bar->v_full[s], p.v_col0 + head_col + a * 64,
+                        j * kBN, seq);
         }
       }
       if (!ok) {
@@ -240,7 +241,8 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
         // MN-major (transposed K): 16 rows of 128 bytes per k-step
         const uint32_t off_k = ((i / 4) * (kBM * 128) + (i % 4) * 32) >> 4;
         const uint32_t off_b = kt ? static_cast<uint32_t>((i * 2048) >> 4) : off_k;
-        umma_ss_elected(tmem_base + t * kBN, da + off_k, db + off_b, idesc_s, i > 0 ? 1u : 0u, issuer);
+        if (i < ksteps_d)   // head dimensions below D use the first d / 16 k-steps only
+          umma_ss_elected(tmem_base + t * kBN, da + off_k, db + off_b, idesc_s, i > 0 ? 1u : 0u, issuer);
       }
       umma_commit_elected(&bar->s_full[t], issuer);
     };
@@ -373,6 +375,13 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
 
       float m_new = m;
       if constexpr (MODE == kModeSoftmax) {
+        if (j == nkv - 1 && (p.L % kBN) != 0) {
+          // partial last block: K rows >= L were zero-filled, their scores must not count
+          const int valid = p.L % kBN;
+#pragma unroll
+          for (int i = 0; i < kBN; ++i)
+            if (i >= valid) sv[i] = __float_as_uint(-INFINITY);
+        }
         float mx[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) mx[u] = fmaxf(__uint_as_float(sv[2 * u]), __uint_as_float(sv[2 * u + 1]));
@@ -486,19 +495,21 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
     if (ok) {
       tc_fence_after_sync();
       const float inv = MODE == kModeSoftmax ? 1.0f / l : 1.0f;
+      const int grow = m0 + t * kBM + row;          // rows >= M (partial last tile) are computed on zero-filled Q, not stored
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
-                      ((static_cast<size_t>(seq) * p.M + m0 + t * kBM + row) * p.out_ld + head_col) * 2;
+                      ((static_cast<size_t>(seq) * p.M + grow) * p.out_ld + head_col) * 2;
 #pragma unroll
       for (int cc = 0; cc < D; cc += 32) {
         uint32_t o[32];
-        tmem_ld_x32_wait(o_col + cc, o);
+        tmem_ld_x32_wait(o_col + cc, o);              // warp-collective: every lane takes part
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           w[i] = pack2<BF16>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          *reinterpret_cast<uint4*>(orow + cc * 2 + i * 16) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          if (grow < p.M && cc + i * 8 < p.d)          // d is a multiple of 16: whole 16-byte pieces
+            *reinterpret_cast<uint4*>(orow + cc * 2 + i * 16) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
       }
     }
   }
@@ -520,7 +531,7 @@ static cudaError_t launch_one(const AttnParams& p, int batch, cudaStream_t strea
   if (e != cudaSuccess) return e;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return e;
-  dim3 grid(p.M / (NT * kBM), batch, 1);
+  dim3 grid((p.M + NT * kBM - 1) / (NT * kBM), batch, 1);
   kern<<<grid, threads_for(NT), SM::kBytes, stream>>>(p);
   return cudaGetLastError();
 }

@@ -5,13 +5,16 @@
 
 namespace ditto_b200 {
 
+// Tensor maps are 3-D (column, row inside the sequence, sequence) so that a partial tile at the end
+// of a sequence is zero-filled by TMA instead of reading the next sequence's rows.
 struct AttnParams {
-  CUtensorMap map_q;  // [batch*M, D] row-major, box 64 x 128, 128B swizzle
-  CUtensorMap map_k;  // [batch*L, D] (box 64 x 128) or, transposed, [batch*D, L] (box 64 x D)
-  CUtensorMap map_v;  // [batch*L, D] row-major, box 64 x 128
-  void* out;          // [batch, M, D] fp16 / bf16
-  int M;              // query rows per slice (multiple of 128 * NT)
-  int L;              // key/value rows per slice (multiple of 128)
+  CUtensorMap map_q;  // [batch, M, d] (or the packed [batch, M, 3*hidden]), box 64 x 128 x 1, 128B swizzle
+  CUtensorMap map_k;  // [batch, L, d] (box 64 x 128 x 1) or, transposed, [batch, d, L] (box 64 x D x 1)
+  CUtensorMap map_v;  // [batch, L, d], box 64 x 128 x 1
+  void* out;          // [batch, M, d] fp16 / bf16
+  int M;              // query rows per sequence (any multiple of 16)
+  int L;              // key/value rows per sequence (any multiple of 16)
+  int d;              // head dimension in use (multiple of 16, <= the kernel's D)
   int k_transposed;   // 1: K stored [batch, D, L] (the reference's layout)
   int heads;          // 1, or heads folded into the slice index of a packed [sequences, rows, cols] input
   int q_col0, k_col0, v_col0;  // first column of Q / K / V inside the packed row (0 when not packed)

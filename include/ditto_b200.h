@@ -55,7 +55,8 @@ extern "C" {
  *   k_layout 1: key is [batch, L, K]
  *   scale 1.0 reproduces the reference's exp(QK^T)/sum semantics; the softmax is evaluated in the
  *   max-subtracted form, which is the same function without the overflow.
- * Supported: N == K in {64, 128}; M, L multiples of 128; fp16 or bf16 in/out, fp32 accumulate. */
+ * Supported: N == K <= 128; M, N, K, L multiples of 16 like the reference asserts (partial 128-row tiles are
+ * zero-filled by TMA, masked and not stored); fp16 or bf16 in/out, fp32 accumulate. */
 int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void* out, int batch, int M, int N,
                                int K, int L, int dtype, int k_layout, float scale, int flags, void* workspace,
                                size_t ws_bytes, int* status_word, void* stream);
@@ -65,7 +66,7 @@ int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void
  *   qkv [batch, M, 3 * heads * head_dim] = [Q | K | V] per row; out [batch, M, heads * head_dim].
  * The reference splits, reshapes to [batch*heads, M, d], transposes K and reshapes the result back in
  * six extra passes; here the head split is done by the TMA coordinates and the result is written in
- * place.  scale 1.0 = the reference's semantics.  head_dim in {64, 128}; M a multiple of 128. */
+ * place.  scale 1.0 = the reference's semantics.  head_dim and M multiples of 16, head_dim <= 128. */
 int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M, int heads, int head_dim, int dtype,
                                     float scale, int flags, int* status_word, void* stream);
 

@@ -212,12 +212,32 @@ def test_reference_style_entry_point(cuda, oracle):
     assert 0 < cost < 1e-2
 
 
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("layout", ["LK", "KL"])
+def test_ragged_shapes(cuda, oracle, dtype, layout):
+    """Shapes that are multiples of 16 but not of the 128-row tiles, and head dimensions other than
+    64 / 128: the rest of the reference's benchmark table (ViT-*/16: 196 -> 208 tokens, ViT-Huge:
+    d = 80, Mixer: M != L; benchmark/chimera/cuda/bmm_softmax_bmm_cuda.py:294-308) plus corner cases
+    (a single 16-row tile, tails on both M and L, d = 16).  Outputs are poison-filled first."""
+    shapes = ((12, 208, 64, 208), (16, 208, 80, 208), (16, 256, 80, 256), (1, 512, 64, 256), (1, 768, 64, 384),
+              (2, 16, 16, 16), (3, 144, 48, 272), (2, 400, 112, 144), (1, 1040, 128, 528))
+    for (b, M, d, L) in shapes:
+        q, k, v = _case(17, b, M, L, d, dtype)
+        scale = d ** -0.5
+        for flags in (0, _lib.FLAG_TWO_TILES):
+            got = _run(cuda, q, k, v, dtype, scale, layout, flags)
+            assert_close(got, _oracle(oracle, q, k, v, dtype, scale), dtype, f"{dtype} {layout} flags={flags} {(b, M, d, L)}")
+
+
 def test_unsupported_shapes_raise(cuda):
-    q = torch.zeros(1, 144, 64, dtype=torch.float16, device=cuda)
+    q = torch.zeros(1, 128, 144, dtype=torch.float16, device=cuda)     # head dimension above 128
     kv = torch.zeros(1, 128, 64, dtype=torch.float16, device=cuda)
     with pytest.raises(_lib.DittoError) as e:
-        ops.bmm_softmax_bmm(q, kv, kv, key_layout="LK")
+        ops.bmm_softmax_bmm(q, q, q, key_layout="LK")
     assert e.value.code == _lib.ERR_UNSUPPORTED
+    with pytest.raises(_lib.DittoError) as e:
+        ops.bmm_softmax_bmm(kv[:, :120].contiguous(), kv, kv, key_layout="LK")   # M = 120 is not a multiple of 16
+    assert e.value.code == _lib.ERR_INVALID_ARG
     with pytest.raises(ValueError):
         ops.bmm_softmax_bmm(kv, kv[:, :, :32].contiguous(), kv, key_layout="LK")
     with pytest.raises(ValueError):

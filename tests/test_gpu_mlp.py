@@ -129,7 +129,7 @@ def test_unsupported_shapes_raise(cuda):
 def test_small_n_chains(cuda, oracle, dtype, act, d):
     """N = K in {64, 128}: the reference's own shape family (benchmark/chimera/cuda/bmm_bmm_cuda.py
     shapes table, python_test/auto_tensorize/test_hyper_fusion_cpu.py) -- batched, per-slice weights."""
-    for (batch, M, L) in ((2, 128, 128), (3, 256, 384), (8, 512, 512)):
+    for (batch, M, L) in ((2, 128, 128), (3, 256, 384), (8, 512, 512), (2, 208, 272), (1, 516 // 4 * 4 // 16 * 16 + 16, 512)):
         rng = np.random.default_rng(31)
         a = W._round(rng.uniform(-1, 1, (batch, M, d)).astype(np.float32), dtype)
         b = W._round(rng.uniform(-1, 1, (batch, d, L)).astype(np.float32), dtype)

@@ -25,10 +25,13 @@ def _mha_reference(oracle, qkv, heads, dtype_code, scale):
     return o.reshape(batch, heads, M, d).transpose(0, 2, 1, 3).reshape(batch, M, hidden)
 
 
-@pytest.mark.parametrize("dtype,heads,d", [("float16", 12, 64), ("bfloat16", 4, 128), ("float16", 3, 64)])
-def test_packed_multi_head_attention(cuda, oracle, dtype, heads, d):
+@pytest.mark.parametrize("dtype,heads,d,M", [("float16", 12, 64, 256), ("bfloat16", 4, 128, 256), ("float16", 3, 64, 256),
+                                             ("float16", 16, 80, 208), ("bfloat16", 5, 48, 400)])
+def test_packed_multi_head_attention(cuda, oracle, dtype, heads, d, M):
+    """Includes ViT-Huge/16 (16 heads of 80, 196 -> 208 tokens): ragged rows and a head dimension that
+    is not a tile size, read straight out of the packed tensor."""
     tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[dtype]
-    batch, M = 2, 256
+    batch = 2
     rng = np.random.default_rng(41)
     qkv = W._round((rng.standard_normal((batch, M, 3 * heads * d)) * 0.5).astype(np.float32), dtype)
     dq = torch.from_numpy(qkv).to(cuda).to(tdt)
