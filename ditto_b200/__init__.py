@@ -18,6 +18,8 @@ from . import auto_compute
 from . import auto_tensorize
 from . import runtime
 from . import ops
+from . import auto_schedule
+from . import chimera
 from .runtime import build
 
-__all__ = ["te", "hardware", "auto_compute", "auto_tensorize", "runtime", "ops", "build"]
+__all__ = ["te", "hardware", "auto_compute", "auto_tensorize", "auto_schedule", "chimera", "runtime", "ops", "build"]

@@ -174,3 +174,33 @@ def test_self_attention_layer_schedules_without_a_fusion_state():
     assert (sch.kind, sch.batch, sch.M, sch.N, sch.K, sch.L, sch.heads) == ("mha", 4, 512, 768, 64, 512, 12)
     func = ditto.build(sch, y.layer.schedule_tensors, "cuda")
     assert func.entry_name == "default_function"
+
+
+def test_model_level_flow_binds_and_schedules_attention_layers():
+    """The flow of benchmark/chimera/cuda/bert_inference.py:68-112: extract tasks by fingerprint,
+    bind them, schedule the bound tasks, build one module per key."""
+    from ditto_b200 import auto_schedule, chimera
+    mha = ac.nn.module.MultiHeadAttentionMMA(12, 768, in_dtype="float16")
+    x = ac.layer_tensor([4, 512, 2304], dtype="float16")
+    y1 = mha(x)
+    g = ac.graph([x], [y1])
+    option = auto_schedule.ScheduleOption("cuda", trials=10, device_name="gpu.cuda.B200", dtype="float16")
+    assert option.device.num_groups == 148
+    tasks = auto_schedule.extract_tasks_from_graph(g)
+    assert list(tasks) == [y1.layer.fingerprint] and len(tasks[y1.layer.fingerprint]) == 1
+    bound = chimera.task_binding(tasks)
+    assert list(bound["chimera"]) == [y1.layer.fingerprint] and not bound["ansor"]
+    schedules = auto_schedule.auto_schedule_bound_tasks(bound, option)
+    built = {key: ditto.build(sch, args, "cuda") for key, (sch, args) in schedules.items()}
+    assert built[y1.layer.fingerprint].schedule.kind == "mha"
+    # a plain fused chain is bound to the same scheduler; an unfusable layer is not
+    ins, outs = ac.nn.functional.BatchGemmReluGemm(1, 256, 512, 128, 1024, "bfloat16", "float32")
+    chain = ac.layer([outs[0].op], inputs=ins)
+    A = te.placeholder([1, 64, 64], "A", "float16")
+    single = ac.layer([te.compute([1, 64, 64], [A], "copy", "float16").op], inputs=[A], name="copy_layer")
+    bound = chimera.task_binding({"c": [chain], "s": [single]})
+    assert list(bound["chimera"]) == ["c"] and list(bound["ansor"]) == ["s"]
+    sch, args = auto_schedule.get_tasks_scheduler_builder("chimera")({"c": [chain]}, option)["c"]
+    assert sch.kind == "relu" and args == chain.schedule_tensors
+    with pytest.raises(NotImplementedError):
+        auto_schedule.get_tasks_scheduler_builder("ansor")
