@@ -28,6 +28,7 @@ EXPORTS = (
     "ditto_b200_bmm_softmax_bmm",
     "ditto_b200_gemm_relu_gemm",
     "ditto_b200_multi_head_attention",
+    "ditto_b200_ffn",
     "ditto_b200_workspace_bytes",
     "ditto_b200_selftest_umma",
     "ditto_b200_selftest_umma_pair",
@@ -73,6 +74,8 @@ def load():
     lib.ditto_b200_gemm_relu_gemm.restype = i
     lib.ditto_b200_multi_head_attention.argtypes = [vp, vp, i, i, i, i, i, f, i, vp, vp]
     lib.ditto_b200_multi_head_attention.restype = i
+    lib.ditto_b200_ffn.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, vp, vp]
+    lib.ditto_b200_ffn.restype = i
     lib.ditto_b200_workspace_bytes.argtypes = [i, i, i, i, i, i, i]
     lib.ditto_b200_workspace_bytes.restype = sz
     lib.ditto_b200_selftest_umma.argtypes = [vp, vp, vp, i, i, i, i, i, vp, vp]

@@ -70,7 +70,9 @@ struct MlpParams {
   void* y;             // Y  [batch, M, N]
   int M, N, K, L;
   int w_oi;            // 1: weights stored [out, in] (K-major B operands)
-  int relu;
+  int act1, act2;      // 0 identity, 1 ReLU, 2 GELU (tanh form) after the first / second GEMM
+  const void* b1;      // optional bias [batch, L] added before act1 (16-bit, same type as X); may be null
+  const void* b2;      // optional bias [batch, N] added before act2; may be null
   int* status;
   long long* trace;    // timeline buffer of -DDITTO_TRACE builds (null otherwise)
 };
@@ -88,6 +90,26 @@ struct Bars {
 };
 static_assert(sizeof(Bars) <= 256, "barrier block too large");
 
+}  // namespace
+
+namespace {
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == 1) return v > 0.f ? v : 0.f;          // if_then_else(x > 0, x, 0) as in the reference's ReLU
+  if (act == 2) {                                  // the reference's GELU: 0.5 x (1 + tanh(0.79788456 x (1 + 0.044715 x^2)))
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(v * 0.7978845608f * (1.0f + 0.044715f * v * v)));
+    return 0.5f * v * (1.0f + t);
+  }
+  return v;
+}
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (BF16) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w));
+  } else {
+    return __half22float2(*reinterpret_cast<__half2*>(&w));
+  }
+}
 }  // namespace
 
 template <bool BF16>
@@ -291,14 +313,18 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       tc_fence_before_sync();
       mbar_arrive(&bar->h_tmem_empty[hb]);
       uint32_t pk[kChunk / 2];
+      const uint32_t* bias1 = p.b1 == nullptr ? nullptr
+                                              : reinterpret_cast<const uint32_t*>(p.b1) +
+                                                    (static_cast<size_t>(b) * p.L + (i * kCluster + q) * kChunk) / 2;
 #pragma unroll
       for (int j = 0; j < kChunk / 2; ++j) {
         float v0 = __uint_as_float(h[2 * j]), v1 = __uint_as_float(h[2 * j + 1]);
-        if (p.relu) {
-          v0 = v0 > 0.f ? v0 : 0.f;       // if_then_else(D > 0, D, 0) as in the reference
-          v1 = v1 > 0.f ? v1 : 0.f;
+        if (bias1 != nullptr) {             // same address in every lane: one broadcast load
+          const float2 bb = unpack2<BF16>(__ldg(bias1 + j));
+          v0 += bb.x;
+          v1 += bb.y;
         }
-        pk[j] = pack2<BF16>(v0, v1);
+        pk[j] = pack2<BF16>(apply_act(v0, p.act1), apply_act(v1, p.act1));
       }
       if (i > 0) {
         // every CTA of the cluster has finished GEMM2 of the previous round: slots may be overwritten
@@ -337,12 +363,23 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       tc_fence_after_sync();
       uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) +
                       ((static_cast<size_t>(b) * p.M + row0 + row) * p.N + static_cast<size_t>(q) * NS) * 2;
+      const uint32_t* bias2 = p.b2 == nullptr ? nullptr
+                                              : reinterpret_cast<const uint32_t*>(p.b2) +
+                                                    (static_cast<size_t>(b) * p.N + static_cast<size_t>(q) * NS) / 2;
       for (int cc = 0; cc < NS; cc += 32) {
         uint32_t o[32];
         tmem_ld_x32_wait(tmem_y + lane_base + cc, o);
         uint32_t w[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) w[j] = pack2<BF16>(__uint_as_float(o[2 * j]), __uint_as_float(o[2 * j + 1]));
+        for (int j = 0; j < 16; ++j) {
+          float v0 = __uint_as_float(o[2 * j]), v1 = __uint_as_float(o[2 * j + 1]);
+          if (bias2 != nullptr) {
+            const float2 bb = unpack2<BF16>(__ldg(bias2 + cc / 2 + j));
+            v0 += bb.x;
+            v1 += bb.y;
+          }
+          w[j] = pack2<BF16>(apply_act(v0, p.act2), apply_act(v1, p.act2));
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           *reinterpret_cast<uint4*>(yrow + cc * 2 + j * 16) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
@@ -391,12 +428,13 @@ bool mlp_make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, 
 
 
 int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
-                     bool bf16, int w_layout, int epilogue, int* status, cudaStream_t stream, long long* trace) {
+                     bool bf16, int w_layout, int epilogue, int* status, cudaStream_t stream, long long* trace,
+                     const void* b1, const void* b2, int act2) {
   // CTA-pair kernel (2-SM MMAs, a third fewer operand bytes per CTA) on request.  It is correct
   // but, as measured, slower than this kernel: its rounds are paced by the exchange of hidden chunks
   // among eight CTAs instead of by the operand feed.
   if (epilogue & 0x200) {
-    if (!mlp_pair_supported(M, N, K, L)) return DITTO_ERR_UNSUPPORTED;
+    if (!mlp_pair_supported(M, N, K, L) || b1 || b2 || act2 || (epilogue & 0xff) > 1) return DITTO_ERR_UNSUPPORTED;
     return launch_mlp_pair(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, epilogue & 0xff, status, stream, trace);
   }
   epilogue &= 0xff;
@@ -423,7 +461,10 @@ int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int
   p.K = K;
   p.L = L;
   p.w_oi = w_layout == 1;
-  p.relu = epilogue == 1;
+  p.act1 = epilogue;
+  p.act2 = act2;
+  p.b1 = b1;
+  p.b2 = b2;
   p.status = status;
   p.trace = trace;
   dim3 grid(kCluster * (M / kRows), batch, 1);

@@ -165,3 +165,58 @@ def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO", p
     _lib.check(rc, "ditto_b200_gemm_relu_gemm")
     launch_count += 1
     return out
+
+
+_ACT_CODE = {"identity": 0, "relu": 1, "gelu": 2}
+
+
+def ffn(x, w1, b1, w2, b2, out=None, act1="relu", act2="relu", weight_layout="OI"):
+    """Position-wise feed-forward block out = act2(act1(x @ W1 + b1) @ W2 + b2), hidden layer on chip.
+
+    Defaults follow the reference's PositionwiseFeedForward (nn/model/transformer.py:21-34): weights
+    stored [out, in] like nn/functional/linear.py, ReLU after both linears.  x [M, K] or [batch, M, K];
+    w1 [L, K], w2 [N, L] ("OI") or [K, L], [L, N] ("IO"); b1 [L], b2 [N] or None."""
+    global launch_count
+    _check_tensor(x, "x")
+    if x.dtype not in _DTYPE_CODE:
+        raise TypeError(f"x dtype {x.dtype} not supported (float16 / bfloat16)")
+    squeeze = x.dim() == 2
+    x3 = x.unsqueeze(0) if squeeze else x
+    w13 = w1.unsqueeze(0) if w1.dim() == 2 else w1
+    w23 = w2.unsqueeze(0) if w2.dim() == 2 else w2
+    _check_tensor(w13, "w1", x.dtype)
+    _check_tensor(w23, "w2", x.dtype)
+    batch, M, K = x3.shape
+    if weight_layout == "OI":
+        (_, L, K1), (_, N, L2) = w13.shape, w23.shape
+    elif weight_layout == "IO":
+        (_, K1, L), (_, L2, N) = w13.shape, w23.shape
+    else:
+        raise ValueError("weight_layout must be 'IO' or 'OI'")
+    if K1 != K or L2 != L or w13.shape[0] != batch or w23.shape[0] != batch:
+        raise ValueError(f"inconsistent shapes: {tuple(x.shape)}, {tuple(w1.shape)}, {tuple(w2.shape)}")
+    for bias, n, nm in ((b1, L, "b1"), (b2, N, "b2")):
+        if bias is not None:
+            _check_tensor(bias, nm, x.dtype)
+            if bias.numel() != batch * n:
+                raise ValueError(f"{nm} must hold {batch * n} values, got {bias.numel()}")
+    if act1 not in _ACT_CODE or act2 not in _ACT_CODE:
+        raise ValueError(f"activations must be one of {sorted(_ACT_CODE)}")
+    if out is None:
+        out3 = torch.empty((batch, M, N), dtype=x.dtype, device=x.device)
+        out = out3[0] if squeeze else out3
+    else:
+        _check_tensor(out, "out", x.dtype)
+        out3 = out.unsqueeze(0) if out.dim() == 2 else out
+        if tuple(out3.shape) != (batch, M, N):
+            raise ValueError(f"out has shape {tuple(out.shape)}, expected {(batch, M, N)}")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.ditto_b200_ffn(x3.data_ptr(), w13.data_ptr(), b1.data_ptr() if b1 is not None else None, w23.data_ptr(),
+                                b2.data_ptr() if b2 is not None else None, out3.data_ptr(), batch, M, N, K, L,
+                                _DTYPE_CODE[x.dtype], 1 if weight_layout == "OI" else 0, _ACT_CODE[act1], _ACT_CODE[act2],
+                                _status_word(x.device).data_ptr(), stream)
+    _lib.check(rc, "ditto_b200_ffn")
+    launch_count += 1
+    return out

@@ -82,6 +82,17 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
                               int K, int L, int dtype, int w_layout, int epilogue, void* workspace,
                               size_t ws_bytes, int* status_word, void* stream);
 
+/* Position-wise feed-forward block  y = act2(act1(X W1 + b1) W2 + b2)  with the hidden layer on chip, the
+ * fused form of PositionwiseFeedForward (python/ditto/auto_compute/nn/model/transformer.py:21-34:
+ * linear -> ReLU -> linear -> ReLU, linear with bias as in nn/functional/linear.py:4-41; GELU as in
+ * nn/functional/activation.py:29-39).
+ *   b1 [batch, L], b2 [batch, N]: bias vectors in the input type, either may be NULL
+ *   act1 / act2: 0 identity, 1 ReLU, 2 GELU (tanh form)
+ * Shapes as for the large-N form of ditto_b200_gemm_relu_gemm (M % 128, K % 64, L % 512 == 0, N in 256..1024). */
+int ditto_b200_ffn(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, void* y, int batch,
+                   int M, int N, int K, int L, int dtype, int w_layout, int act1, int act2, int* status_word,
+                   void* stream);
+
 /* Scratch bytes the op needs for this shape (0 when none). */
 size_t ditto_b200_workspace_bytes(int op, int batch, int M, int N, int K, int L, int dtype);
 

@@ -351,3 +351,47 @@ int oracle_max_threads(void) {
   return 1;
 #endif
 }
+
+/* Position-wise feed-forward block  F = act2(in_dtype(act1(A B + b1)) C + b2), fp32 accumulate
+ * (wide: fp64): PositionwiseFeedForward, python/ditto/auto_compute/nn/model/transformer.py:21-34, with
+ * linear + bias as in nn/functional/linear.py:4-41.  act: 0 identity, 1 ReLU (activation.py:9-26),
+ * 2 GELU in the reference's tanh form (activation.py:29-39).  b1 [batch, L], b2 [batch, N] or NULL. */
+static double act_d(double v, int act) {
+  if (act == 1) return v > 0.0 ? v : 0.0;
+  if (act == 2) return 0.5 * v * (1.0 + tanh(v * 0.7978845608 * (1.0 + 0.044715 * v * v)));
+  return v;
+}
+
+void oracle_ffn(const float* A, const float* B, const float* b1, const float* C, const float* b2, float* F, int batch,
+                int M, int N, int K, int L, int act1, int act2, int in_dtype) {
+#pragma omp parallel
+  {
+    double* h = (double*)malloc(sizeof(double) * (size_t)L);
+    double* e = (double*)malloc(sizeof(double) * (size_t)N);
+#pragma omp for collapse(2) schedule(static)
+    for (int b = 0; b < batch; ++b) {
+      for (int m = 0; m < M; ++m) {
+        const float* a = A + ((size_t)b * M + m) * K;
+        const float* Bb = B + (size_t)b * K * L;
+        const float* Cb = C + (size_t)b * L * N;
+        float* f = F + ((size_t)b * M + m) * N;
+        for (int l = 0; l < L; ++l) h[l] = 0.0;
+        for (int k = 0; k < K; ++k) {
+          const double av = a[k];
+          const float* brow = Bb + (size_t)k * L;
+          for (int l = 0; l < L; ++l) h[l] += av * (double)brow[l];
+        }
+        for (int n = 0; n < N; ++n) e[n] = 0.0;
+        for (int l = 0; l < L; ++l) {
+          double hv = (double)(float)h[l] + (b1 ? (double)b1[(size_t)b * L + l] : 0.0);
+          const double hr = (double)round_to((float)act_d(hv, act1), in_dtype);
+          const float* crow = Cb + (size_t)l * N;
+          for (int n = 0; n < N; ++n) e[n] += hr * (double)crow[n];
+        }
+        for (int n = 0; n < N; ++n) f[n] = (float)act_d((double)(float)e[n] + (b2 ? (double)b2[(size_t)b * N + n] : 0.0), act2);
+      }
+    }
+    free(h);
+    free(e);
+  }
+}

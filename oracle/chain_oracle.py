@@ -38,6 +38,7 @@ def lib():
         L.oracle_bmm_softmax_bmm_literal.argtypes = [fp, fp, fp, fp, i, i, i, i, i, i]
         L.oracle_bmm_softmax_bmm.argtypes = [fp, fp, fp, fp, i, i, i, i, i, f, i, i]
         L.oracle_gemm_act_gemm.argtypes = [fp, fp, fp, fp, i, i, i, i, i, i, i, i]
+        L.oracle_ffn.argtypes = [fp, fp, fp, fp, fp, fp, i, i, i, i, i, i, i, i]
         L.baseline_chain_fp32.argtypes = [fp, fp, fp, fp, i, i, i, i, i, i, f, i]
         L.baseline_chain_fp32.restype = i
         L.oracle_max_threads.restype = i
@@ -109,6 +110,38 @@ def gemm_act_gemm(A, B, C, act=1, in_dtype=BF16, wide=False):
     F = np.empty((batch, M, N), np.float32)
     lib().oracle_gemm_act_gemm(_p(A), _p(B), _p(C), _p(F), batch, M, N, K, L, act, in_dtype, int(wide))
     return F
+
+
+def ffn(A, B, b1, C, b2, act1=1, act2=1, in_dtype=BF16):
+    """act2(round(act1(A B + b1)) C + b2); weights [in, out]; biases [batch, L] / [batch, N] or None."""
+    A, B, C = _f32(A), _f32(B), _f32(C)
+    batch, M, N, K, L = _shape(A, B, C)
+    b1 = None if b1 is None else _f32(b1).reshape(batch, L)
+    b2 = None if b2 is None else _f32(b2).reshape(batch, N)
+    F = np.empty((batch, M, N), np.float32)
+    null = ctypes.POINTER(ctypes.c_float)()
+    lib().oracle_ffn(_p(A), _p(B), _p(b1) if b1 is not None else null, _p(C), _p(b2) if b2 is not None else null, _p(F),
+                     batch, M, N, K, L, act1, act2, in_dtype)
+    return F
+
+
+def np_ffn(A, B, b1, C, b2, act1=1, act2=1, in_dtype=BF16):
+    """numpy / fp64 restatement of ffn() for cross-checking the C code."""
+    def act(v, a):
+        if a == 1:
+            return np.where(v > 0, v, 0.0)
+        if a == 2:
+            return 0.5 * v * (1.0 + np.tanh(v * 0.7978845608 * (1.0 + 0.044715 * v * v)))
+        return v
+    A, B, C = (np.asarray(t, np.float64) for t in (A, B, C))
+    H = np.einsum("bmk,bkl->bml", A, B).astype(np.float32).astype(np.float64)
+    if b1 is not None:
+        H = H + np.asarray(b1, np.float64).reshape(A.shape[0], 1, -1)
+    H = round_np(act(H, act1).astype(np.float32), in_dtype).astype(np.float64)
+    Y = np.einsum("bml,bln->bmn", H, C).astype(np.float32).astype(np.float64)
+    if b2 is not None:
+        Y = Y + np.asarray(b2, np.float64).reshape(A.shape[0], 1, -1)
+    return act(Y, act2).astype(np.float32)
 
 
 def baseline_chain_fp32(A, B, C, kind, scale=1.0, threads=0):

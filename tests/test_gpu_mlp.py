@@ -155,3 +155,32 @@ def test_small_n_golden_and_cfg1_shape(cuda, oracle):
     got = _run(cuda, a, b, c, "float16", "identity", "IO")
     want = oracle.gemm_act_gemm(a, b, c, 0, oracle.FP16, wide=False)
     assert_close(got, want, "float16", "cfg1 shape fp16", scale=float(np.abs(want).max()))
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("acts", [("relu", "relu"), ("gelu", "identity"), ("identity", "gelu")])
+@pytest.mark.parametrize("layout", ["OI", "IO"])
+def test_ffn_with_bias(cuda, oracle, dtype, acts, layout):
+    """The reference's feed-forward block: linear (+ bias, [out, in] weights) -> ReLU -> linear -> ReLU
+    (nn/model/transformer.py:21-34), plus its GELU (nn/functional/activation.py:29-39)."""
+    code = {"identity": 0, "relu": 1, "gelu": 2}
+    for (M, N, K, L) in ((128, 256, 64, 512), (256, 1024, 128, 1024)):
+        x, w1, w2 = _inputs(51, 1, M, N, K, L, dtype)
+        rng = np.random.default_rng(52)
+        b1 = W._round(rng.standard_normal((1, L)).astype(np.float32) * 0.5, dtype)
+        b2 = W._round(rng.standard_normal((1, N)).astype(np.float32) * 0.5, dtype)
+        if layout == "OI":
+            d1, d2 = _dev(w1.transpose(0, 2, 1), dtype, cuda), _dev(w2.transpose(0, 2, 1), dtype, cuda)
+        else:
+            d1, d2 = _dev(w1, dtype, cuda), _dev(w2, dtype, cuda)
+        out = torch.full((1, M, N), float("nan"), dtype=TDT[dtype], device=cuda)
+        ops.ffn(_dev(x, dtype, cuda), d1, _dev(b1, dtype, cuda), d2, _dev(b2, dtype, cuda), out=out, act1=acts[0],
+                act2=acts[1], weight_layout=layout)
+        assert ops.device_status(cuda) == 0
+        want = oracle.ffn(x, w1, b1, w2, b2, code[acts[0]], code[acts[1]], ODT[dtype])
+        assert_close(out.float().cpu().numpy(), want, dtype, f"ffn {dtype} {acts} {layout} {(M, N, K, L)}")
+        # no bias, ReLU then identity == the plain chain entry point, bit for bit
+        if acts == ("relu", "relu"):
+            a = ops.ffn(_dev(x, dtype, cuda), d1, None, d2, None, act1="relu", act2="identity", weight_layout=layout)
+            bq = ops.gemm_relu_gemm(_dev(x, dtype, cuda), d1, d2, activation="relu", weight_layout=layout)
+            assert torch.equal(a, bq)

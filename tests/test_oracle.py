@@ -117,6 +117,18 @@ def test_baseline_matches_oracle(oracle, kind):
     np.testing.assert_allclose(got, want, rtol=2e-4, atol=2e-4)
 
 
+def test_ffn_c_matches_numpy(oracle):
+    A, B, C = _rand(20, (2, 40, 64)), _rand(21, (2, 64, 96), -0.2, 0.2), _rand(22, (2, 96, 48), -0.2, 0.2)
+    b1, b2 = _rand(23, (2, 96)), _rand(24, (2, 48))
+    for a1, a2 in ((1, 1), (2, 0), (0, 2)):
+        got = oracle.ffn(A, B, b1, C, b2, a1, a2, oracle.BF16)
+        want = oracle.np_ffn(A, B, b1, C, b2, a1, a2, oracle.BF16)
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+    # without biases and with ReLU / identity it is the plain chain
+    np.testing.assert_allclose(oracle.ffn(A, B, None, C, None, 1, 0, oracle.BF16),
+                               oracle.gemm_act_gemm(A, B, C, 1, oracle.BF16, wide=True), rtol=1e-6, atol=1e-6)
+
+
 def test_cfg1_cpu_case(oracle):
     """BASELINE config 1: E = (A B) D in fp32, A[8,512,64] B[8,64,512] D[8,512,64] ~ U(-1,1)."""
     w = W.WORKLOADS["cfg1"]
