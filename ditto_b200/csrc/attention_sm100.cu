@@ -162,6 +162,7 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bar->tmem_base;
+  if (warp == 0) DITTO_STAMP(512, 0, 8);
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer (one thread)
@@ -382,16 +383,19 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
           for (int i = 0; i < kBN; ++i)
             if (i >= valid) sv[i] = __float_as_uint(-INFINITY);
         }
-        float mx[8];
+        float mx[16];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) mx[u] = fmaxf(__uint_as_float(sv[2 * u]), __uint_as_float(sv[2 * u + 1]));
+        for (int u = 0; u < 16; ++u) mx[u] = __uint_as_float(sv[u]);
 #pragma unroll
         for (int i = 16; i < kBN; i += 16) {
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
-            mx[u] = max3(mx[u], __uint_as_float(sv[i + 2 * u]), __uint_as_float(sv[i + 2 * u + 1]));
+          for (int u = 0; u < 16; ++u) mx[u] = fmaxf(mx[u], __uint_as_float(sv[i + u]));
         }
-        m_new = fmaxf(max3(m, mx[0], mx[1]), fmaxf(max3(mx[2], mx[3], mx[4]), max3(mx[5], mx[6], mx[7])));
+#pragma unroll
+        for (int u = 0; u < 8; ++u) mx[u] = fmaxf(mx[u], mx[u + 8]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], mx[u + 4]);
+        m_new = fmaxf(fmaxf(m, mx[0]), fmaxf(fmaxf(mx[1], mx[2]), mx[3]));
       }
       if constexpr (kSep) {
         if (j > 0) {
@@ -516,6 +520,7 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
 
   tc_fence_before_sync();
   __syncthreads();
+  if (warp == 0) DITTO_STAMP(512, 0, 9);
   if (warp == 0) {
     tmem_dealloc(tmem_base, kTmemCols);
     if (lane == 0 && bar->abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, static_cast<int>(bar->abort_word));
