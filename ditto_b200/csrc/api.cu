@@ -119,7 +119,7 @@ int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void
   // 128-row tiles are handled by TMA zero fill, masked scores and predicated stores.
   if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
   if (N != K || K > 128) return DITTO_ERR_UNSUPPORTED;
-  if (batch > 65535) return DITTO_ERR_UNSUPPORTED;
+  if (static_cast<long long>(batch) * ((M + 127) / 128) > 0x7fffffffLL) return DITTO_ERR_UNSUPPORTED;
 
   const bool bf16 = dtype == DITTO_DTYPE_BF16;
   const int d = K <= 64 ? 64 : 128;             // kernel variant; K itself may be any multiple of 16 below it
@@ -165,7 +165,7 @@ int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M
   if (!(scale > 0.f) || !std::isfinite(scale)) return DITTO_ERR_INVALID_ARG;
   if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
   if (head_dim % 16 || head_dim > 128 || M % 16) return DITTO_ERR_UNSUPPORTED;
-  if (static_cast<long long>(batch) * heads > 65535) return DITTO_ERR_UNSUPPORTED;
+  if (static_cast<long long>(batch) * heads * ((M + 127) / 128) > 0x7fffffffLL) return DITTO_ERR_UNSUPPORTED;
   const bool bf16 = dtype == DITTO_DTYPE_BF16;
   const int d = head_dim <= 64 ? 64 : 128, hidden = heads * head_dim;
   int nt = (M > 128 && !(flags & DITTO_FLAG_ONE_TILE)) ? 2 : 1;
@@ -211,7 +211,7 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
     // Small-N chains (the reference's shape family: N = K = 64, L = 512 ...): the result tile
     // [128, N] fits TMEM next to the intermediate, so the chain runs on the attention kernel with
     // the activation in place of the softmax: A = x, B = w1, C = w2.
-    if (batch > 65535) return DITTO_ERR_UNSUPPORTED;
+    if (static_cast<long long>(batch) * ((M + 127) / 128) > 0x7fffffffLL) return DITTO_ERR_UNSUPPORTED;
     if (w_layout != 0) return DITTO_ERR_UNSUPPORTED;   // w2 as [N, L] is not an operand form of that kernel
     const bool bf16 = dtype == DITTO_DTYPE_BF16;
     const int dk = K <= 64 ? 64 : 128;

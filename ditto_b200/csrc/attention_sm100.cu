@@ -127,12 +127,15 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
   constexpr int kMmaWarp = 4 * NT + 1;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int slice = blockIdx.y;
+  // 1-D grid, tile index fastest: the tiles of a slice are scheduled together (their K/V share L2),
+  // and the number of slices is not limited by the 65535 of the other grid dimensions
+  const int tiles = (p.M + NT * kBM - 1) / (NT * kBM);
+  const int slice = blockIdx.x / tiles;
   // Packed multi-head input: slice = (sequence, head); rows come from the sequence, columns from
   // the head.  Plain batched input has heads == 1 and zero column offsets.
   const int seq = slice / p.heads;
   const int head_col = (slice % p.heads) * p.d;
-  const int m0 = blockIdx.x * (NT * kBM);
+  const int m0 = (blockIdx.x % tiles) * (NT * kBM);
   const int nkv = (p.L + kBN - 1) / kBN;        // the last block may be partial: TMA zero-fills rows >= L
   const int ksteps_d = p.d / 16;                // head dimension actually used by S = Q K^T (<= D / 16)
 
@@ -536,7 +539,7 @@ static cudaError_t launch_one(const AttnParams& p, int batch, cudaStream_t strea
   if (e != cudaSuccess) return e;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.M + NT * kBM - 1) / (NT * kBM), batch, 1);
+  dim3 grid(static_cast<unsigned>((p.M + NT * kBM - 1) / (NT * kBM)) * static_cast<unsigned>(batch), 1, 1);
   kern<<<grid, threads_for(NT), SM::kBytes, stream>>>(p);
   return cudaGetLastError();
 }

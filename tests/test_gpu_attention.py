@@ -229,6 +229,20 @@ def test_ragged_shapes(cuda, oracle, dtype, layout):
             assert_close(got, _oracle(oracle, q, k, v, dtype, scale), dtype, f"{dtype} {layout} flags={flags} {(b, M, d, L)}")
 
 
+def test_many_slices(cuda):
+    """More slices than the 65535 of a grid's y / z dimension (e.g. batch x heads of a long batch)."""
+    n = 70000
+    g = torch.Generator(device=cuda).manual_seed(2)
+    q = torch.randn(n, 128, 64, device=cuda, generator=g).half()
+    k = torch.randn(n, 128, 64, device=cuda, generator=g).half()
+    v = torch.randn(n, 128, 64, device=cuda, generator=g).half()
+    out = ops.bmm_softmax_bmm(q, k, v, scale=0.125, key_layout="LK")
+    assert ops.device_status(cuda) == 0
+    for i in (0, 65535, 65536, n - 1):
+        ref = torch.softmax(q[i].float() @ k[i].float().t() * 0.125, -1) @ v[i].float()
+        assert (out[i].float() - ref).abs().max().item() <= 2e-3
+
+
 def test_unsupported_shapes_raise(cuda):
     q = torch.zeros(1, 128, 144, dtype=torch.float16, device=cuda)     # head dimension above 128
     kv = torch.zeros(1, 128, 64, dtype=torch.float16, device=cuda)
