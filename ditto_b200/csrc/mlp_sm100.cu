@@ -70,6 +70,7 @@ struct MlpParams {
   void* y;             // Y  [batch, M, N]
   int M, N, K, L;
   int w_oi;            // 1: weights stored [out, in] (K-major B operands)
+  int w_atoms;         // [in, out] weights: maps are 3-D atom views, one box per operand tile
   int act1, act2;      // 0 identity, 1 ReLU, 2 GELU (tanh form) after the first / second GEMM
   const void* b1;      // optional bias [batch, L] added before act1 (16-bit, same type as X); may be null
   const void* b2;      // optional bias [batch, N] added before act2; may be null
@@ -186,6 +187,8 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           tma_load_2d(dst, &p.map_x, &bar->full[ps], ks * 64, b * p.M + row0);
           if (p.w_oi) {
             tma_load_2d(dst + 16384, &p.map_w1, &bar->full[ps], ks * 64, b * p.L + g * kChunk);
+          } else if (p.w_atoms) {
+            tma_load_3d(dst + 16384, &p.map_w1, &bar->full[ps], 0, b * p.K + ks * 64, g * (kChunk / 64));
           } else {
             tma_load_2d(dst + 16384, &p.map_w1, &bar->full[ps], g * kChunk, b * p.K + ks * 64);
             tma_load_2d(dst + 16384 + 8192, &p.map_w1, &bar->full[ps], g * kChunk + 64, b * p.K + ks * 64);
@@ -201,6 +204,8 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
             if (!ok) break;
             if (p.w_oi) {
               tma_load_2d(dst, &p.map_w2, &bar->full[ps], g * kChunk + kk * 64, b * p.N + q * NS);
+            } else if (p.w_atoms) {
+              tma_load_3d(dst, &p.map_w2, &bar->full[ps], 0, b * p.L + g * kChunk + kk * 64, q * (NS / 64));
             } else {
               for (int a = 0; a < NS / 64; ++a)
                 tma_load_2d(dst + a * 8192, &p.map_w2, &bar->full[ps], q * NS + a * 64, b * p.L + g * kChunk + kk * 64);
@@ -426,6 +431,26 @@ bool mlp_make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// [rows, cols] row-major seen as (64 columns, rows, cols / 64): one box of 64 x box_rows x box_atoms
+// brings box_atoms 64-column swizzle atoms of an MN-major operand tile with a single TMA operation
+// (atom a lands at a * box_rows * 128 bytes, exactly the operand layout).
+bool mlp_make_atom_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows,
+                       uint32_t box_atoms) {
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return false;
+  EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  const cuuint64_t dims[3] = {64, rows, cols / 64};
+  const cuuint64_t strides[2] = {cols * 2, 128};
+  const cuuint32_t box[3] = {64, box_rows, box_atoms};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
                      bool bf16, int w_layout, int epilogue, int* status, cudaStream_t stream, long long* trace,
@@ -451,8 +476,13 @@ int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int
     ok = ok && mlp_make_map(&p.map_w1, bf16, w1, K, static_cast<uint64_t>(batch) * L, 64, 128);
     ok = ok && mlp_make_map(&p.map_w2, bf16, w2, L, static_cast<uint64_t>(batch) * N, 64, NS);
   } else {
-    ok = ok && mlp_make_map(&p.map_w1, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, 64);
-    ok = ok && mlp_make_map(&p.map_w2, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, 64);
+    // one TMA operation per operand tile where the driver accepts the atom view, else one per atom
+    p.w_atoms = mlp_make_atom_map(&p.map_w1, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, 2) &&
+                mlp_make_atom_map(&p.map_w2, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, NS / 64);
+    if (!p.w_atoms) {
+      ok = ok && mlp_make_map(&p.map_w1, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, 64);
+      ok = ok && mlp_make_map(&p.map_w2, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, 64);
+    }
   }
   if (!ok) return DITTO_ERR_DRIVER;
   p.y = y;
