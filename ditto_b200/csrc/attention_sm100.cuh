@@ -29,4 +29,8 @@ struct AttnParams {
 cudaError_t launch_attention(const AttnParams& p, int batch, int d, bool bf16, int nt, bool psmem, int mode,
                              cudaStream_t stream);
 
+// Persistent variant for head dimensions up to 64 (attention_persistent_sm100.cu): two CTAs per SM walk the
+// (slice, tile) work items.  mode as above.
+cudaError_t launch_attention_persistent(const AttnParams& p, int batch, bool bf16, int mode, cudaStream_t stream);
+
 }  // namespace ditto_b200

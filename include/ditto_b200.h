@@ -44,7 +44,7 @@ extern "C" {
 
 /* flags of ditto_b200_bmm_softmax_bmm */
 #define DITTO_FLAG_P_VIA_SMEM 1   /* stage the probabilities through shared memory instead of TMEM */
-#define DITTO_FLAG_ONE_TILE 2     /* one 128-row query tile per CTA */
+#define DITTO_FLAG_ONE_TILE 2     /* one 128-row query tile per CTA, one CTA per tile (no persistent work loop) */
 #define DITTO_FLAG_TWO_TILES 4    /* two query tiles per CTA even where one is the default (N = K = 64) */
 
 /* Fused attention chain  out = softmax(scale * Q K^T) V, replacing the module TVM builds from

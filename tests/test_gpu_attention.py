@@ -224,7 +224,7 @@ def test_ragged_shapes(cuda, oracle, dtype, layout):
     for (b, M, d, L) in shapes:
         q, k, v = _case(17, b, M, L, d, dtype)
         scale = d ** -0.5
-        for flags in (0, _lib.FLAG_TWO_TILES):
+        for flags in (0, _lib.FLAG_ONE_TILE, _lib.FLAG_TWO_TILES):
             got = _run(cuda, q, k, v, dtype, scale, layout, flags)
             assert_close(got, _oracle(oracle, q, k, v, dtype, scale), dtype, f"{dtype} {layout} flags={flags} {(b, M, d, L)}")
 
@@ -241,6 +241,29 @@ def test_many_slices(cuda):
     for i in (0, 65535, 65536, n - 1):
         ref = torch.softmax(q[i].float() @ k[i].float().t() * 0.125, -1) @ v[i].float()
         assert (out[i].float() - ref).abs().max().item() <= 2e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_work_loop_many_items(cuda, dtype):
+    """Head dims <= 64 with at most 1024 keys run a persistent kernel whose CTAs walk several
+    (slice, row block) items each, with Q double-buffered and scores issued across item borders:
+    every output row of a launch with ~7 items per CTA is compared with a float32 product, for one
+    to five key blocks per item and a ragged tail.  1152 keys take the non-persistent kernel."""
+    g = torch.Generator(device=cuda).manual_seed(5)
+    for (b, M, L, d) in ((2100, 128, 128, 64), (1050, 256, 256, 64), (700, 384, 640, 64), (530, 208, 400, 48),
+                         (300, 512, 1024, 32), (40, 512, 1152, 64)):
+        q = (torch.rand(b, M, d, device=cuda, generator=g) - 0.5).to(dtype)
+        k = (torch.rand(b, L, d, device=cuda, generator=g) - 0.5).to(dtype)
+        v = (torch.rand(b, L, d, device=cuda, generator=g) - 0.5).to(dtype)
+        out = torch.full((b, M, d), float("nan"), dtype=dtype, device=cuda)
+        ops.bmm_softmax_bmm(q, k, v, out=out, scale=1.0, key_layout="LK")
+        assert ops.device_status(cuda) == 0
+        ref = torch.softmax(q.float() @ k.float().transpose(1, 2), -1) @ v.float()
+        tol = 2e-2 if dtype == torch.float16 else 3e-2
+        err = (out.float() - ref).abs()
+        bound = tol * ref.abs() + (1e-3 if dtype == torch.float16 else 4e-3)
+        assert not torch.isnan(out).any(), (b, M, L, d)
+        assert bool((err <= bound).all()), ((b, M, L, d), err.max().item())
 
 
 def test_unsupported_shapes_raise(cuda):
