@@ -11,8 +11,9 @@ Reference definitions: python/ditto/auto_compute/nn/functional/bmm_chain.py:40-1
 chain), benchmark/chimera/cpu/bmm_bmm_cpu.py:55-116 (plain chain),
 python_test/auto_tensorize/test_hyper_fusion_cpu.py:24-96 (ReLU chain).
 
-Parity unpinned: the reference ships no golden vectors for these chains and cannot be built here
-(TVM is an absent submodule); see the header of chain_oracle.c for what its tests do assert.
+Parity: pinned at the reference's CPU micro-kernels (ref_microkernels.py, bit for bit), unpinned for
+the fp16 / bf16 forms above them - the reference ships no golden vectors and its generated kernels
+cannot be built here (TVM is an absent submodule); the header of chain_oracle.c has the details.
 """
 import ctypes
 import os
@@ -28,9 +29,12 @@ _lib = None
 def lib():
     global _lib
     if _lib is None:
-        path = _build.LIB
-        if not os.path.exists(path):
-            path = _build.build()
+        try:
+            path = _build.build()              # rebuilds only when chain_oracle.c is newer than the library
+        except (OSError, RuntimeError):
+            path = _build.LIB
+            if not os.path.exists(path):
+                raise
         L = ctypes.CDLL(path)
         fp = ctypes.POINTER(ctypes.c_float)
         i, f = ctypes.c_int, ctypes.c_float
@@ -39,6 +43,8 @@ def lib():
         L.oracle_bmm_softmax_bmm.argtypes = [fp, fp, fp, fp, i, i, i, i, i, f, i, i]
         L.oracle_gemm_act_gemm.argtypes = [fp, fp, fp, fp, i, i, i, i, i, i, i, i]
         L.oracle_ffn.argtypes = [fp, fp, fp, fp, fp, fp, i, i, i, i, i, i, i, i]
+        L.oracle_exp_ref_literal.argtypes = [fp, fp, ctypes.c_long]
+        L.oracle_bmm_softmax_bmm_cpu_literal.argtypes = [fp, fp, fp, fp, i, i, i, i, i]
         L.baseline_chain_fp32.argtypes = [fp, fp, fp, fp, i, i, i, i, i, i, f, i]
         L.baseline_chain_fp32.restype = i
         L.oracle_max_threads.restype = i
@@ -91,6 +97,23 @@ def bmm_softmax_bmm_literal(A, B, C, in_dtype=FP16):
     batch, M, N, K, L = _shape(A, B, C)
     F = np.empty((batch, M, N), np.float32)
     lib().oracle_bmm_softmax_bmm_literal(_p(A), _p(B), _p(C), _p(F), batch, M, N, K, L, in_dtype)
+    return F
+
+
+def exp_ref_literal(x):
+    """The reference's CPU exponential (polynomial, clamped), bit for bit: intrinsic.py:1480-1672."""
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().oracle_exp_ref_literal(_p(x), _p(y), x.size)
+    return y
+
+
+def bmm_softmax_bmm_cpu_literal(A, B, C):
+    """The reference's fp32 CPU attention chain (benchmark/chimera/cpu/bmm_softmax_bmm.py:64-170)."""
+    A, B, C = _f32(A), _f32(B), _f32(C)
+    batch, M, N, K, L = _shape(A, B, C)
+    F = np.empty((batch, M, N), dtype=np.float32)
+    lib().oracle_bmm_softmax_bmm_cpu_literal(_p(A), _p(B), _p(C), _p(F), batch, M, N, K, L)
     return F
 
 

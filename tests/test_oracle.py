@@ -143,7 +143,8 @@ def test_golden_vectors(oracle):
     """Committed outputs (tests/golden/*.npz, written by tests/golden/make_golden.py) are
     reproduced bit for bit by today's oracle on the regenerated seeded inputs."""
     from tests.golden import make_golden
-    files = sorted(glob.glob(os.path.join(GOLDEN, "*.npz")))
+    files = [f for f in sorted(glob.glob(os.path.join(GOLDEN, "*.npz")))
+             if os.path.splitext(os.path.basename(f))[0] in make_golden.CASES]
     assert files, "no golden vectors committed"
     for path in files:
         case = os.path.splitext(os.path.basename(path))[0]
@@ -151,3 +152,70 @@ def test_golden_vectors(oracle):
         fresh = make_golden.compute(case, oracle)
         for key in stored.files:
             assert np.array_equal(stored[key], fresh[key]), f"{case}:{key} changed"
+
+
+# ---------------------------------------------------------------- pins against the reference's own micro-kernels
+REF_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "ref_microkernels.npz")
+
+
+def _bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def test_reference_microkernel_golden_exp(oracle):
+    """oracle_exp_ref_literal reproduces the reference's AVX-512 exponential bit for bit on the committed
+    vectors (edge values, +-90, N(0, 8), U(-1, 1)); those vectors were produced by the kernel the reference
+    generates (intrinsic.py:1480-1672), see tests/golden/make_ref_golden.py."""
+    g = np.load(REF_GOLDEN)
+    got = oracle.exp_ref_literal(g["exp_x"])
+    assert np.array_equal(_bits(got), _bits(g["exp_y"]))
+    # and what that kernel is: exp up to the Cody-Waite sign slip, 4.24e-4 relative per unit of round(x / ln 2)
+    x = g["exp_x"].astype(np.float64)
+    inside = np.abs(x) < 80
+    n = np.floor(g["exp_x"] * np.float32(1.44269504088896341) + np.float32(0.5)).astype(np.float64)   # as the kernel rounds it
+    model = np.exp(x) * np.exp(2 * n * -2.12194440e-4)
+    assert np.max(np.abs(g["exp_y"][inside] / model[inside] - 1)) < 5e-6
+
+
+def test_reference_microkernel_golden_chains(oracle):
+    """The three CPU chains evaluated through the reference's 6 x 16 GEMM micro-kernel (and its exponential):
+    the C restatement equals them bit for bit where it fixes the operation order (the literal softmax chain,
+    the timed baseline's register tile), and to 1e-6 relative where the compiler chooses it."""
+    g = np.load(REF_GOLDEN)
+    i = 0
+    while f"c{i}_shape" in g:
+        a, b, c = g[f"c{i}_a"], g[f"c{i}_b"], g[f"c{i}_c"]
+        assert np.array_equal(_bits(oracle.bmm_softmax_bmm_cpu_literal(a, b, c)), _bits(g[f"c{i}_bmm_softmax_bmm"])), i
+        assert np.array_equal(_bits(oracle.baseline_chain_fp32(a, b, c, 2)), _bits(g[f"c{i}_bmm_bmm"])), i
+        assert np.array_equal(_bits(oracle.baseline_chain_fp32(a, b, c, 1)), _bits(g[f"c{i}_bmm_relu_bmm"])), i
+        for act, key in ((2, "bmm_bmm"), (1, "bmm_relu_bmm")):
+            got = oracle.gemm_act_gemm(a, b, c, act=act, in_dtype=oracle.FP32)
+            want = g[f"c{i}_{key}"]
+            assert np.max(np.abs(got - want)) <= 1e-6 * np.max(np.abs(want)) + 1e-6, (i, key)
+        # the stable-softmax oracle the GPU tests use differs from the reference's CPU chain only by the
+        # exponential's error (<= 4.24e-4 * |n|, partly cancelling in the quotient) and summation order
+        stable = oracle.bmm_softmax_bmm(a, b, c, 1.0, oracle.FP32, wide=True)
+        want = g[f"c{i}_bmm_softmax_bmm"]
+        assert np.max(np.abs(stable - want)) <= 2e-2 * np.max(np.abs(want)), i
+        i += 1
+    assert i == 3
+
+
+def test_reference_microkernels_live(oracle):
+    """Where the reference tree (or the library built from it) is present: fresh seeded inputs through the
+    reference's micro-kernels against the restatement, so the pin is not limited to the committed cases."""
+    from oracle import ref_microkernels as R
+    if not R.available():
+        pytest.skip("reference micro-kernel library not built (no reference tree on this machine)")
+    rng = np.random.default_rng(2024)
+    for (batch, M, N, K, L) in ((1, 13, 16, 32, 32), (2, 30, 48, 128, 64)):
+        a = rng.uniform(-1, 1, (batch, M, K)).astype(np.float32)
+        b = rng.uniform(-1, 1, (batch, K, L)).astype(np.float32)
+        c = rng.uniform(-1, 1, (batch, L, N)).astype(np.float32)
+        assert np.array_equal(_bits(oracle.baseline_chain_fp32(a, b, c, 2)), _bits(R.bmm_bmm(a, b, c)))
+        assert np.array_equal(_bits(oracle.baseline_chain_fp32(a, b, c, 1)), _bits(R.bmm_relu_bmm(a, b, c)))
+        if R.has_exp():
+            assert np.array_equal(_bits(oracle.bmm_softmax_bmm_cpu_literal(a, b, c)), _bits(R.bmm_softmax_bmm_cpu(a, b, c)))
+    if R.has_exp():
+        x = rng.normal(0, 20, (24, 64)).astype(np.float32)
+        assert np.array_equal(_bits(oracle.exp_ref_literal(x)), _bits(R.exp(x)))
