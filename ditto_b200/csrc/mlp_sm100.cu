@@ -17,9 +17,9 @@
 // The hidden activations therefore exist only in TMEM and (distributed) shared memory.
 // No TMA load in this file uses cluster multicast; every CTA fetches its own operands.
 //
-// Warp roles (224 threads): warps 0-3 epilogue (thread r <-> row r / TMEM lane r), warp 4 TMA
-// producer, warp 5 MMA issuer (converged, one elected lane issues), warp 6 relay (tells all four
-// CTAs when this CTA has finished reading a round of hidden chunks).
+// Warp roles (256 threads): warps 0-3 epilogue (thread r <-> row r / TMEM lane r), warps 4 and 7 TMA
+// producers (alternate ring stages), warp 5 MMA issuer (converged, one elected lane issues),
+// warp 6 relay (tells all four CTAs when this CTA has finished reading a round of hidden chunks).
 //
 // Per round i (four chunks, one per CTA) on each CTA's tensor pipe:
 //   GEMM1(own chunk of round i+1)  |  GEMM2(4 chunks of round i)
@@ -47,6 +47,10 @@
 #define DITTO_STAMP(i, k) do {} while (0)
 #endif
 
+#ifndef DITTO_MLP_SLOTS
+#define DITTO_MLP_SLOTS 3
+#endif
+
 namespace ditto_b200 {
 
 namespace {
@@ -55,11 +59,16 @@ constexpr int kCluster = 4;
 constexpr int kRows = 128;            // rows of X / Y per cluster
 constexpr int kChunk = 128;           // hidden columns per chunk
 constexpr int kStageBytes = 32 * 1024;
-constexpr int kStages = 3;
 constexpr int kSlotBytes = kRows * kChunk * 2;   // one hidden chunk, 16-bit: 32 KB
-constexpr int kThreads = 224;
+// Shared memory holds kSlots hidden-chunk slots and a kStages-deep operand ring, 7 x 32 KB together.
+// Chunk n (owner CTA n % 4) lives in slot n % kSlots; a slot is handed on chunk by chunk, so the
+// exchange of chunk n + kSlots overlaps GEMM2 on the chunks in between.
+constexpr int kSlots = DITTO_MLP_SLOTS;
+constexpr int kStages = 7 - kSlots;
+constexpr int kThreads = 256;
+constexpr uint32_t kProducers = 2;         // TMA-issuing threads (warps 4 and 7)
 constexpr int kOffSlots = 0;
-constexpr int kOffRing = kOffSlots + kCluster * kSlotBytes;
+constexpr int kOffRing = kOffSlots + kSlots * kSlotBytes;
 constexpr int kOffBar = kOffRing + kStages * kStageBytes;
 constexpr int kSmemBytes = kOffBar + 256 + 1024;
 
@@ -81,9 +90,9 @@ struct MlpParams {
 struct Bars {
   uint64_t full[kStages], empty[kStages];
   uint64_t h_tmem_full[2], h_tmem_empty[2];
-  uint64_t h_ready;      // this round's four hidden chunks are in this CTA's slots
-  uint64_t g2_done;      // this CTA's GEMM2 of the round has finished reading the slots
-  uint64_t slots_free;   // all four CTAs have (count 4, remote arrivals)
+  uint64_t h_ready[kSlots];    // the chunk of the slot's current use is present (own: local arrive; peer's: pushed bytes)
+  uint64_t g2_done[kSlots];    // this CTA's GEMM2 has finished reading the slot
+  uint64_t slot_free[kSlots];  // all four CTAs have (count 4, remote arrivals); kept at the CTA that writes the slot next
   uint64_t y_done;
   uint64_t epi_sync;     // the 128 epilogue threads, once per round (bounded, unlike bar.sync)
   uint32_t tmem_base;
@@ -130,6 +139,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const int b = blockIdx.y;
   const int NS = p.N / kCluster;          // this CTA's Y columns
   const int rounds = p.L / (kCluster * kChunk);
+  const int chunks = rounds * kCluster;   // hidden chunks in all; this CTA owns chunk 4 i + q of round i
   const int ksteps1 = p.K / 64;
 
   if (threadIdx.x == 0) {
@@ -141,9 +151,11 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       mbar_init(&bar->h_tmem_full[i], 1);
       mbar_init(&bar->h_tmem_empty[i], kRows);
     }
-    mbar_init(&bar->h_ready, 1);
-    mbar_init(&bar->g2_done, 1);
-    mbar_init(&bar->slots_free, kCluster);
+    for (int i = 0; i < kSlots; ++i) {
+      mbar_init(&bar->h_ready[i], 1);
+      mbar_init(&bar->g2_done[i], 1);
+      mbar_init(&bar->slot_free[i], kCluster);
+    }
     mbar_init(&bar->y_done, 1);
     mbar_init(&bar->epi_sync, kRows);
     bar->abort_word = 0;
@@ -161,16 +173,21 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const uint32_t tmem_y = tmem_base;
   const uint32_t tmem_h = tmem_base + 256;
 
-  if (warp == 4) {
-    // ------------------------------------------------------------ TMA producer (one thread)
+  if (warp == 4 || warp == 7) {
+    // ------------------------------------------------------------ TMA producers (one thread each)
+    // One thread gets a ring stage out per ~350-700 clocks (barrier wait + expect_tx + the copies),
+    // i.e. at most ~46 B/clk of operands; two threads taking alternate stages lift that limit.
     if (lane == 0) {
+      const uint32_t pw = warp == 4 ? 0u : 1u;
       tma_prefetch_desc(&p.map_x);
       tma_prefetch_desc(&p.map_w1);
       tma_prefetch_desc(&p.map_w2);
       int ps = 0;
-      uint32_t pph = 0;
+      uint32_t pph = 0, cnt = 0;
       bool ok = true;
+      // Both producers walk the same sequence of stages; each fills the ones of its parity.
       auto acquire = [&](uint32_t bytes, uint32_t code) -> uint8_t* {
+        if ((cnt++ & (kProducers - 1)) != pw) return nullptr;
         ok = mbar_wait(&bar->empty[ps], pph ^ 1, abort_word, code);
         if (!ok) return nullptr;
         mbar_arrive_expect_tx(&bar->full[ps], bytes);
@@ -179,29 +196,28 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       auto advance = [&]() {
         if (++ps == kStages) { ps = 0; pph ^= 1; }
       };
-      auto load_g1 = [&](int i) {         // operands of GEMM1 for this CTA's chunk of round i
+      auto load_g1 = [&](int i, int ks0, int ks1) {   // operands of k-steps [ks0, ks1) of GEMM1 for this CTA's chunk of round i
         const int g = i * kCluster + static_cast<int>(q);
-        for (int ks = 0; ks < ksteps1 && ok; ++ks) {
+        for (int ks = ks0; ks < ks1 && ok; ++ks) {
           uint8_t* dst = acquire(2 * 16384, 0x100 + i);
-          if (!ok) break;
-          tma_load_2d(dst, &p.map_x, &bar->full[ps], ks * 64, b * p.M + row0);
-          if (p.w_oi) {
-            tma_load_2d(dst + 16384, &p.map_w1, &bar->full[ps], ks * 64, b * p.L + g * kChunk);
-          } else if (p.w_atoms) {
-            tma_load_3d(dst + 16384, &p.map_w1, &bar->full[ps], 0, b * p.K + ks * 64, g * (kChunk / 64));
-          } else {
-            tma_load_2d(dst + 16384, &p.map_w1, &bar->full[ps], g * kChunk, b * p.K + ks * 64);
-            tma_load_2d(dst + 16384 + 8192, &p.map_w1, &bar->full[ps], g * kChunk + 64, b * p.K + ks * 64);
+          if (dst != nullptr) {
+            tma_load_2d(dst, &p.map_x, &bar->full[ps], ks * 64, b * p.M + row0);
+            if (p.w_oi) {
+              tma_load_2d(dst + 16384, &p.map_w1, &bar->full[ps], ks * 64, b * p.L + g * kChunk);
+            } else if (p.w_atoms) {
+              tma_load_3d(dst + 16384, &p.map_w1, &bar->full[ps], 0, b * p.K + ks * 64, g * (kChunk / 64));
+            } else {
+              tma_load_2d(dst + 16384, &p.map_w1, &bar->full[ps], g * kChunk, b * p.K + ks * 64);
+              tma_load_2d(dst + 16384 + 8192, &p.map_w1, &bar->full[ps], g * kChunk + 64, b * p.K + ks * 64);
+            }
           }
           advance();
         }
       };
-      auto load_g2 = [&](int i) {         // this CTA's W2 slice for the four chunks of round i
-        for (int c = 0; c < kCluster && ok; ++c) {
-          const int g = i * kCluster + c;
-          for (int kk = 0; kk < 2 && ok; ++kk) {
-            uint8_t* dst = acquire(64 * NS * 2, 0x200 + i);
-            if (!ok) break;
+      auto load_g2 = [&](int g) {         // this CTA's W2 slice for hidden chunk g
+        for (int kk = 0; kk < 2 && ok; ++kk) {
+          uint8_t* dst = acquire(64 * NS * 2, 0x200 + (g >> 2));
+          if (dst != nullptr) {
             if (p.w_oi) {
               tma_load_2d(dst, &p.map_w2, &bar->full[ps], g * kChunk + kk * 64, b * p.N + q * NS);
             } else if (p.w_atoms) {
@@ -210,15 +226,17 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
               for (int a = 0; a < NS / 64; ++a)
                 tma_load_2d(dst + a * 8192, &p.map_w2, &bar->full[ps], q * NS + a * 64, b * p.L + g * kChunk + kk * 64);
             }
-            advance();
           }
+          advance();
         }
       };
-      load_g1(0);
-      if (rounds > 1) load_g1(1);
-      for (int i = 0; i < rounds && ok; ++i) {
-        load_g2(i);
-        if (i + 2 < rounds) load_g1(i + 2);
+      // the order the MMA warp consumes the ring in: see there
+      load_g1(0, 0, ksteps1);
+      if (rounds > 1) load_g1(1, 0, ksteps1);
+      for (int n = 0; n < chunks && ok; ++n) {
+        const int i = n >> 2, c = n & 3;
+        load_g2(n);
+        if (i + 2 < rounds) load_g1(i + 2, c * ksteps1 / 4, (c + 1) * ksteps1 / 4);
       }
     }
   } else if (warp == 5) {
@@ -240,11 +258,12 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     auto advance = [&]() {
       if (++cs == kStages) { cs = 0; cph ^= 1; }
     };
-    auto g1 = [&](int i) {
+    // GEMM1 of this CTA's chunk of round i, k-steps [ks0, ks1); `first` / `last`: the part that starts / ends the chunk
+    auto g1 = [&](int i, int ks0, int ks1, bool first, bool last) {
       const int hb = i & 1;
-      if (i >= 2) ok = wait(&bar->h_tmem_empty[hb], ((i >> 1) - 1) & 1, 0x300 + i);
-      if (lane == 0) DITTO_STAMP(i, 0);
-      for (int ks = 0; ks < ksteps1 && ok; ++ks) {
+      if (first && i >= 2) ok = wait(&bar->h_tmem_empty[hb], ((i >> 1) - 1) & 1, 0x300 + i);
+      if (first && lane == 0) DITTO_STAMP(i, 0);
+      for (int ks = ks0; ks < ks1 && ok; ++ks) {
         ok = wait(&bar->full[cs], cph, 0x310 + i);
         if (!ok) break;
         const uint32_t st = ring + cs * kStageBytes;
@@ -258,56 +277,67 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         umma_commit_elected(&bar->empty[cs], issuer);
         advance();
       }
-      if (ok) umma_commit_elected(&bar->h_tmem_full[hb], issuer);
-      if (lane == 0) DITTO_STAMP(i, 1);
+      if (last && ok) umma_commit_elected(&bar->h_tmem_full[hb], issuer);
+      if (last && lane == 0) DITTO_STAMP(i, 1);
     };
-    auto g2 = [&](int i) {
-      if (lane == 0) DITTO_STAMP(i, 2);
-      ok = wait(&bar->h_ready, i & 1, 0x400 + i);
-      if (lane == 0) DITTO_STAMP(i, 3);
-      for (int c = 0; c < kCluster && ok; ++c) {
-        for (int kk = 0; kk < 2 && ok; ++kk) {
-          ok = wait(&bar->full[cs], cph, 0x410 + i);
-          if (!ok) break;
-          const uint32_t st = ring + cs * kStageBytes;
-          const uint64_t da = umma_desc_sw128(slots + c * kSlotBytes + kk * 16384, 16, 1024);
-          const uint64_t db = p.w_oi ? umma_desc_sw128(st, 16, 1024) : umma_desc_sw128(st, 8192, 1024);
+    // GEMM2 on hidden chunk g (any CTA's), accumulated into Y
+    auto g2 = [&](int g) {
+      const int sl = g % kSlots;
+      if ((g & 3) != static_cast<int>(q) && lane == 0)
+        mbar_arrive_expect_tx(&bar->h_ready[sl], kSlotBytes);   // a peer pushes this chunk; the owner's own copy arrives locally
+      __syncwarp();
+      if (lane == 0 && (g & 3) == 0) DITTO_STAMP(g >> 2, 2);
+      ok = wait(&bar->h_ready[sl], (g / kSlots) & 1, 0x400 + (g >> 2));
+      if (lane == 0) DITTO_STAMP(g >> 2, 9 + (g & 3));
+      for (int kk = 0; kk < 2 && ok; ++kk) {
+        ok = wait(&bar->full[cs], cph, 0x410 + (g >> 2));
+        if (!ok) break;
+        const uint32_t st = ring + cs * kStageBytes;
+        const uint64_t da = umma_desc_sw128(slots + sl * kSlotBytes + kk * 16384, 16, 1024);
+        const uint64_t db = p.w_oi ? umma_desc_sw128(st, 16, 1024) : umma_desc_sw128(st, 8192, 1024);
 #pragma unroll
-          for (int s4 = 0; s4 < 4; ++s4) {
-            const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
-            umma_ss_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (i | c | kk | s4) ? 1u : 0u, issuer);
-          }
-          umma_commit_elected(&bar->empty[cs], issuer);
-          advance();
+        for (int s4 = 0; s4 < 4; ++s4) {
+          const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
+          umma_ss_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (g | kk | s4) ? 1u : 0u, issuer);
         }
+        umma_commit_elected(&bar->empty[cs], issuer);
+        advance();
       }
-      if (ok) umma_commit_elected(&bar->g2_done, issuer);
-      if (lane == 0) DITTO_STAMP(i, 4);
+      if (ok) umma_commit_elected(&bar->g2_done[sl], issuer);
+      if (lane == 0 && (g & 3) == 3) DITTO_STAMP(g >> 2, 4);
     };
-    g1(0);
-    if (rounds > 1 && ok) g1(1);
-    for (int i = 0; i < rounds && ok; ++i) {
-      g2(i);
-      if (i + 2 < rounds && ok) g1(i + 2);
+    // Tensor-pipe order: GEMM1 of the first two own chunks, then chunk by chunk GEMM2(chunk n) followed by a
+    // quarter of GEMM1 of the own chunk two rounds ahead, so that a chunk that arrives late stalls little.
+    g1(0, 0, ksteps1, true, true);
+    if (rounds > 1 && ok) g1(1, 0, ksteps1, true, true);
+    for (int n = 0; n < chunks && ok; ++n) {
+      const int i = n >> 2, c = n & 3;
+      g2(n);
+      if (i + 2 < rounds && ok) g1(i + 2, c * ksteps1 / 4, (c + 1) * ksteps1 / 4, c == 0, c == 3);
     }
     if (ok) umma_commit_elected(&bar->y_done, issuer);
   } else if (warp == 6) {
     // ------------------------------------------------------------ relay (one thread)
     if (lane == 0) {
-      for (int i = 0; i < rounds; ++i) {
-        if (!mbar_wait(&bar->g2_done, i & 1, abort_word, 0x500 + i)) break;
-        DITTO_STAMP(i, 5);
-        for (uint32_t c = 0; c < kCluster; ++c) mbar_arrive_cluster(&bar->slots_free, c);
+      for (int n = 0; n < chunks; ++n) {
+        const int sl = n % kSlots;
+        if (!mbar_wait(&bar->g2_done[sl], (n / kSlots) & 1, abort_word, 0x500 + (n >> 2))) break;
+        if ((n & 3) == 3) DITTO_STAMP(n >> 2, 5);
+        // tell the CTA that writes this slot next (the owner of chunk n + kSlots)
+        if (n + kSlots < chunks) mbar_arrive_cluster(&bar->slot_free[sl], static_cast<uint32_t>((n + kSlots) & 3));
       }
     }
   } else if (warp < 4) {
     // ------------------------------------------------------------ epilogue
     const int row = warp * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    uint8_t* my_slot = smem + kOffSlots + q * kSlotBytes;
     bool ok = true;
+    uint32_t free_waits[kSlots] = {};       // completed waits per slot: the parity of the next one
     for (int i = 0; i < rounds; ++i) {
       const int hb = i & 1;
+      const int g = i * kCluster + static_cast<int>(q);   // this CTA's chunk of the round
+      const int sl = g % kSlots;
+      uint8_t* my_slot = smem + kOffSlots + sl * kSlotBytes;
       ok = mbar_wait(&bar->h_tmem_full[hb], (i >> 1) & 1, abort_word, 0x600 + i);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -331,9 +361,13 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         }
         pk[j] = pack2<BF16>(apply_act(v0, p.act1), apply_act(v1, p.act1));
       }
-      if (i > 0) {
-        // every CTA of the cluster has finished GEMM2 of the previous round: slots may be overwritten
-        ok = mbar_wait_cluster(&bar->slots_free, (i - 1) & 1, abort_word, 0x700 + i);
+      if (g >= kSlots) {
+        // every CTA of the cluster has finished GEMM2 on the slot's previous chunk: it may be overwritten
+        uint32_t par = 0;
+#pragma unroll
+        for (int t = 0; t < kSlots; ++t)
+          if (t == sl) par = free_waits[t]++ & 1;
+        ok = mbar_wait_cluster(&bar->slot_free[sl], par, abort_word, 0x700 + i);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
@@ -350,13 +384,12 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       if (!ok) break;
       if (threadIdx.x == 0) {
         const uint32_t slot_addr = smem_u32(my_slot);
-        const uint32_t bar_addr = smem_u32(&bar->h_ready);
+        const uint32_t bar_addr = smem_u32(&bar->h_ready[sl]);
         for (uint32_t d = 1; d < kCluster; ++d) {
-          const uint32_t c = (q + d) % kCluster;   // rotated: senders do not all hit the same destination first
+          const uint32_t c = (q + d) % kCluster;
           bulk_copy_to_peer(map_to_cta(slot_addr, c), my_slot, kSlotBytes, map_to_cta(bar_addr, c));
         }
-        // the local chunk is in place; the expected bytes are the three chunks the peers push
-        mbar_arrive_expect_tx(&bar->h_ready, (kCluster - 1) * kSlotBytes);
+        mbar_arrive(&bar->h_ready[sl]);      // the local copy is in place
         DITTO_STAMP(i, 8);
       }
     }
