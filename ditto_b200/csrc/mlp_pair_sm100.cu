@@ -49,7 +49,8 @@ constexpr int kStageBytes = 24 * 1024;
 constexpr int kStages = 4;
 constexpr int kSets = 2;              // a chunk is exchanged and consumed as two 64-column halves
 constexpr int kSlotBytes = kRows * (kChunk / kSets) * 2;   // one half chunk: a 128-row x 128-byte atom, 16 KB
-constexpr int kThreads = 224;
+constexpr int kThreads = 256;
+constexpr uint32_t kProducers = 2;      // TMA-issuing threads (warps 4 and 7), alternate ring stages
 constexpr int kOffSlots = 0;
 constexpr int kOffRing = kOffSlots + kSets * kPairs * kSlotBytes;
 constexpr int kOffBar = kOffRing + kStages * kStageBytes;
@@ -139,9 +140,11 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const uint32_t tmem_y = tmem_base;
   const uint32_t tmem_h = tmem_base + 256;
 
-  if (warp == 4) {
-    // ------------------------------------------------------------ TMA producer (one thread)
+  if (warp == 4 || warp == 7) {
+    // ------------------------------------------------------------ TMA producers (one thread each, alternate stages)
     if (lane == 0) {
+      const uint32_t pw = warp == 4 ? 0u : 1u;
+      uint32_t cnt = 0;
       tma_prefetch_desc(&p.map_x);
       tma_prefetch_desc(&p.map_w1);
       tma_prefetch_desc(&p.map_w2);
@@ -151,6 +154,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       uint32_t full_addr = 0;             // the leader's full[ps] as a cluster address
       // `pair_bytes`: what both CTAs of the pair put into the stage (armed by the leader only)
       auto acquire = [&](uint32_t pair_bytes, uint32_t code) -> uint8_t* {
+        if ((cnt++ & (kProducers - 1)) != pw) return nullptr;
         ok = mbar_wait(&bar->empty[ps], pph ^ 1, abort_word, code);
         if (!ok) return nullptr;
         if (half == 0) mbar_arrive_expect_tx(&bar->full[ps], pair_bytes);
@@ -164,12 +168,13 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         const int g = i * kPairs + static_cast<int>(pair);
         for (int ks = 0; ks < ksteps1 && ok; ++ks) {
           uint8_t* dst = acquire(2 * (16384 + 8192), 0x100 + i);
-          if (!ok) break;
-          tma_load_2d_pair(dst, &p.map_x, full_addr, ks * 64, b * p.M + row0);
-          if (p.w_oi)
-            tma_load_2d_pair(dst + 16384, &p.map_w1, full_addr, ks * 64, b * p.L + g * kChunk + half * 64);
-          else
-            tma_load_2d_pair(dst + 16384, &p.map_w1, full_addr, g * kChunk + half * 64, b * p.K + ks * 64);
+          if (dst != nullptr) {
+            tma_load_2d_pair(dst, &p.map_x, full_addr, ks * 64, b * p.M + row0);
+            if (p.w_oi)
+              tma_load_2d_pair(dst + 16384, &p.map_w1, full_addr, ks * 64, b * p.L + g * kChunk + half * 64);
+            else
+              tma_load_2d_pair(dst + 16384, &p.map_w1, full_addr, g * kChunk + half * 64, b * p.K + ks * 64);
+          }
           advance();
         }
       };
@@ -178,13 +183,14 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           for (int c = 0; c < kPairs && ok; ++c) {
             const int g = i * kPairs + c;
             uint8_t* dst = acquire(2 * 64 * NH * 2, 0x200 + i);
-            if (!ok) break;
-            if (p.w_oi) {
-              tma_load_2d_pair(dst, &p.map_w2, full_addr, g * kChunk + kk * 64, b * p.N + pair * NS + half * NH);
-            } else {
-              for (int a = 0; a < NH / 64; ++a)
-                tma_load_2d_pair(dst + a * 8192, &p.map_w2, full_addr, pair * NS + half * NH + a * 64,
-                                 b * p.L + g * kChunk + kk * 64);
+            if (dst != nullptr) {
+              if (p.w_oi) {
+                tma_load_2d_pair(dst, &p.map_w2, full_addr, g * kChunk + kk * 64, b * p.N + pair * NS + half * NH);
+              } else {
+                for (int a = 0; a < NH / 64; ++a)
+                  tma_load_2d_pair(dst + a * 8192, &p.map_w2, full_addr, pair * NS + half * NH + a * 64,
+                                   b * p.L + g * kChunk + kk * 64);
+              }
             }
             advance();
           }
