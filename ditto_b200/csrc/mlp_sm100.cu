@@ -19,11 +19,14 @@
 //
 // Warp roles (256 threads): warps 0-3 epilogue (thread r <-> row r / TMEM lane r), warps 4 and 7 TMA
 // producers (alternate ring stages), warp 5 MMA issuer (converged, one elected lane issues),
-// warp 6 relay (tells all four CTAs when this CTA has finished reading a round of hidden chunks).
+// warp 6 relay (after this CTA's GEMM2 has finished with a slot, tells the CTA that fills it next).
 //
-// Per round i (four chunks, one per CTA) on each CTA's tensor pipe:
-//   GEMM1(own chunk of round i+1)  |  GEMM2(4 chunks of round i)
-// and the epilogue warps drain GEMM1's accumulator (two TMEM buffers, ping-pong) while GEMM2 runs.
+// Hand-over of hidden chunks: in units of 64 columns (16 KB), six unit slots per CTA; unit u goes to
+// slot u % 6 of all four CTAs.  The owner refills a slot as soon as all four CTAs have consumed the
+// previous unit in it (slot_free, count 4), so the copy of unit u + 6 runs under GEMM2 of units
+// u + 1 .. u + 5.  Tensor-pipe order on every CTA: GEMM1 of its first two chunks, then per unit
+//   GEMM2(unit u)  |  an eighth of GEMM1 of the own chunk two rounds ahead
+// while the epilogue warps drain GEMM1's accumulator (two TMEM buffers, ping-pong).
 #include "mlp_sm100.cuh"
 
 #include <cuda.h>
@@ -47,8 +50,8 @@
 #define DITTO_STAMP(i, k) do {} while (0)
 #endif
 
-#ifndef DITTO_MLP_SLOTS
-#define DITTO_MLP_SLOTS 3
+#ifndef DITTO_MLP_UNITS
+#define DITTO_MLP_UNITS 6
 #endif
 
 namespace ditto_b200 {
@@ -59,18 +62,20 @@ constexpr int kCluster = 4;
 constexpr int kRows = 128;            // rows of X / Y per cluster
 constexpr int kChunk = 128;           // hidden columns per chunk
 constexpr int kStageBytes = 32 * 1024;
-constexpr int kSlotBytes = kRows * kChunk * 2;   // one hidden chunk, 16-bit: 32 KB
-// Shared memory holds kSlots hidden-chunk slots and a kStages-deep operand ring, 7 x 32 KB together.
-// Chunk n (owner CTA n % 4) lives in slot n % kSlots; a slot is handed on chunk by chunk, so the
-// exchange of chunk n + kSlots overlaps GEMM2 on the chunks in between.
-constexpr int kSlots = DITTO_MLP_SLOTS;
-constexpr int kStages = 7 - kSlots;
+// Hidden chunks travel and are consumed in units of 64 columns (128 rows x 64 x 16 bit = 16 KB, one
+// swizzle atom column = one GEMM2 k-step group).  Unit u = 2 * chunk + half lives in slot u % kUnits of
+// every CTA; a slot is handed on unit by unit, so the exchange of unit u + kUnits overlaps GEMM2 on the
+// units in between.  Small units keep the hand-over loop (GEMM2 done everywhere -> owner refills ->
+// copies land) short relative to the work that hides it.  Slots and operand ring share 224 KB.
+constexpr int kUnitBytes = kRows * 64 * 2;
+constexpr int kUnits = DITTO_MLP_UNITS;
+constexpr int kStages = (14 - kUnits) / 2;
 constexpr int kThreads = 256;
 constexpr uint32_t kProducers = 2;         // TMA-issuing threads (warps 4 and 7)
 constexpr int kOffSlots = 0;
-constexpr int kOffRing = kOffSlots + kSlots * kSlotBytes;
+constexpr int kOffRing = kOffSlots + kUnits * kUnitBytes;
 constexpr int kOffBar = kOffRing + kStages * kStageBytes;
-constexpr int kSmemBytes = kOffBar + 256 + 1024;
+constexpr int kSmemBytes = kOffBar + 512 + 1024;
 
 struct MlpParams {
   CUtensorMap map_x;   // X  [batch*M, K], box 64 x 128
@@ -90,15 +95,15 @@ struct MlpParams {
 struct Bars {
   uint64_t full[kStages], empty[kStages];
   uint64_t h_tmem_full[2], h_tmem_empty[2];
-  uint64_t h_ready[kSlots];    // the chunk of the slot's current use is present (own: local arrive; peer's: pushed bytes)
-  uint64_t g2_done[kSlots];    // this CTA's GEMM2 has finished reading the slot
-  uint64_t slot_free[kSlots];  // all four CTAs have (count 4, remote arrivals); kept at the CTA that writes the slot next
+  uint64_t h_ready[kUnits];    // the unit of the slot's current use is present (own: local arrive; peer's: pushed bytes)
+  uint64_t g2_done[kUnits];    // this CTA's GEMM2 has finished reading the slot
+  uint64_t slot_free[kUnits];  // all four CTAs have (count 4, remote arrivals); kept at the CTA that writes the slot next
   uint64_t y_done;
   uint64_t epi_sync;     // the 128 epilogue threads, once per round (bounded, unlike bar.sync)
   uint32_t tmem_base;
   uint32_t abort_word;
 };
-static_assert(sizeof(Bars) <= 256, "barrier block too large");
+static_assert(sizeof(Bars) <= 512, "barrier block too large");
 
 }  // namespace
 
@@ -140,6 +145,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const int NS = p.N / kCluster;          // this CTA's Y columns
   const int rounds = p.L / (kCluster * kChunk);
   const int chunks = rounds * kCluster;   // hidden chunks in all; this CTA owns chunk 4 i + q of round i
+  const int units = 2 * chunks;           // 64-column halves of them
   const int ksteps1 = p.K / 64;
 
   if (threadIdx.x == 0) {
@@ -151,7 +157,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       mbar_init(&bar->h_tmem_full[i], 1);
       mbar_init(&bar->h_tmem_empty[i], kRows);
     }
-    for (int i = 0; i < kSlots; ++i) {
+    for (int i = 0; i < kUnits; ++i) {
       mbar_init(&bar->h_ready[i], 1);
       mbar_init(&bar->g2_done[i], 1);
       mbar_init(&bar->slot_free[i], kCluster);
@@ -214,29 +220,28 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           advance();
         }
       };
-      auto load_g2 = [&](int g) {         // this CTA's W2 slice for hidden chunk g
-        for (int kk = 0; kk < 2 && ok; ++kk) {
-          uint8_t* dst = acquire(64 * NS * 2, 0x200 + (g >> 2));
-          if (dst != nullptr) {
-            if (p.w_oi) {
-              tma_load_2d(dst, &p.map_w2, &bar->full[ps], g * kChunk + kk * 64, b * p.N + q * NS);
-            } else if (p.w_atoms) {
-              tma_load_3d(dst, &p.map_w2, &bar->full[ps], 0, b * p.L + g * kChunk + kk * 64, q * (NS / 64));
-            } else {
-              for (int a = 0; a < NS / 64; ++a)
-                tma_load_2d(dst + a * 8192, &p.map_w2, &bar->full[ps], q * NS + a * 64, b * p.L + g * kChunk + kk * 64);
-            }
+      auto load_g2 = [&](int u) {         // this CTA's W2 slice for hidden unit u (64 hidden columns)
+        const int g = u >> 1, kk = u & 1;
+        uint8_t* dst = acquire(64 * NS * 2, 0x200 + (g >> 2));
+        if (dst != nullptr) {
+          if (p.w_oi) {
+            tma_load_2d(dst, &p.map_w2, &bar->full[ps], g * kChunk + kk * 64, b * p.N + q * NS);
+          } else if (p.w_atoms) {
+            tma_load_3d(dst, &p.map_w2, &bar->full[ps], 0, b * p.L + g * kChunk + kk * 64, q * (NS / 64));
+          } else {
+            for (int a = 0; a < NS / 64; ++a)
+              tma_load_2d(dst + a * 8192, &p.map_w2, &bar->full[ps], q * NS + a * 64, b * p.L + g * kChunk + kk * 64);
           }
-          advance();
         }
+        advance();
       };
       // the order the MMA warp consumes the ring in: see there
       load_g1(0, 0, ksteps1);
       if (rounds > 1) load_g1(1, 0, ksteps1);
-      for (int n = 0; n < chunks && ok; ++n) {
-        const int i = n >> 2, c = n & 3;
-        load_g2(n);
-        if (i + 2 < rounds) load_g1(i + 2, c * ksteps1 / 4, (c + 1) * ksteps1 / 4);
+      for (int u = 0; u < units && ok; ++u) {
+        const int i = u >> 3, e = u & 7;
+        load_g2(u);
+        if (i + 2 < rounds) load_g1(i + 2, e * ksteps1 / 8, (e + 1) * ksteps1 / 8);
       }
     }
   } else if (warp == 5) {
@@ -280,51 +285,51 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       if (last && ok) umma_commit_elected(&bar->h_tmem_full[hb], issuer);
       if (last && lane == 0) DITTO_STAMP(i, 1);
     };
-    // GEMM2 on hidden chunk g (any CTA's), accumulated into Y
-    auto g2 = [&](int g) {
-      const int sl = g % kSlots;
-      if ((g & 3) != static_cast<int>(q) && lane == 0)
-        mbar_arrive_expect_tx(&bar->h_ready[sl], kSlotBytes);   // a peer pushes this chunk; the owner's own copy arrives locally
+    // GEMM2 on hidden unit u (64 hidden columns of any CTA's chunk), accumulated into Y
+    auto g2 = [&](int u) {
+      const int sl = u % kUnits;
+      const int owner = (u >> 1) & 3;
+      if (owner != static_cast<int>(q) && lane == 0)
+        mbar_arrive_expect_tx(&bar->h_ready[sl], kUnitBytes);   // a peer pushes this unit; the owner's own copy arrives locally
       __syncwarp();
-      if (lane == 0 && (g & 3) == 0) DITTO_STAMP(g >> 2, 2);
-      ok = wait(&bar->h_ready[sl], (g / kSlots) & 1, 0x400 + (g >> 2));
-      if (lane == 0) DITTO_STAMP(g >> 2, 9 + (g & 3));
-      for (int kk = 0; kk < 2 && ok; ++kk) {
-        ok = wait(&bar->full[cs], cph, 0x410 + (g >> 2));
-        if (!ok) break;
+      if (lane == 0 && (u & 7) == 0) DITTO_STAMP(u >> 3, 2);
+      ok = wait(&bar->h_ready[sl], (u / kUnits) & 1, 0x400 + (u >> 3));
+      if (lane == 0 && (u & 1) == 0) DITTO_STAMP(u >> 3, 9 + ((u >> 1) & 3));
+      if (ok) ok = wait(&bar->full[cs], cph, 0x410 + (u >> 3));
+      if (ok) {
         const uint32_t st = ring + cs * kStageBytes;
-        const uint64_t da = umma_desc_sw128(slots + sl * kSlotBytes + kk * 16384, 16, 1024);
+        const uint64_t da = umma_desc_sw128(slots + sl * kUnitBytes, 16, 1024);
         const uint64_t db = p.w_oi ? umma_desc_sw128(st, 16, 1024) : umma_desc_sw128(st, 8192, 1024);
 #pragma unroll
         for (int s4 = 0; s4 < 4; ++s4) {
           const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
-          umma_ss_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (g | kk | s4) ? 1u : 0u, issuer);
+          umma_ss_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (u | s4) ? 1u : 0u, issuer);
         }
         umma_commit_elected(&bar->empty[cs], issuer);
         advance();
+        umma_commit_elected(&bar->g2_done[sl], issuer);
       }
-      if (ok) umma_commit_elected(&bar->g2_done[sl], issuer);
-      if (lane == 0 && (g & 3) == 3) DITTO_STAMP(g >> 2, 4);
+      if (lane == 0 && (u & 7) == 7) DITTO_STAMP(u >> 3, 4);
     };
-    // Tensor-pipe order: GEMM1 of the first two own chunks, then chunk by chunk GEMM2(chunk n) followed by a
-    // quarter of GEMM1 of the own chunk two rounds ahead, so that a chunk that arrives late stalls little.
+    // Tensor-pipe order: GEMM1 of the first two own chunks, then unit by unit GEMM2(unit u) followed by an
+    // eighth of GEMM1 of the own chunk two rounds ahead, so that a unit that arrives late stalls little.
     g1(0, 0, ksteps1, true, true);
     if (rounds > 1 && ok) g1(1, 0, ksteps1, true, true);
-    for (int n = 0; n < chunks && ok; ++n) {
-      const int i = n >> 2, c = n & 3;
-      g2(n);
-      if (i + 2 < rounds && ok) g1(i + 2, c * ksteps1 / 4, (c + 1) * ksteps1 / 4, c == 0, c == 3);
+    for (int u = 0; u < units && ok; ++u) {
+      const int i = u >> 3, e = u & 7;
+      g2(u);
+      if (i + 2 < rounds && ok) g1(i + 2, e * ksteps1 / 8, (e + 1) * ksteps1 / 8, e == 0, e == 7);
     }
     if (ok) umma_commit_elected(&bar->y_done, issuer);
   } else if (warp == 6) {
     // ------------------------------------------------------------ relay (one thread)
     if (lane == 0) {
-      for (int n = 0; n < chunks; ++n) {
-        const int sl = n % kSlots;
-        if (!mbar_wait(&bar->g2_done[sl], (n / kSlots) & 1, abort_word, 0x500 + (n >> 2))) break;
-        if ((n & 3) == 3) DITTO_STAMP(n >> 2, 5);
-        // tell the CTA that writes this slot next (the owner of chunk n + kSlots)
-        if (n + kSlots < chunks) mbar_arrive_cluster(&bar->slot_free[sl], static_cast<uint32_t>((n + kSlots) & 3));
+      for (int u = 0; u < units; ++u) {
+        const int sl = u % kUnits;
+        if (!mbar_wait(&bar->g2_done[sl], (u / kUnits) & 1, abort_word, 0x500 + (u >> 3))) break;
+        if ((u & 7) == 7) DITTO_STAMP(u >> 3, 5);
+        // tell the CTA that writes this slot next (the owner of unit u + kUnits)
+        if (u + kUnits < units) mbar_arrive_cluster(&bar->slot_free[sl], static_cast<uint32_t>(((u + kUnits) >> 1) & 3));
       }
     }
   } else if (warp < 4) {
@@ -332,12 +337,10 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     const int row = warp * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     bool ok = true;
-    uint32_t free_waits[kSlots] = {};       // completed waits per slot: the parity of the next one
+    uint32_t free_waits[kUnits] = {};       // completed waits per slot: the parity of the next one
     for (int i = 0; i < rounds; ++i) {
       const int hb = i & 1;
       const int g = i * kCluster + static_cast<int>(q);   // this CTA's chunk of the round
-      const int sl = g % kSlots;
-      uint8_t* my_slot = smem + kOffSlots + sl * kSlotBytes;
       ok = mbar_wait(&bar->h_tmem_full[hb], (i >> 1) & 1, abort_word, 0x600 + i);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -361,37 +364,46 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         }
         pk[j] = pack2<BF16>(apply_act(v0, p.act1), apply_act(v1, p.act1));
       }
-      if (g >= kSlots) {
-        // every CTA of the cluster has finished GEMM2 on the slot's previous chunk: it may be overwritten
-        uint32_t par = 0;
+      // the chunk leaves as two units of 64 columns
 #pragma unroll
-        for (int t = 0; t < kSlots; ++t)
-          if (t == sl) par = free_waits[t]++ & 1;
-        ok = mbar_wait_cluster(&bar->slot_free[sl], par, abort_word, 0x700 + i);
+      for (int kk = 0; kk < 2; ++kk) {
+        const int u = 2 * g + kk;
+        const int sl = u % kUnits;
+        uint8_t* my_slot = smem + kOffSlots + sl * kUnitBytes;
+        if (u >= kUnits) {
+          // every CTA of the cluster has finished GEMM2 on the slot's previous unit: it may be overwritten
+          uint32_t par = 0;
+#pragma unroll
+          for (int t = 0; t < kUnits; ++t)
+            if (t == sl) par = free_waits[t]++ & 1;
+          ok = mbar_wait_cluster(&bar->slot_free[sl], par, abort_word, 0x700 + i);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        if (threadIdx.x == 0 && kk == 0) DITTO_STAMP(i, 7);
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+          const int ch = kk * 8 + c8;
+          const uint4 v = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+          *reinterpret_cast<uint4*>(my_slot + row * 128 + ((c8 ^ (row & 7)) << 4)) = v;
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bar->epi_sync);                        // all 128 rows of the unit are written
+        ok = mbar_wait(&bar->epi_sync, kk, abort_word, 0x780 + i);   // two phases per round
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-      }
-      if (threadIdx.x == 0) DITTO_STAMP(i, 7);
-#pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        const uint4 v = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-        *reinterpret_cast<uint4*>(my_slot + (ch >> 3) * 16384 + row * 128 + (((ch & 7) ^ (row & 7)) << 4)) = v;
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(&bar->epi_sync);                        // all 128 rows of the chunk are written
-      ok = mbar_wait(&bar->epi_sync, i & 1, abort_word, 0x780 + i);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (threadIdx.x == 0) {
-        const uint32_t slot_addr = smem_u32(my_slot);
-        const uint32_t bar_addr = smem_u32(&bar->h_ready[sl]);
-        for (uint32_t d = 1; d < kCluster; ++d) {
-          const uint32_t c = (q + d) % kCluster;
-          bulk_copy_to_peer(map_to_cta(slot_addr, c), my_slot, kSlotBytes, map_to_cta(bar_addr, c));
+        if (threadIdx.x == 0) {
+          const uint32_t slot_addr = smem_u32(my_slot);
+          const uint32_t bar_addr = smem_u32(&bar->h_ready[sl]);
+          for (uint32_t d = 1; d < kCluster; ++d) {
+            const uint32_t c = (q + d) % kCluster;
+            bulk_copy_to_peer(map_to_cta(slot_addr, c), my_slot, kUnitBytes, map_to_cta(bar_addr, c));
+          }
+          mbar_arrive(&bar->h_ready[sl]);      // the local copy is in place
+          if (kk == 1) DITTO_STAMP(i, 8);
         }
-        mbar_arrive(&bar->h_ready[sl]);      // the local copy is in place
-        DITTO_STAMP(i, 8);
       }
+      if (!ok) break;
     }
     if (ok) {
       ok = mbar_wait(&bar->y_done, 0, abort_word, 0x800);
