@@ -37,7 +37,7 @@ L2_BYTES = 126 * 1024 * 1024
 NCU_TRAFFIC_BYTES_PER_UNIT = {
     "cfg5": (201.488e6 + 47.643e6) / 128,   # profiles/attention_bf16_d128_cfg5.md: 128-slice capture
     "cfg3": (101.050e6 + 11.025e6) / 512,   # profiles/attention_fp16_d64_cfg3.md: full launch
-    "cfg4": (50.441e6 + 2.819e6) / 128,     # profiles/mlp_bf16_cfg4.md: full launch (128 row blocks)
+    "cfg4": (50.457e6 + 2.913e6) / 128,     # profiles/mlp_bf16_cfg4.md: full launch (128 row blocks)
 }
 
 
