@@ -22,7 +22,8 @@ _LIB = None
 
 
 def available():
-    return build_ref.build() is not None
+    """The library exists (built here or shipped prebuilt) and this host can execute its AVX2 + FMA code."""
+    return {"avx2", "fma"} <= build_ref.host_flags() and build_ref.build() is not None
 
 
 def lib():
@@ -36,7 +37,8 @@ def lib():
 
 
 def has_exp():
-    return hasattr(lib(), "ref_exp_6x16_compute_exp")
+    """The exponential kernels are AVX-512: built only on such a host, and only callable on one."""
+    return "avx512f" in build_ref.host_flags() and hasattr(lib(), "ref_exp_6x16_compute_exp")
 
 
 def _fp(a):
