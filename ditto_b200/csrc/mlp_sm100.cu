@@ -78,7 +78,7 @@ constexpr int kOffBar = kOffRing + kStages * kStageBytes;
 constexpr int kSmemBytes = kOffBar + 512 + 1024;
 
 struct MlpParams {
-  CUtensorMap map_x;   // X  [batch*M, K], box 64 x 128
+  CUtensorMap map_x;   // X  [batch, M, K] (3-D: a partial last row block is zero-filled), box 64 x 128 x 1
   CUtensorMap map_w1;  // IO: W1 [batch*K, L], box 64 x 64;  OI: W1 [batch*L, K], box 64 x 128
   CUtensorMap map_w2;  // IO: W2 [batch*L, N], box 64 x 64;  OI: W2 [batch*N, L], box 64 x N/4
   void* y;             // Y  [batch, M, N]
@@ -207,7 +207,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         for (int ks = ks0; ks < ks1 && ok; ++ks) {
           uint8_t* dst = acquire(2 * 16384, 0x100 + i);
           if (dst != nullptr) {
-            tma_load_2d(dst, &p.map_x, &bar->full[ps], ks * 64, b * p.M + row0);
+            tma_load_3d(dst, &p.map_x, &bar->full[ps], ks * 64, row0, b);
             if (p.w_oi) {
               tma_load_2d(dst + 16384, &p.map_w1, &bar->full[ps], ks * 64, b * p.L + g * kChunk);
             } else if (p.w_atoms) {
@@ -430,9 +430,11 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           }
           w[j] = pack2<BF16>(apply_act(v0, p.act2), apply_act(v1, p.act2));
         }
+        if (row0 + row < p.M) {               // rows >= M of a partial last block were computed on zero-filled X
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(yrow + cc * 2 + j * 16) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(yrow + cc * 2 + j * 16) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        }
       }
     }
   }
@@ -476,6 +478,26 @@ bool mlp_make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// [batch, rows, cols] row-major, boxes of box_cols x box_rows inside one batch entry: rows past the end of
+// an entry are zero-filled instead of running into the next entry.
+bool mlp_make_map_3d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint64_t batch,
+                     uint32_t box_cols, uint32_t box_rows) {
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return false;
+  EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  const cuuint64_t dims[3] = {cols, rows, batch};
+  const cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
+  const cuuint32_t box[3] = {box_cols, box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // [rows, cols] row-major seen as (64 columns, rows, cols / 64): one box of 64 x box_rows x box_atoms
 // brings box_atoms 64-column swizzle atoms of an MN-major operand tile with a single TMA operation
 // (atom a lands at a * box_rows * 128 bytes, exactly the operand layout).
@@ -508,15 +530,16 @@ int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int
     return launch_mlp_pair(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, epilogue & 0xff, status, stream, trace);
   }
   epilogue &= 0xff;
-  // Coverage of the cluster kernel: 128-row blocks; hidden size a multiple of 4 chunks of 128;
-  // N/4 Y columns per CTA (<= 256 TMEM columns, whole 64-column swizzle atoms); K in 64-wide steps.
-  if (M % kRows || L % (kCluster * kChunk) || K % 64) return DITTO_ERR_UNSUPPORTED;
+  // Coverage of the cluster kernel: 128-row blocks (the last one may be partial); hidden size a multiple
+  // of 4 chunks of 128; N/4 Y columns per CTA (<= 256 TMEM columns, whole 64-column swizzle atoms);
+  // K in 64-wide steps.
+  if (L % (kCluster * kChunk) || K % 64) return DITTO_ERR_UNSUPPORTED;
   if (N % (kCluster * 64) || N > kCluster * 256) return DITTO_ERR_UNSUPPORTED;
   if (batch > 65535) return DITTO_ERR_UNSUPPORTED;
   const int NS = N / kCluster;
   MlpParams p;
   std::memset(&p, 0, sizeof(p));
-  bool ok = mlp_make_map(&p.map_x, bf16, x, K, static_cast<uint64_t>(batch) * M, 64, 128);
+  bool ok = mlp_make_map_3d(&p.map_x, bf16, x, K, M, batch, 64, 128);
   if (w_layout == 1) {
     ok = ok && mlp_make_map(&p.map_w1, bf16, w1, K, static_cast<uint64_t>(batch) * L, 64, 128);
     ok = ok && mlp_make_map(&p.map_w2, bf16, w2, L, static_cast<uint64_t>(batch) * N, 64, NS);
@@ -542,7 +565,7 @@ int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int
   p.b2 = b2;
   p.status = status;
   p.trace = trace;
-  dim3 grid(kCluster * (M / kRows), batch, 1);
+  dim3 grid(kCluster * ((M + kRows - 1) / kRows), batch, 1);
   cudaError_t e;
   if (bf16) {
     e = cudaFuncSetAttribute(mlp_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);

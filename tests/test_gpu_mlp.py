@@ -53,7 +53,9 @@ def test_parity_small(cuda, oracle, dtype, act, layout, pair):
     # L = 4096 gives eight rounds: every hidden-chunk slot and barrier phase wraps several times
     shapes = ((2, 256, 512, 128, 1024), (1, 512, 1024, 256, 1536), (1, 256, 512, 64, 4096))
     if not pair:
-        shapes += ((1, 128, 256, 64, 512), (1, 128, 1024, 192, 512), (3, 384, 768, 960, 2048))
+        # the last two: row counts that are not multiples of the 128-row block (208 tokens, a 16-row call)
+        shapes += ((1, 128, 256, 64, 512), (1, 128, 1024, 192, 512), (3, 384, 768, 960, 2048),
+                   (2, 208, 768, 768, 1024), (1, 16, 256, 64, 512))
     for (batch, M, N, K, L) in shapes:
         x, w1, w2 = _inputs(21, batch, M, N, K, L, dtype)
         got = _run(cuda, x, w1, w2, dtype, act, layout, pair)
