@@ -32,6 +32,7 @@ EXPORTS = (
     "ditto_b200_workspace_bytes",
     "ditto_b200_selftest_umma",
     "ditto_b200_selftest_umma_pair",
+    "ditto_b200_selftest_wait_limit",
     "ditto_b200_strerror",
     "ditto_b200_last_cuda_error",
     "ditto_b200_version",
@@ -82,6 +83,8 @@ def load():
     lib.ditto_b200_selftest_umma.restype = i
     lib.ditto_b200_selftest_umma_pair.argtypes = [vp, vp, vp, i, i, i, i, vp, vp]
     lib.ditto_b200_selftest_umma_pair.restype = i
+    lib.ditto_b200_selftest_wait_limit.argtypes = [i, vp, vp]
+    lib.ditto_b200_selftest_wait_limit.restype = i
     lib.ditto_b200_strerror.argtypes = [i]
     lib.ditto_b200_strerror.restype = ctypes.c_char_p
     lib.ditto_b200_last_cuda_error.argtypes = []

@@ -332,6 +332,13 @@ int ditto_b200_selftest_umma_pair(const void* a, const void* b, float* c, int N,
   return DITTO_OK;
 }
 
+int ditto_b200_selftest_wait_limit(int code, int* status_word, void* stream) {
+  if (code <= 0 || status_word == nullptr) return DITTO_ERR_INVALID_ARG;
+  cudaError_t e = ditto_b200::launch_wait_limit_selftest(code, status_word, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("selftest_wait_limit launch", e);
+  return DITTO_OK;
+}
+
 const char* ditto_b200_strerror(int code) {
   switch (code) {
     case DITTO_OK: return "ok";

@@ -223,3 +223,35 @@ cudaError_t launch_umma_pair_selftest(const SelftestParams& p, cudaStream_t stre
 }
 
 }  // namespace ditto_b200
+
+// ------------------------------------------------------------------ bounded-wait self test
+// The failure path every kernel of the library relies on, run on purpose and harmlessly: a barrier
+// that is never signalled, the shared bounded wait, the abort word, the host-visible status word.
+namespace ditto_b200 {
+
+__global__ void __launch_bounds__(64, 1) wait_limit_selftest_kernel(int code, int* status) {
+  __shared__ uint64_t never;
+  __shared__ uint32_t abort_word_storage;
+  volatile uint32_t* abort_word = &abort_word_storage;
+  if (threadIdx.x == 0) {
+    mbar_init(&never, 1);
+    abort_word_storage = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = mbar_wait(&never, 0, abort_word, static_cast<uint32_t>(code));   // gives up at the limit
+  // the other waiter sees the abort word the first one set and returns at once, as the kernels' warps do
+  __syncthreads();
+  if (threadIdx.x == 32) ok = mbar_wait(&never, 0, abort_word, 0x7fffffffu);
+  __syncthreads();
+  if (threadIdx.x == 0 && status != nullptr && abort_word_storage != 0) atomicCAS(status, 0, static_cast<int>(abort_word_storage));
+  (void)ok;
+}
+
+cudaError_t launch_wait_limit_selftest(int code, int* status, cudaStream_t stream) {
+  wait_limit_selftest_kernel<<<1, 64, 0, stream>>>(code, status);
+  return cudaGetLastError();
+}
+
+}  // namespace ditto_b200

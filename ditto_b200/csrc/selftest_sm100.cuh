@@ -19,4 +19,7 @@ cudaError_t launch_umma_selftest(const SelftestParams& p, cudaStream_t stream);
 // CTA-pair variant: A has 256 rows (box 64 x 128 per CTA), B boxes cover half of N.
 cudaError_t launch_umma_pair_selftest(const SelftestParams& p, cudaStream_t stream);
 
+// One CTA runs the library's bounded wait on a barrier nobody signals and reports `code` through `status`.
+cudaError_t launch_wait_limit_selftest(int code, int* status, cudaStream_t stream);
+
 }  // namespace ditto_b200

@@ -109,6 +109,12 @@ int ditto_b200_selftest_umma(const void* a, const void* b, float* c, int N, int 
 int ditto_b200_selftest_umma_pair(const void* a, const void* b, float* c, int N, int K, int dtype, int b_mn,
                                   int* status_word, void* stream);
 
+/* Exercises the failure path of the device-side waits without faulting anything: one CTA waits, with the
+ * same bounded wait every kernel here uses, on a barrier that nothing ever signals; when the limit is
+ * reached the wait gives up, the kernel writes `code` to *status_word and ends normally, and the context
+ * stays usable.  Takes about a second.  No counterpart in the reference. */
+int ditto_b200_selftest_wait_limit(int code, int* status_word, void* stream);
+
 const char* ditto_b200_strerror(int code);
 /* Text of the last CUDA / driver error seen by the calling thread ("" if none). */
 const char* ditto_b200_last_cuda_error(void);

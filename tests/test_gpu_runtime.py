@@ -7,6 +7,7 @@ import torch
 import ditto_b200 as ditto
 from ditto_b200 import auto_compute as ac, auto_tensorize as at, hardware as hw, ops, runtime
 from ditto_b200 import workloads as W
+from ditto_b200 import _lib
 from tests.tolerances import assert_close
 
 pytestmark = pytest.mark.gpu
@@ -80,3 +81,23 @@ def test_graph_engine_runs_the_attention_layer(cuda, oracle, factory):
     assert 0 < ms < 5
     with pytest.raises(AttributeError):
         engine.get_function("no_such_function")
+
+
+def test_expired_wait_is_reported_not_fatal(cuda):
+    """The failure path of the device-side waits, exercised without faulting anything: a CTA waits (with the
+    bounded wait all kernels share) on a barrier nobody signals; at the limit the wait gives up, the code
+    lands in the status word, the kernel ends normally -- and the context keeps working: the next fused
+    call on the same device is correct and leaves the status word clean."""
+    lib = _lib.load()
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    with torch.cuda.device(cuda):
+        rc = lib.ditto_b200_selftest_wait_limit(0x6A1, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize(cuda)
+    assert int(status.item()) == 0x6A1
+    assert lib.ditto_b200_selftest_wait_limit(0, status.data_ptr(), None) == _lib.ERR_INVALID_ARG
+    q = (torch.rand(2, 256, 64, device=cuda) - 0.5).half()
+    out = ops.bmm_softmax_bmm(q, q, q, scale=1.0, key_layout="LK")
+    assert ops.device_status(cuda) == 0
+    ref = torch.softmax(q.float() @ q.float().transpose(1, 2), -1) @ q.float()
+    assert (out.float() - ref).abs().max().item() < 2e-3
