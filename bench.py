@@ -35,9 +35,9 @@ L2_BYTES = 126 * 1024 * 1024
 # (dram__bytes_read.sum + dram__bytes_write.sum, scaled by the number of units when the capture
 # ran a smaller launch of the same kernel).  None = not captured yet.
 NCU_TRAFFIC_BYTES_PER_UNIT = {
-    "cfg5": (201.488e6 + 47.643e6) / 128,   # profiles/attention_bf16_d128_cfg5.md: 128-slice capture
-    "cfg3": (101.050e6 + 11.025e6) / 512,   # profiles/attention_fp16_d64_cfg3.md: full launch
-    "cfg4": (50.457e6 + 2.913e6) / 128,     # profiles/mlp_bf16_cfg4.md: full launch (128 row blocks)
+    "cfg5": (201.488e6 + 47.643e6) / 128,   # ncu capture of the first 128 slices (summary under profiles/)
+    "cfg3": (101.050e6 + 11.025e6) / 512,   # ncu capture of a full launch (summary under profiles/)
+    "cfg4": (50.457e6 + 2.913e6) / 128,     # ncu capture of a full launch, 128 row blocks (summary under profiles/)
 }
 
 

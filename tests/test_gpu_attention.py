@@ -114,7 +114,7 @@ def test_golden_vectors(cuda, case):
 
 
 def test_cfg2_full(cuda, oracle):
-    """BASELINE config 2 at full size: 12 slices, S = 512, d = 64, fp16, scale 1/8, both key layouts."""
+    """Benchmark configuration 2 at full size: 12 slices, S = 512, d = 64, fp16, scale 1/8, both key layouts."""
     w = W.WORKLOADS["cfg2"]
     q, k, v = W.attention_inputs(w, 0, w.batch)
     want = _oracle(oracle, q, k, v, w.dtype, w.scale)

@@ -74,7 +74,7 @@ def test_golden_vector(cuda):
 
 
 def test_cfg4_sampled_row_blocks(cuda, oracle):
-    """BASELINE config 4 at full size (X[16384,1024], W1[1024,4096], W2[4096,1024], bf16): seeded
+    """Benchmark configuration 4 at full size (X[16384,1024], W1[1024,4096], W2[4096,1024], bf16): seeded
     row blocks (first, last and the shard boundaries of 2/4/8 GPUs) are placed at their index, the
     rest of X is unrelated random data, and those blocks are compared with the oracle."""
     w = W.WORKLOADS["cfg4"]
@@ -151,7 +151,7 @@ def test_small_n_golden_and_cfg1_shape(cuda, oracle):
     assert ops.device_status(cuda) == 0
     stored = np.load(os.path.join(GOLDEN, case + ".npz"))["chain_fp32"]
     assert_close(out.float().cpu().numpy(), stored, w.dtype, case, scale=float(np.abs(stored).max()))
-    # BASELINE config 1's shape (A[8,512,64] B[8,64,512] D[8,512,64], U(-1,1)) in fp16 on the GPU; the
+    # benchmark configuration 1's shape (A[8,512,64] B[8,64,512] D[8,512,64], U(-1,1)) in fp16 on the GPU; the
     # fp32 CPU case itself is checked in tests/test_oracle.py
     cfg1 = W.WORKLOADS["cfg1"]
     a, b, c = (W._round(t, "float16") for t in W.chain_inputs(cfg1))

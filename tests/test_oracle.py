@@ -130,7 +130,7 @@ def test_ffn_c_matches_numpy(oracle):
 
 
 def test_cfg1_cpu_case(oracle):
-    """BASELINE config 1: E = (A B) D in fp32, A[8,512,64] B[8,64,512] D[8,512,64] ~ U(-1,1)."""
+    """Benchmark configuration 1: E = (A B) D in fp32, A[8,512,64] B[8,64,512] D[8,512,64] ~ U(-1,1)."""
     w = W.WORKLOADS["cfg1"]
     A, B, C = W.chain_inputs(w)
     want = np.einsum("bml,bln->bmn", np.einsum("bmk,bkl->bml", A.astype(np.float64), B.astype(np.float64)), C.astype(np.float64))
