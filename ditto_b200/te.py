@@ -8,7 +8,7 @@ objects: they carry names, shapes, dtypes and iteration variables, but no expres
 the arithmetic of every supported chain is fixed by its kernel.
 """
 from dataclasses import dataclass, field
-from typing import List, Optional, Tuple
+from typing import List, Tuple
 
 _DTYPES = ("float16", "bfloat16", "float32")
 

@@ -11,7 +11,6 @@ They are slow (one ctypes call per 6 x 16 tile) and meant for small shapes: thei
 golden vectors under tests/golden/ that pin the C restatement in chain_oracle.c.
 """
 import ctypes
-import os
 
 import numpy as np
 
