@@ -143,9 +143,10 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const int row0 = (blockIdx.x / kCluster) * kRows;
   const int b = blockIdx.y;
   const int NS = p.N / kCluster;          // this CTA's Y columns
-  const int rounds = p.L / (kCluster * kChunk);
-  const int chunks = rounds * kCluster;   // hidden chunks in all; this CTA owns chunk 4 i + q of round i
+  const int chunks = p.L / kChunk;        // hidden chunks in all (any count); chunk n belongs to CTA n % 4
   const int units = 2 * chunks;           // 64-column halves of them
+  // this CTA owns chunk 4 i + q for i < rounds: one round fewer than its peers if the last round is partial
+  const int rounds = (chunks - static_cast<int>(q) + kCluster - 1) / kCluster;
   const int ksteps1 = p.K / 64;
 
   if (threadIdx.x == 0) {
@@ -236,7 +237,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         advance();
       };
       // the order the MMA warp consumes the ring in: see there
-      load_g1(0, 0, ksteps1);
+      if (rounds > 0) load_g1(0, 0, ksteps1);
       if (rounds > 1) load_g1(1, 0, ksteps1);
       for (int u = 0; u < units && ok; ++u) {
         const int i = u >> 3, e = u & 7;
@@ -313,7 +314,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     };
     // Tensor-pipe order: GEMM1 of the first two own chunks, then unit by unit GEMM2(unit u) followed by an
     // eighth of GEMM1 of the own chunk two rounds ahead, so that a unit that arrives late stalls little.
-    g1(0, 0, ksteps1, true, true);
+    if (rounds > 0) g1(0, 0, ksteps1, true, true);
     if (rounds > 1 && ok) g1(1, 0, ksteps1, true, true);
     for (int u = 0; u < units && ok; ++u) {
       const int i = u >> 3, e = u & 7;
@@ -531,9 +532,9 @@ int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int
   }
   epilogue &= 0xff;
   // Coverage of the cluster kernel: 128-row blocks (the last one may be partial); hidden size a multiple
-  // of 4 chunks of 128; N/4 Y columns per CTA (<= 256 TMEM columns, whole 64-column swizzle atoms);
-  // K in 64-wide steps.
-  if (L % (kCluster * kChunk) || K % 64) return DITTO_ERR_UNSUPPORTED;
+  // of the 128-wide chunk (the last round of four chunks may be partial); N/4 Y columns per CTA
+  // (<= 256 TMEM columns, whole 64-column swizzle atoms); K in 64-wide steps.
+  if (L % kChunk || K % 64) return DITTO_ERR_UNSUPPORTED;
   if (N % (kCluster * 64) || N > kCluster * 256) return DITTO_ERR_UNSUPPORTED;
   if (batch > 65535) return DITTO_ERR_UNSUPPORTED;
   const int NS = N / kCluster;

@@ -88,7 +88,7 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
  * nn/functional/activation.py:29-39).
  *   b1 [batch, L], b2 [batch, N]: bias vectors in the input type, either may be NULL
  *   act1 / act2: 0 identity, 1 ReLU, 2 GELU (tanh form)
- * Shapes as for the large-N form of ditto_b200_gemm_relu_gemm (K % 64, L % 512 == 0, N in {256, 512, 768, 1024},
+ * Shapes as for the large-N form of ditto_b200_gemm_relu_gemm (K % 64, L % 128 == 0, N in {256, 512, 768, 1024},
  * M any multiple of 16). */
 int ditto_b200_ffn(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, void* y, int batch,
                    int M, int N, int K, int L, int dtype, int w_layout, int act1, int act2, int* status_word,

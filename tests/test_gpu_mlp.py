@@ -55,7 +55,10 @@ def test_parity_small(cuda, oracle, dtype, act, layout, pair):
     if not pair:
         # the last two: row counts that are not multiples of the 128-row block (208 tokens, a 16-row call)
         shapes += ((1, 128, 256, 64, 512), (1, 128, 1024, 192, 512), (3, 384, 768, 960, 2048),
-                   (2, 208, 768, 768, 1024), (1, 16, 256, 64, 512))
+                   (2, 208, 768, 768, 1024), (1, 16, 256, 64, 512),
+                   # hidden sizes that are not multiples of four chunks: the last round is partial, with fewer
+                   # than four chunks in all some CTAs own none
+                   (1, 256, 512, 128, 768), (2, 128, 256, 64, 128), (1, 384, 1024, 192, 1664))
     for (batch, M, N, K, L) in shapes:
         x, w1, w2 = _inputs(21, batch, M, N, K, L, dtype)
         got = _run(cuda, x, w1, w2, dtype, act, layout, pair)
@@ -119,8 +122,8 @@ def test_full_size_properties(cuda):
 
 def test_unsupported_shapes_raise(cuda):
     x = torch.zeros(128, 64, dtype=torch.bfloat16, device=cuda)
-    w1 = torch.zeros(64, 256, dtype=torch.bfloat16, device=cuda)   # hidden 256 is not a multiple of 512
-    w2 = torch.zeros(256, 256, dtype=torch.bfloat16, device=cuda)
+    w1 = torch.zeros(64, 192, dtype=torch.bfloat16, device=cuda)   # hidden 192 is not a multiple of 128
+    w2 = torch.zeros(192, 256, dtype=torch.bfloat16, device=cuda)
     with pytest.raises(_lib.DittoError) as e:
         ops.gemm_relu_gemm(x, w1, w2)
     assert e.value.code == _lib.ERR_UNSUPPORTED
