@@ -38,7 +38,7 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 }
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word,
                                                   uint32_t code) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+  for (uint32_t spin = 0; spin < (1u << 22); ++spin) {   // unhinted polls: the default limit
     if (mbar_try_wait_cluster(bar, parity)) return true;
     if (*abort_word != 0u) return false;
     if (spin > 4096u) __nanosleep(64);

@@ -27,6 +27,7 @@
 // u + 1 .. u + 5.  Tensor-pipe order on every CTA: GEMM1 of its first two chunks, then per unit
 //   GEMM2(unit u)  |  an eighth of GEMM1 of the own chunk two rounds ahead
 // while the epilogue warps drain GEMM1's accumulator (two TMEM buffers, ping-pong).
+#define DITTO_TRY_WAIT_HINT_NS 5000   // see mbar_try_wait
 #include "mlp_sm100.cuh"
 
 #include <cuda.h>

@@ -43,8 +43,22 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta)
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(cta));
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
 }
+// A translation unit may define DITTO_TRY_WAIT_HINT_NS before including this header: its polls then
+// carry the optional suspend-time hint of mbarrier.try_wait (the thread may stay suspended that long
+// before the poll returns false).  The MLP chain kernel does: its waits are long and many, and fewer
+// wake-ups of the waiting warps leave more issue slots to the working ones (+3 % measured); the
+// attention kernels and the CTA-pair kernel lose 1-5 % with it and keep the default.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
+#ifdef DITTO_TRY_WAIT_HINT_NS
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(static_cast<uint32_t>(DITTO_TRY_WAIT_HINT_NS))
+      : "memory");
+#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -52,10 +66,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
+#endif
   return ok != 0;
 }
 
-constexpr uint32_t kSpinLimit = 1u << 22;  // polls; with back-off this is well under a second
+// polls before a bounded wait gives up: about a second either way (a hinted poll may take the hint's time)
+#ifdef DITTO_TRY_WAIT_HINT_NS
+constexpr uint32_t kSpinLimit = 1u << 18;
+#else
+constexpr uint32_t kSpinLimit = 1u << 22;
+#endif
 
 // Bounded wait.  `abort_word` lives in shared memory; `code` identifies the
 // waiter so a timeout can be traced from the host-visible status word.
