@@ -37,7 +37,7 @@ L2_BYTES = 126 * 1024 * 1024
 NCU_TRAFFIC_BYTES_PER_UNIT = {
     "cfg5": (201.488e6 + 47.643e6) / 128,   # ncu capture of the first 128 slices (summary under profiles/)
     "cfg3": (101.050e6 + 11.025e6) / 512,   # ncu capture of a full launch (summary under profiles/)
-    "cfg4": (50.457e6 + 2.913e6) / 128,     # ncu capture of a full launch, 128 row blocks (summary under profiles/)
+    "cfg4": (50.477e6 + 3.117e6) / 128,     # ncu capture of a full launch, 128 row blocks (summary under profiles/)
 }
 
 
