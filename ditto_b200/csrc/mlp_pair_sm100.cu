@@ -13,12 +13,16 @@
 //   * TMA: each CTA loads its own X rows and its half of W1 / W2 tiles; byte counts go to the
 //     pair leader's `full` barrier (cp.async.bulk.tensor ... cta_group::2, no multicast).
 //   * MMA: only the leader's warp 5 issues; commits are delivered to both CTAs of the pair.
-//   * Hidden chunks: CTA (p, h) drains its 128 rows of the chunk from its TMEM, writes slot p of
-//     its own shared memory and pushes it to the CTAs (p', h) of the other pairs.
-//   * A pair's GEMM2 may start when both CTAs hold the round's four chunks: each CTA's relay
-//     thread forwards its `h_ready` to the leader's `h_pair` barrier.
-//   * Slots may be overwritten when all four pairs have finished the round's GEMM2: each CTA's
-//     relay thread tells the four CTAs of its half.
+//   * Hidden chunks travel in units of 64 columns (16 KB per CTA); unit u = 2 chunk + half lives in slot
+//     u % 6 of every CTA.  CTA (p, h) drains its 128 rows of its pair's chunk from TMEM, writes the two
+//     units into its own slots and pushes them to the CTAs (p', h) of the other pairs.
+//   * Each CTA's ready-relay thread takes the units in order, arms the slot's barrier for units a peer
+//     pushes, waits until the unit is present and tells the pair leader (h_pair, 2 arrivals): the pair's
+//     GEMM2 on a unit needs it in both CTAs.
+//   * A slot may be refilled when all four pairs have finished GEMM2 on the unit in it: each CTA's
+//     free-relay thread forwards the leader's g2_done to the CTA of its half that writes the slot next.
+//   * Tensor-pipe order on the leader: GEMM1 of the pair's first two chunks, then per unit
+//     GEMM2(unit) | an eighth of GEMM1 of the chunk two rounds ahead.
 #include <cuda.h>
 
 #include <cstring>
@@ -46,15 +50,15 @@ constexpr int kPairs = 4;
 constexpr int kRows = 128;            // rows per CTA (256 per pair / cluster)
 constexpr int kChunk = 128;           // hidden columns per chunk
 constexpr int kStageBytes = 24 * 1024;
-constexpr int kStages = 4;
-constexpr int kSets = 2;              // a chunk is exchanged and consumed as two 64-column halves
-constexpr int kSlotBytes = kRows * (kChunk / kSets) * 2;   // one half chunk: a 128-row x 128-byte atom, 16 KB
-constexpr int kThreads = 256;
+constexpr int kUnitBytes = kRows * 64 * 2;   // 64 hidden columns of this CTA's 128 rows: one 128-byte-row atom, 16 KB
+constexpr int kUnits = 6;                   // unit slots per CTA
+constexpr int kStages = 5;
+constexpr int kThreads = 288;
 constexpr uint32_t kProducers = 2;      // TMA-issuing threads (warps 4 and 7), alternate ring stages
 constexpr int kOffSlots = 0;
-constexpr int kOffRing = kOffSlots + kSets * kPairs * kSlotBytes;
+constexpr int kOffRing = kOffSlots + kUnits * kUnitBytes;
 constexpr int kOffBar = kOffRing + kStages * kStageBytes;
-constexpr int kSmemBytes = kOffBar + 256 + 1024;
+constexpr int kSmemBytes = kOffBar + 512 + 1024;
 
 struct PairParams {
   CUtensorMap map_x;   // X  [batch*M, K], box 64 x 128
@@ -73,17 +77,16 @@ struct PairBars {
   uint64_t empty[kStages];     // each CTA: the pair's MMAs have finished with the stage
   uint64_t h_tmem_full[2];     // each CTA: GEMM1 of the chunk is in TMEM
   uint64_t h_tmem_empty[2];    // leader: both CTAs' epilogues have read the TMEM buffer (8 warp arrivals)
-  // one of each per half-chunk set: the exchange of one set overlaps GEMM2 on the other
-  uint64_t h_ready[kSets];     // each CTA: the round's four half chunks are in this CTA's slots
-  uint64_t h_pair[kSets];      // leader: ... in both CTAs' slots (2 arrivals)
-  uint64_t g2_done[kSets];     // each CTA: the pair's GEMM2 over the set has finished
-  uint64_t slots_free[kSets];  // each CTA: all four pairs have (4 arrivals)
+  uint64_t h_ready[kUnits];    // each CTA: the unit of the slot's current use is present (own: local arrive; peer's: pushed bytes)
+  uint64_t h_pair[kUnits];     // leader: ... in both CTAs of the pair (2 arrivals)
+  uint64_t g2_done[kUnits];    // each CTA: the pair's GEMM2 has finished reading the slot
+  uint64_t slot_free[kUnits];  // all four pairs have (4 arrivals); kept at the CTA that writes the slot next
   uint64_t y_done;
   uint64_t epi_sync;
   uint32_t tmem_base;
   uint32_t abort_word;
 };
-static_assert(sizeof(PairBars) <= 256, "barrier block too large");
+static_assert(sizeof(PairBars) <= 512, "barrier block too large");
 
 }  // namespace
 
@@ -106,6 +109,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const int NS = p.N / kPairs;            // the pair's Y columns
   const int NH = NS / 2;                  // this CTA's share of the W2 tile's N extent
   const int rounds = p.L / (kPairs * kChunk);
+  const int units = 2 * kPairs * rounds;  // 64-column units of hidden chunks in all
   const int ksteps1 = p.K / 64;
 
   if (threadIdx.x == 0) {
@@ -117,11 +121,11 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       mbar_init(&bar->h_tmem_full[i], 1);
       mbar_init(&bar->h_tmem_empty[i], 8);
     }
-    for (int x = 0; x < kSets; ++x) {
+    for (int x = 0; x < kUnits; ++x) {
       mbar_init(&bar->h_ready[x], 1);
       mbar_init(&bar->h_pair[x], 2);
       mbar_init(&bar->g2_done[x], 1);
-      mbar_init(&bar->slots_free[x], kPairs);
+      mbar_init(&bar->slot_free[x], kPairs);
     }
     mbar_init(&bar->y_done, 1);
     mbar_init(&bar->epi_sync, kRows);
@@ -164,9 +168,9 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       auto advance = [&]() {
         if (++ps == kStages) { ps = 0; pph ^= 1; }
       };
-      auto load_g1 = [&](int i) {         // X rows of this CTA and its half of the W1 chunk tile
+      auto load_g1 = [&](int i, int ks0, int ks1) {   // X rows of this CTA and its half of the W1 chunk tile, k-steps [ks0, ks1)
         const int g = i * kPairs + static_cast<int>(pair);
-        for (int ks = 0; ks < ksteps1 && ok; ++ks) {
+        for (int ks = ks0; ks < ks1 && ok; ++ks) {
           uint8_t* dst = acquire(2 * (16384 + 8192), 0x100 + i);
           if (dst != nullptr) {
             tma_load_2d_pair(dst, &p.map_x, full_addr, ks * 64, b * p.M + row0);
@@ -178,29 +182,27 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           advance();
         }
       };
-      auto load_g2 = [&](int i) {         // this CTA's half of the pair's W2 slice: set by set, four chunks each
-        for (int kk = 0; kk < kSets && ok; ++kk) {
-          for (int c = 0; c < kPairs && ok; ++c) {
-            const int g = i * kPairs + c;
-            uint8_t* dst = acquire(2 * 64 * NH * 2, 0x200 + i);
-            if (dst != nullptr) {
-              if (p.w_oi) {
-                tma_load_2d_pair(dst, &p.map_w2, full_addr, g * kChunk + kk * 64, b * p.N + pair * NS + half * NH);
-              } else {
-                for (int a = 0; a < NH / 64; ++a)
-                  tma_load_2d_pair(dst + a * 8192, &p.map_w2, full_addr, pair * NS + half * NH + a * 64,
-                                   b * p.L + g * kChunk + kk * 64);
-              }
-            }
-            advance();
+      auto load_g2 = [&](int u) {         // this CTA's half of the pair's W2 slice for hidden unit u
+        const int g = u >> 1, kk = u & 1;
+        uint8_t* dst = acquire(2 * 64 * NH * 2, 0x200 + (u >> 3));
+        if (dst != nullptr) {
+          if (p.w_oi) {
+            tma_load_2d_pair(dst, &p.map_w2, full_addr, g * kChunk + kk * 64, b * p.N + pair * NS + half * NH);
+          } else {
+            for (int a = 0; a < NH / 64; ++a)
+              tma_load_2d_pair(dst + a * 8192, &p.map_w2, full_addr, pair * NS + half * NH + a * 64,
+                               b * p.L + g * kChunk + kk * 64);
           }
         }
+        advance();
       };
-      load_g1(0);
-      if (rounds > 1) load_g1(1);
-      for (int i = 0; i < rounds && ok; ++i) {
-        load_g2(i);
-        if (i + 2 < rounds) load_g1(i + 2);
+      // the order the leader's MMA warp consumes the ring in
+      load_g1(0, 0, ksteps1);
+      if (rounds > 1) load_g1(1, 0, ksteps1);
+      for (int u = 0; u < units && ok; ++u) {
+        const int i = u >> 3, e = u & 7;
+        load_g2(u);
+        if (i + 2 < rounds) load_g1(i + 2, e * ksteps1 / 8, (e + 1) * ksteps1 / 8);
       }
     }
   } else if (warp == 5) {
@@ -230,11 +232,11 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       auto advance = [&]() {
         if (++cs == kStages) { cs = 0; cph ^= 1; }
       };
-      auto g1 = [&](int i) {
+      auto g1 = [&](int i, int ks0, int ks1, bool first, bool last) {
         const int hb = i & 1;
-        if (i >= 2) ok = wait_cluster(&bar->h_tmem_empty[hb], ((i >> 1) - 1) & 1, 0x300 + i);
-        if (lane == 0) DITTO_STAMP(i, 0);
-        for (int ks = 0; ks < ksteps1 && ok; ++ks) {
+        if (first && i >= 2) ok = wait_cluster(&bar->h_tmem_empty[hb], ((i >> 1) - 1) & 1, 0x300 + i);
+        if (first && lane == 0) DITTO_STAMP(i, 0);
+        for (int ks = ks0; ks < ks1 && ok; ++ks) {
           ok = wait(&bar->full[cs], cph, 0x310 + i);
           if (!ok) break;
           const uint32_t st = ring + cs * kStageBytes;
@@ -249,53 +251,60 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           umma_commit_pair_elected(&bar->empty[cs], pair_mask, issuer);
           advance();
         }
-        if (ok) umma_commit_pair_elected(&bar->h_tmem_full[hb], pair_mask, issuer);
-        if (lane == 0) DITTO_STAMP(i, 1);
+        if (last && ok) umma_commit_pair_elected(&bar->h_tmem_full[hb], pair_mask, issuer);
+        if (last && lane == 0) DITTO_STAMP(i, 1);
       };
-      auto g2 = [&](int i) {
-        for (int x = 0; x < kSets && ok; ++x) {
-          if (lane == 0) DITTO_STAMP(i, 2 + 8 * x);
-          ok = wait_cluster(&bar->h_pair[x], i & 1, 0x400 + i);
-          if (lane == 0) DITTO_STAMP(i, 3 + 8 * x);
-          for (int c = 0; c < kPairs && ok; ++c) {
-            ok = wait(&bar->full[cs], cph, 0x410 + i);
-            if (!ok) break;
-            const uint32_t st = ring + cs * kStageBytes;
-            const uint64_t da = umma_desc_sw128(slots + (x * kPairs + c) * kSlotBytes, 16, 1024);
-            const uint64_t db = p.w_oi ? umma_desc_sw128(st, 16, 1024) : umma_desc_sw128(st, 8192, 1024);
+      auto g2 = [&](int u) {              // GEMM2 on hidden unit u: needs it in both CTAs' slots
+        const int sl = u % kUnits;
+        if (lane == 0 && (u & 7) == 0) DITTO_STAMP(u >> 3, 2);
+        ok = wait_cluster(&bar->h_pair[sl], (u / kUnits) & 1, 0x400 + (u >> 3));
+        if (lane == 0 && (u & 7) == 0) DITTO_STAMP(u >> 3, 3);
+        if (ok) ok = wait(&bar->full[cs], cph, 0x410 + (u >> 3));
+        if (ok) {
+          const uint32_t st = ring + cs * kStageBytes;
+          const uint64_t da = umma_desc_sw128(slots + sl * kUnitBytes, 16, 1024);
+          const uint64_t db = p.w_oi ? umma_desc_sw128(st, 16, 1024) : umma_desc_sw128(st, 8192, 1024);
 #pragma unroll
-            for (int s4 = 0; s4 < 4; ++s4) {
-              const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
-              umma_ss_pair_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (i | x | c | s4) ? 1u : 0u,
-                                   issuer);
-            }
-            umma_commit_pair_elected(&bar->empty[cs], pair_mask, issuer);
-            advance();
+          for (int s4 = 0; s4 < 4; ++s4) {
+            const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
+            umma_ss_pair_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (u | s4) ? 1u : 0u, issuer);
           }
-          if (ok) umma_commit_pair_elected(&bar->g2_done[x], pair_mask, issuer);
-          if (lane == 0) DITTO_STAMP(i, 4 + 8 * x);
+          umma_commit_pair_elected(&bar->empty[cs], pair_mask, issuer);
+          advance();
+          umma_commit_pair_elected(&bar->g2_done[sl], pair_mask, issuer);
         }
+        if (lane == 0 && (u & 7) == 7) DITTO_STAMP(u >> 3, 4);
       };
-      g1(0);
-      if (rounds > 1 && ok) g1(1);
-      for (int i = 0; i < rounds && ok; ++i) {
-        g2(i);
-        if (i + 2 < rounds && ok) g1(i + 2);
+      g1(0, 0, ksteps1, true, true);
+      if (rounds > 1 && ok) g1(1, 0, ksteps1, true, true);
+      for (int u = 0; u < units && ok; ++u) {
+        const int i = u >> 3, e = u & 7;
+        g2(u);
+        if (i + 2 < rounds && ok) g1(i + 2, e * ksteps1 / 8, (e + 1) * ksteps1 / 8, e == 0, e == 7);
       }
       if (ok) umma_commit_pair_elected(&bar->y_done, pair_mask, issuer);
     }
   } else if (warp == 6) {
-    // ------------------------------------------------------------ relay (one thread per set)
-    if (lane < kSets) {
-      const int x = lane;
-      for (int i = 0; i < rounds; ++i) {
-        // this CTA holds the round's four half chunks of the set -> tell the pair leader
-        if (!mbar_wait_cluster(&bar->h_ready[x], i & 1, abort_word, 0x500 + i)) break;
-        mbar_arrive_cluster(&bar->h_pair[x], leader);
-        // the pair has finished reading the set's slots -> tell the four CTAs of this half
-        if (!mbar_wait(&bar->g2_done[x], i & 1, abort_word, 0x580 + i)) break;
-        if (x == 0) DITTO_STAMP(i, 5);
-        for (uint32_t c = 0; c < kPairs; ++c) mbar_arrive_cluster(&bar->slots_free[x], 2 * c + half);
+    // ------------------------------------------------------------ ready relay (one thread)
+    if (lane == 0) {
+      for (int u = 0; u < units; ++u) {
+        const int sl = u % kUnits;
+        // a peer pushes this unit: arm the slot's barrier for its bytes (the own pair's units arrive locally)
+        if (static_cast<uint32_t>((u >> 1) & 3) != pair) mbar_arrive_expect_tx(&bar->h_ready[sl], kUnitBytes);
+        if (!mbar_wait(&bar->h_ready[sl], (u / kUnits) & 1, abort_word, 0x500 + (u >> 3))) break;
+        mbar_arrive_cluster(&bar->h_pair[sl], leader);
+      }
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------ free relay (one thread)
+    if (lane == 0) {
+      for (int u = 0; u < units; ++u) {
+        const int sl = u % kUnits;
+        if (!mbar_wait(&bar->g2_done[sl], (u / kUnits) & 1, abort_word, 0x580 + (u >> 3))) break;
+        if ((u & 7) == 7) DITTO_STAMP(u >> 3, 5);
+        // tell the CTA of this half that writes the slot next (the pair that owns unit u + kUnits)
+        if (u + kUnits < units)
+          mbar_arrive_cluster(&bar->slot_free[sl], 2 * static_cast<uint32_t>(((u + kUnits) >> 1) & 3) + half);
       }
     }
   } else if (warp < 4) {
@@ -303,6 +312,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     const int row = warp * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     bool ok = true;
+    uint32_t free_waits[kUnits] = {};       // completed waits per slot: the parity of the next one
     for (int i = 0; i < rounds; ++i) {
       const int hb = i & 1;
       ok = mbar_wait(&bar->h_tmem_full[hb], (i >> 1) & 1, abort_word, 0x600 + i);
@@ -325,37 +335,43 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         }
         pk[j] = pack2<BF16>(v0, v1);
       }
+      const int g = i * kPairs + static_cast<int>(pair);   // this pair's chunk of the round
 #pragma unroll
-      for (int x = 0; x < kSets; ++x) {
-        if (i > 0) {
-          // every pair has finished GEMM2 over this set in the previous round: its slots may be overwritten
-          ok = mbar_wait_cluster(&bar->slots_free[x], (i - 1) & 1, abort_word, 0x700 + i);
+      for (int kk = 0; kk < 2; ++kk) {
+        const int u = 2 * g + kk;
+        const int sl = u % kUnits;
+        if (u >= kUnits) {
+          // every pair has finished GEMM2 on the slot's previous unit: it may be overwritten
+          uint32_t par = 0;
+#pragma unroll
+          for (int t = 0; t < kUnits; ++t)
+            if (t == sl) par = free_waits[t]++ & 1;
+          ok = mbar_wait_cluster(&bar->slot_free[sl], par, abort_word, 0x700 + i);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
         }
-        if (threadIdx.x == 0 && x == 0) DITTO_STAMP(i, 7);
-        uint8_t* slot = smem + kOffSlots + (x * kPairs + pair) * kSlotBytes;
+        if (threadIdx.x == 0 && kk == 0) DITTO_STAMP(i, 7);
+        uint8_t* slot = smem + kOffSlots + sl * kUnitBytes;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
-          const int w = x * 32 + 4 * ch;
+          const int w = kk * 32 + 4 * ch;
           const uint4 v = make_uint4(pk[w], pk[w + 1], pk[w + 2], pk[w + 3]);
           *reinterpret_cast<uint4*>(slot + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
         }
         fence_proxy_async_smem();
         mbar_arrive(&bar->epi_sync);
-        ok = mbar_wait(&bar->epi_sync, (2 * i + x) & 1, abort_word, 0x780 + i);
+        ok = mbar_wait(&bar->epi_sync, kk, abort_word, 0x780 + i);   // two phases per round
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (threadIdx.x == 0) {
           const uint32_t slot_addr = smem_u32(slot);
-          const uint32_t bar_addr = smem_u32(&bar->h_ready[x]);
+          const uint32_t bar_addr = smem_u32(&bar->h_ready[sl]);
           for (uint32_t d = 1; d < kPairs; ++d) {
-            // same rows, other pairs; rotated so the senders do not all hit the same destination first
-            const uint32_t peer = 2 * ((pair + d) % kPairs) + half;
-            bulk_copy_to_peer(map_to_cta(slot_addr, peer), slot, kSlotBytes, map_to_cta(bar_addr, peer));
+            const uint32_t peer = 2 * ((pair + d) % kPairs) + half;   // same rows, other pairs
+            bulk_copy_to_peer(map_to_cta(slot_addr, peer), slot, kUnitBytes, map_to_cta(bar_addr, peer));
           }
-          mbar_arrive_expect_tx(&bar->h_ready[x], (kPairs - 1) * kSlotBytes);
-          if (x == 0) DITTO_STAMP(i, 8);
+          mbar_arrive(&bar->h_ready[sl]);    // the local copy is in place
+          if (kk == 1) DITTO_STAMP(i, 8);
         }
       }
       if (!ok) break;
