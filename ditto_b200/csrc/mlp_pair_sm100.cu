@@ -51,8 +51,14 @@ constexpr int kRows = 128;            // rows per CTA (256 per pair / cluster)
 constexpr int kChunk = 128;           // hidden columns per chunk
 constexpr int kStageBytes = 24 * 1024;
 constexpr int kUnitBytes = kRows * 64 * 2;   // 64 hidden columns of this CTA's 128 rows: one 128-byte-row atom, 16 KB
-constexpr int kUnits = 6;                   // unit slots per CTA
-constexpr int kStages = 5;
+#ifndef DITTO_PAIR_UNITS
+#define DITTO_PAIR_UNITS 6
+#endif
+#ifndef DITTO_PAIR_STAGES
+#define DITTO_PAIR_STAGES 5
+#endif
+constexpr int kUnits = DITTO_PAIR_UNITS;    // unit slots per CTA
+constexpr int kStages = DITTO_PAIR_STAGES;
 constexpr int kThreads = 288;
 constexpr uint32_t kProducers = 2;      // TMA-issuing threads (warps 4 and 7), alternate ring stages
 constexpr int kOffSlots = 0;
