@@ -55,6 +55,9 @@ def parse_args():
     ap.add_argument("--also", default="cfg4,cfg3,cfg2",
                     help="at 1 GPU, also time these workloads kernel-only and list them under other_workloads ('' = none)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the baseline sample")
+    ap.add_argument("--shape-table", action="store_true",
+                    help="instead of the benchmark: time both chains on the reference's own benchmark shapes (1 GPU, "
+                         "fp16, inputs resident, L2 flushed between launches) and print one JSON line")
     return ap.parse_args()
 
 
@@ -356,8 +359,57 @@ def reference_arm(args, w):
 
 
 # ---------------------------------------------------------------------------- main
+# The shape table of the reference's GPU benchmarks, (batch, M, N, K, L)
+# (benchmark/chimera/cuda/bmm_softmax_bmm_cuda.py:294-308, bmm_bmm_cuda.py:304-321; 196 tokens are rounded up
+# to 208 and 49 to 64 there as well).
+REFERENCE_SHAPES = [
+    ("Bert-Small", 8, 512, 64, 64, 512), ("Bert-Base", 12, 512, 64, 64, 512), ("Bert-Large", 16, 512, 64, 64, 512),
+    ("ViT-Base/14", 12, 256, 64, 64, 256), ("ViT-Large/14", 16, 256, 64, 64, 256), ("ViT-Huge/14", 16, 256, 80, 80, 256),
+    ("ViT-Base/16", 12, 208, 64, 64, 208), ("ViT-Large/16", 16, 208, 64, 64, 208), ("ViT-Huge/16", 16, 208, 80, 80, 208),
+    ("Mixer-Small/32-S", 1, 512, 64, 64, 256), ("Mixer-Base/32-S", 1, 768, 64, 64, 384), ("Mixer-Large/32-S", 1, 1024, 64, 64, 512),
+]
+
+
+def shape_table(steps):
+    """Both chains on the reference's benchmark shapes: device time per launch, L2 flushed between launches."""
+    import torch
+    from ditto_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    g = torch.Generator(device=dev).manual_seed(11)
+    rows = []
+    for name, b, M, N, K, L in REFERENCE_SHAPES:
+        a = (torch.rand(b, M, K, device=dev, generator=g) * 2 - 1).half()      # U(-1, 1) like the reference's inputs
+        bm = (torch.rand(b, K, L, device=dev, generator=g) * 2 - 1).half()     # the reference's [batch, K, L] layout
+        c = (torch.rand(b, L, N, device=dev, generator=g) * 2 - 1).half()
+        out = torch.empty(b, M, N, dtype=torch.float16, device=dev)
+        entry = {"shape": name, "batch_M_N_K_L": [b, M, N, K, L]}
+        for chain, call in (("bmm_softmax_bmm", lambda: ops.bmm_softmax_bmm(a, bm, c, out=out, scale=K ** -0.5, key_layout="KL")),
+                            ("bmm_bmm", lambda: ops.gemm_relu_gemm(a, bm, c, out=out, activation="identity"))):
+            for _ in range(3):
+                call()
+            total = 0.0
+            for _ in range(steps):
+                flush.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                call()
+                e1.record()
+                e1.synchronize()
+                total += e0.elapsed_time(e1)
+            us = total / steps * 1e3
+            entry[chain] = {"us": round(us, 2), "tflops": round(2.0 * b * M * L * (K + N) / us / 1e6, 2)}
+        entry["device_status"] = ops.device_status(dev)
+        rows.append(entry)
+    print(json.dumps({"table": "reference benchmark shapes, fp16, one B200", "steps": steps, "rows": rows}))
+
+
 def main():
     args = parse_args()
+    if args.shape_table:
+        shape_table(max(args.steps, 1))
+        return
     from ditto_b200 import workloads as W
     if args.workload not in W.WORKLOADS:
         raise SystemExit(f"unknown workload {args.workload}; choose from {sorted(W.WORKLOADS)}")
