@@ -74,8 +74,36 @@ int make_map_2d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, ui
 // 3-D tensor [slices, rows, cols] of 16-bit elements: coordinates (col, row, slice), boxes of
 // box_cols x box_rows x 1.  Rows beyond `rows` inside a slice are out of bounds and read as zero,
 // which is what makes partial tiles at the end of a sequence safe.
+// A tensor map is a pure function of these arguments, and callers with pre-allocated buffers (the
+// reference's calling convention) present the same ones call after call: the last few encodings are
+// kept per thread, which takes the three driver calls out of a repeated launch.
+struct MapKey {
+  const void* base;
+  uint64_t cols, rows, slices, row_stride, slice_stride;
+  uint32_t box_cols, box_rows, bf16;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && cols == o.cols && rows == o.rows && slices == o.slices && row_stride == o.row_stride &&
+           slice_stride == o.slice_stride && box_cols == o.box_cols && box_rows == o.box_rows && bf16 == o.bf16;
+  }
+};
+struct MapCache {
+  static constexpr int kEntries = 8;
+  MapKey key[kEntries];
+  CUtensorMap map[kEntries];
+  bool valid[kEntries] = {};
+  int next = 0;
+};
+thread_local MapCache g_map_cache;
+
 int make_map_3d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint64_t slices,
                 uint64_t row_stride_elems, uint64_t slice_stride_elems, uint32_t box_cols, uint32_t box_rows) {
+  const MapKey want{base, cols, rows, slices, row_stride_elems, slice_stride_elems, box_cols, box_rows, bf16 ? 1u : 0u};
+  MapCache& cache = g_map_cache;
+  for (int i = 0; i < MapCache::kEntries; ++i)
+    if (cache.valid[i] && cache.key[i] == want) {
+      *map = cache.map[i];
+      return DITTO_OK;
+    }
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) {
     set_error("cuTensorMapEncodeTiled", "entry point not found");
@@ -94,6 +122,10 @@ int make_map_3d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, ui
     set_error("cuTensorMapEncodeTiled", buf);
     return DITTO_ERR_CUDA;
   }
+  cache.key[cache.next] = want;
+  cache.map[cache.next] = *map;
+  cache.valid[cache.next] = true;
+  cache.next = (cache.next + 1) % MapCache::kEntries;
   return DITTO_OK;
 }
 

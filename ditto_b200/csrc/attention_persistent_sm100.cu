@@ -14,6 +14,8 @@
 // identically.  Every wait is bounded as everywhere else in this library.
 #include "attention_sm100.cuh"
 
+#include <atomic>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -38,6 +40,7 @@ namespace ditto_b200 {
 namespace {
 
 constexpr int kBM = 128, kBN = 128, kD = 64;
+constexpr int kMaxDevices = 64;
 constexpr int kStages = 2;
 constexpr int kTileQ = kBM * kD * 2;     // 16 KB
 constexpr int kTileKV = kBN * kD * 2;    // 16 KB
@@ -396,15 +399,23 @@ __global__ void __launch_bounds__(kThreads, 2) attention_persistent_kernel(const
 template <bool BF16, int MODE>
 static cudaError_t launch_p(const AttnParams& p, long long total_items, cudaStream_t stream) {
   auto kern = attention_persistent_kernel<BF16, MODE>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  // function attributes and the SM count are looked up once per device (this instantiation's statics):
+  // the launches of short sequences are a few microseconds long and every runtime call shows
+  static std::atomic<int> sm_count[kMaxDevices];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-  if (e != cudaSuccess) return e;
-  int dev = 0, sms = 0;
-  e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  int sms = sm_count[dev].load(std::memory_order_acquire);
+  if (sms == 0) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    sm_count[dev].store(sms, std::memory_order_release);
+  }
   const long long slots = 2LL * sms;                 // two CTAs per SM (TMEM: 2 x 256 columns)
   const unsigned grid = static_cast<unsigned>(total_items < slots ? total_items : slots);
   kern<<<grid, kThreads, kSmemBytes, stream>>>(p, static_cast<int>(total_items));

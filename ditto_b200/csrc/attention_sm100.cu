@@ -31,6 +31,8 @@
 // that reads it, and the tensor pipe executes one thread's MMAs in order.
 #include "attention_sm100.cuh"
 
+#include <atomic>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -535,10 +537,19 @@ template <bool BF16, int D, int NT, bool PSMEM, int MODE>
 static cudaError_t launch_one(const AttnParams& p, int batch, cudaStream_t stream) {
   using SM = Smem<D, NT, PSMEM>;
   auto kern = attention_kernel<BF16, D, NT, PSMEM, MODE>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kBytes);
+  // the function attributes are set once per device (this instantiation's static)
+  static std::atomic<unsigned long long> configured{0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!((configured.load(std::memory_order_acquire) >> dev) & 1ull)) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
+    configured.fetch_or(1ull << dev, std::memory_order_release);
+  }
   dim3 grid(static_cast<unsigned>((p.M + NT * kBM - 1) / (NT * kBM)) * static_cast<unsigned>(batch), 1, 1);
   kern<<<grid, threads_for(NT), SM::kBytes, stream>>>(p);
   return cudaGetLastError();

@@ -8,6 +8,24 @@ import torch
 from . import _lib
 
 _DTYPE_CODE = {torch.float16: _lib.DTYPE_FP16, torch.bfloat16: _lib.DTYPE_BF16}
+
+
+class _NoGuard:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def _on_device(device):
+    """Context that makes `device` current for the launch; free when it already is (the common case)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)
 _status_words = {}
 
 # number of kernel launches issued through this module (benchmarks report it)
@@ -75,7 +93,7 @@ def bmm_softmax_bmm(query, key, value, out=None, scale=1.0, key_layout="KL", fla
         if tuple(out.shape) != (batch, M, N):
             raise ValueError(f"out has shape {tuple(out.shape)}, expected {(batch, M, N)}")
     lib = _lib.load()
-    with torch.cuda.device(query.device):
+    with _on_device(query.device):
         stream = torch.cuda.current_stream().cuda_stream
         rc = lib.ditto_b200_bmm_softmax_bmm(query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(),
                                             batch, M, N, K, L, _DTYPE_CODE[query.dtype], klay, float(scale),
@@ -104,7 +122,7 @@ def multi_head_attention(qkv, num_heads, out=None, scale=1.0, flags=0):
         if tuple(out.shape) != (batch, M, hidden):
             raise ValueError(f"out has shape {tuple(out.shape)}, expected {(batch, M, hidden)}")
     lib = _lib.load()
-    with torch.cuda.device(qkv.device):
+    with _on_device(qkv.device):
         stream = torch.cuda.current_stream().cuda_stream
         rc = lib.ditto_b200_multi_head_attention(qkv.data_ptr(), out.data_ptr(), batch, M, num_heads, hidden // num_heads,
                                                  _DTYPE_CODE[qkv.dtype], float(scale), int(flags),
@@ -156,7 +174,7 @@ def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO", p
         if tuple(out3.shape) != (batch, M, N):
             raise ValueError(f"out has shape {tuple(out.shape)}, expected {(batch, M, N)}")
     lib = _lib.load()
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         stream = torch.cuda.current_stream().cuda_stream
         rc = lib.ditto_b200_gemm_relu_gemm(x3.data_ptr(), w13.data_ptr(), w23.data_ptr(), out3.data_ptr(), batch, M, N,
                                            K, L, _DTYPE_CODE[x.dtype], wl,
@@ -211,7 +229,7 @@ def ffn(x, w1, b1, w2, b2, out=None, act1="relu", act2="relu", weight_layout="OI
         if tuple(out3.shape) != (batch, M, N):
             raise ValueError(f"out has shape {tuple(out.shape)}, expected {(batch, M, N)}")
     lib = _lib.load()
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         stream = torch.cuda.current_stream().cuda_stream
         rc = lib.ditto_b200_ffn(x3.data_ptr(), w13.data_ptr(), b1.data_ptr() if b1 is not None else None, w23.data_ptr(),
                                 b2.data_ptr() if b2 is not None else None, out3.data_ptr(), batch, M, N, K, L,

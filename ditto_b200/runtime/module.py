@@ -5,12 +5,13 @@ pre-allocated by the caller, and times it with `func.time_evaluator(func.entry_n
 min_repeat_ms=600)(*args).mean` (benchmark/chimera/cuda/bmm_softmax_bmm_cuda.py:23-42, 239-256).
 ChainModule keeps that calling convention on torch CUDA tensors.
 """
+import weakref
 from dataclasses import dataclass
 from typing import List
 
 import torch
 
-from .. import ops
+from .. import _lib, ops
 from ..auto_tensorize import ChainSchedule
 
 _TORCH_DTYPE = {"float16": torch.float16, "bfloat16": torch.bfloat16}
@@ -28,6 +29,7 @@ class ChainModule:
     def __init__(self, sch: ChainSchedule, name="default_function"):
         self.schedule = sch
         self.entry_name = name
+        self._fast = None
 
     def _check(self, tensors):
         s = self.schedule
@@ -51,16 +53,54 @@ class ChainModule:
                 raise TypeError(f"{nm}: dtype {t.dtype} does not match the compiled dtype {s.dtype}")
 
     def __call__(self, *tensors):
+        # Shapes, dtypes and the argument order are fixed at build time, as in the reference, so a call
+        # with the same tensor objects as the previous one (a benchmark loop, an inference engine with
+        # pre-allocated buffers; held by weak reference) needs no re-validation: it fetches the current pointers and the current
+        # stream and goes straight to the C ABI.  Anything else takes the checked path below once.
+        fast = self._fast
+        if fast is not None and len(tensors) == len(fast[0]) and all(r() is t for r, t in zip(fast[0], tensors)):
+            fn, head, tail, dev_index = fast[1:]
+            if torch.cuda.current_device() == dev_index:
+                rc = fn(*[t.data_ptr() for t in tensors], *head, *tail, torch.cuda.current_stream().cuda_stream)
+                if rc != 0:
+                    _lib.check(rc, self.entry_name)
+                ops.launch_count += 1
+                return
         self._check(tensors)
         s = self.schedule
         if s.kind == "mha":
             ops.multi_head_attention(tensors[0], s.heads, out=tensors[1], scale=s.scale)
-            return
-        a, b, c, f = tensors
-        if s.kind == "softmax":
-            ops.bmm_softmax_bmm(a, b, c, out=f, scale=s.scale, key_layout="KL")
         else:
-            ops.gemm_relu_gemm(a, b, c, out=f, activation="relu" if s.kind == "relu" else "identity")
+            a, b, c, f = tensors
+            if s.kind == "softmax":
+                ops.bmm_softmax_bmm(a, b, c, out=f, scale=s.scale, key_layout="KL")
+            else:
+                ops.gemm_relu_gemm(a, b, c, out=f, activation="relu" if s.kind == "relu" else "identity")
+        self._fast = self._prepare(tensors)
+
+    def _prepare(self, tensors):
+        """Arguments of the C entry point that do not change between calls with these tensor objects
+        (everything but the data pointers and the stream), or None where the checked path must stay."""
+        s = self.schedule
+        if not all(t.is_cuda and t.is_contiguous() for t in tensors):
+            return None
+        dev = tensors[0].device
+        if any(t.device != dev for t in tensors):
+            return None
+        lib = _lib.load()
+        code = ops._DTYPE_CODE[_TORCH_DTYPE[s.dtype]]
+        if s.kind == "softmax":
+            fn = lib.ditto_b200_bmm_softmax_bmm
+            head = (s.batch, s.M, s.N, s.K, s.L, code, 0, float(s.scale), 0, None, 0)
+        elif s.kind == "mha":
+            fn = lib.ditto_b200_multi_head_attention
+            head = (s.batch, s.M, s.heads, s.N // s.heads, code, float(s.scale), 0)
+        else:
+            fn = lib.ditto_b200_gemm_relu_gemm
+            head = (s.batch, s.M, s.N, s.K, s.L, code, 0, 1 if s.kind == "relu" else 0, None, 0)
+        tail = (ops._status_word(dev).data_ptr(),)
+        return (tuple(weakref.ref(t) for t in tensors), fn, head, tail,
+                dev.index if dev.index is not None else torch.cuda.current_device())
 
     def get_function(self, name):
         if name != self.entry_name:
