@@ -120,6 +120,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_persistent_kernel(const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bar->tmem_base;
+  // Programmatic dependent launch: everything above touches no global memory, so it may run while the
+  // kernel ahead of this one in the stream is still finishing; from here on its results are needed.
+  // The kernel behind this one may start its own set-up right away (it waits at the same point).
+  grid_dependency_wait();
+  grid_launch_dependents();
 
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer (one thread)
@@ -418,8 +423,17 @@ static cudaError_t launch_p(const AttnParams& p, long long total_items, cudaStre
   }
   const long long slots = 2LL * sms;                 // two CTAs per SM (TMEM: 2 x 256 columns)
   const unsigned grid = static_cast<unsigned>(total_items < slots ? total_items : slots);
-  kern<<<grid, kThreads, kSmemBytes, stream>>>(p, static_cast<int>(total_items));
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see grid_dependency_wait in the kernel
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p, static_cast<int>(total_items));
 }
 
 cudaError_t launch_attention_persistent(const AttnParams& p, int batch, bool bf16, int mode, cudaStream_t stream) {

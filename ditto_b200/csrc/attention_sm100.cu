@@ -167,6 +167,10 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bar->tmem_base;
+  // Programmatic dependent launch: nothing above touches global memory, so it may overlap the end of the
+  // kernel ahead in the stream; its results are needed from here on.  The kernel behind may begin its set-up.
+  grid_dependency_wait();
+  grid_launch_dependents();
   if (warp == 0) DITTO_STAMP(512, 0, 8);
 
   if (warp == kProducerWarp) {
@@ -550,9 +554,17 @@ static cudaError_t launch_one(const AttnParams& p, int batch, cudaStream_t strea
     if (e != cudaSuccess) return e;
     configured.fetch_or(1ull << dev, std::memory_order_release);
   }
-  dim3 grid(static_cast<unsigned>((p.M + NT * kBM - 1) / (NT * kBM)) * static_cast<unsigned>(batch), 1, 1);
-  kern<<<grid, threads_for(NT), SM::kBytes, stream>>>(p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>((p.M + NT * kBM - 1) / (NT * kBM)) * static_cast<unsigned>(batch), 1, 1);
+  cfg.blockDim = dim3(threads_for(NT), 1, 1);
+  cfg.dynamicSmemBytes = SM::kBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see grid_dependency_wait in the kernel
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 cudaError_t launch_attention(const AttnParams& p, int batch, int d, bool bf16, int nt, bool psmem, int mode,

@@ -303,6 +303,13 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(bool bf16, uint32_t m, uin
          ((b_mn_major ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// wait: returns once the grids this one depends on have completed and their memory is visible (a no-op
+// when the kernel was launched without the programmatic-serialization attribute);
+// launch_dependents: lets the next kernel in the stream begin (it blocks at its own wait).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- math
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
