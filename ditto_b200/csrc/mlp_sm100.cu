@@ -178,6 +178,10 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   cluster_sync_all();                     // peers' barriers exist before anyone signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = bar->tmem_base;
+  // Programmatic dependent launch: the set-up above touches no global memory and may overlap the end of
+  // the kernel ahead in the stream; from here on its results are needed.
+  grid_dependency_wait();
+  grid_launch_dependents();
   const uint32_t tmem_y = tmem_base;
   const uint32_t tmem_h = tmem_base + 256;
 
@@ -567,16 +571,24 @@ int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int
   p.b2 = b2;
   p.status = status;
   p.trace = trace;
-  dim3 grid(kCluster * ((M + kRows - 1) / kRows), batch, 1);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(kCluster * ((M + kRows - 1) / kRows), batch, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see grid_dependency_wait in the kernel
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   cudaError_t e;
   if (bf16) {
     e = cudaFuncSetAttribute(mlp_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e == cudaSuccess) mlp_chain_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(p);
+    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, mlp_chain_kernel<true>, p);
   } else {
     e = cudaFuncSetAttribute(mlp_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e == cudaSuccess) mlp_chain_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(p);
+    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, mlp_chain_kernel<false>, p);
   }
-  if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? DITTO_OK : DITTO_ERR_CUDA;
 }
 

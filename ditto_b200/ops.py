@@ -32,11 +32,22 @@ _status_words = {}
 launch_count = 0
 
 
+_status_ptrs = {}
+
+
 def _status_word(device):
     key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
     if key not in _status_words:
         _status_words[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
     return _status_words[key]
+
+
+def _status_ptr(device):
+    """Device address of the status word of `device` (a torch.device), looked up once per device object."""
+    p = _status_ptrs.get(device)
+    if p is None:
+        p = _status_ptrs[device] = _status_word(device).data_ptr()
+    return p
 
 
 def device_status(device=None, reset=True):
@@ -97,7 +108,7 @@ def bmm_softmax_bmm(query, key, value, out=None, scale=1.0, key_layout="KL", fla
         stream = torch.cuda.current_stream().cuda_stream
         rc = lib.ditto_b200_bmm_softmax_bmm(query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(),
                                             batch, M, N, K, L, _DTYPE_CODE[query.dtype], klay, float(scale),
-                                            int(flags), None, 0, _status_word(query.device).data_ptr(), stream)
+                                            int(flags), None, 0, _status_ptr(query.device), stream)
     _lib.check(rc, "ditto_b200_bmm_softmax_bmm")
     launch_count += 1
     return out
@@ -126,7 +137,7 @@ def multi_head_attention(qkv, num_heads, out=None, scale=1.0, flags=0):
         stream = torch.cuda.current_stream().cuda_stream
         rc = lib.ditto_b200_multi_head_attention(qkv.data_ptr(), out.data_ptr(), batch, M, num_heads, hidden // num_heads,
                                                  _DTYPE_CODE[qkv.dtype], float(scale), int(flags),
-                                                 _status_word(qkv.device).data_ptr(), stream)
+                                                 _status_ptr(qkv.device), stream)
     _lib.check(rc, "ditto_b200_multi_head_attention")
     launch_count += 1
     return out
@@ -179,7 +190,7 @@ def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO", p
         rc = lib.ditto_b200_gemm_relu_gemm(x3.data_ptr(), w13.data_ptr(), w23.data_ptr(), out3.data_ptr(), batch, M, N,
                                            K, L, _DTYPE_CODE[x.dtype], wl,
                                            (1 if activation == "relu" else 0) | (0x200 if pair_mma else 0), None, 0,
-                                           _status_word(x.device).data_ptr(), stream)
+                                           _status_ptr(x.device), stream)
     _lib.check(rc, "ditto_b200_gemm_relu_gemm")
     launch_count += 1
     return out
@@ -234,7 +245,7 @@ def ffn(x, w1, b1, w2, b2, out=None, act1="relu", act2="relu", weight_layout="OI
         rc = lib.ditto_b200_ffn(x3.data_ptr(), w13.data_ptr(), b1.data_ptr() if b1 is not None else None, w23.data_ptr(),
                                 b2.data_ptr() if b2 is not None else None, out3.data_ptr(), batch, M, N, K, L,
                                 _DTYPE_CODE[x.dtype], 1 if weight_layout == "OI" else 0, _ACT_CODE[act1], _ACT_CODE[act2],
-                                _status_word(x.device).data_ptr(), stream)
+                                _status_ptr(x.device), stream)
     _lib.check(rc, "ditto_b200_ffn")
     launch_count += 1
     return out
