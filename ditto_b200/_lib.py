@@ -23,6 +23,8 @@ OP_GEMM_RELU_GEMM = 1
 FLAG_P_VIA_SMEM = 1
 FLAG_ONE_TILE = 2
 FLAG_TWO_TILES = 4
+EPILOGUE_PAIR_MMA = 0x200
+EPILOGUE_QUAD_MMA = 0x400
 
 EXPORTS = (
     "ditto_b200_bmm_softmax_bmm",
@@ -30,6 +32,7 @@ EXPORTS = (
     "ditto_b200_multi_head_attention",
     "ditto_b200_ffn",
     "ditto_b200_workspace_bytes",
+    "ditto_b200_mlp_cluster_slots",
     "ditto_b200_selftest_umma",
     "ditto_b200_selftest_umma_pair",
     "ditto_b200_selftest_wait_limit",
@@ -79,6 +82,8 @@ def load():
     lib.ditto_b200_ffn.restype = i
     lib.ditto_b200_workspace_bytes.argtypes = [i, i, i, i, i, i, i]
     lib.ditto_b200_workspace_bytes.restype = sz
+    lib.ditto_b200_mlp_cluster_slots.argtypes = [i, i]
+    lib.ditto_b200_mlp_cluster_slots.restype = i
     lib.ditto_b200_selftest_umma.argtypes = [vp, vp, vp, i, i, i, i, i, vp, vp]
     lib.ditto_b200_selftest_umma.restype = i
     lib.ditto_b200_selftest_umma_pair.argtypes = [vp, vp, vp, i, i, i, i, vp, vp]

@@ -1,2 +1,3 @@
 from . import functional
 from . import module
+from . import model

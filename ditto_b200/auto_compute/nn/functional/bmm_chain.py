@@ -7,7 +7,7 @@ query/A [batch, M, K], key/B [batch, K, L], value/C [batch, L, N], result [batch
 """
 import math
 
-from ... import te
+from .... import te
 
 
 def _dims(A, B, C):

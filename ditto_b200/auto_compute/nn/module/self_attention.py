@@ -1,7 +1,7 @@
 """Modules that wrap the fused chains (`ditto.auto_compute.nn.module`)."""
-from ... import te
-from ..graph import LayerTensor, layer
-from .functional import BatchGemmSoftmaxGemmMMA
+from .... import te
+from ...graph import LayerTensor, layer
+from ..functional import BatchGemmSoftmaxGemmMMA
 
 MUTI_HEAD_ATTENTION_LAYER = "multi_head_attention_mma_layer"
 SELF_ATTENTION_MODULE_REG = {MUTI_HEAD_ATTENTION_LAYER}

@@ -47,7 +47,7 @@ def extract_tasks_from_graph(graph):
 
 def _schedule_layer(layer, option):
     device = option.device or hw.query_hw_param("gpu.cuda.B200")
-    if is_self_attention_layer(layer):
+    if is_self_attention_layer(layer) or layer.name == "ffn_layer":
         return at.tensorize_cuda(layer, None, device)
     sfs = at.build_serial_fusion_state(layer)          # raises FusionError for non-chains
     choice = at.build_fusion_choice(sfs, device, option.mma_in_dtype, -1)

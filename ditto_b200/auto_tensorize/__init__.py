@@ -232,7 +232,7 @@ class ChainSchedule:
     """What `tensorize_cuda` returns in place of a te.Schedule: the recognised chain, ready for
     `ditto_b200.build`."""
     layer: Layer
-    kind: str          # "softmax" | "relu" | "identity"
+    kind: str          # "softmax" | "relu" | "identity" | "mha" | "ffn"
     batch: int
     M: int
     N: int
@@ -243,6 +243,10 @@ class ChainSchedule:
     device: HardwareParam
     param: CUDATensorizeParam
     heads: int = 1     # "mha": heads folded into the packed [batch, M, 3 * heads * K] input
+    act1: str = "identity"     # "ffn": activation after the first / second linear, and which biases exist
+    act2: str = "identity"
+    bias1: bool = False
+    bias2: bool = False
 
 
 def _schedule_self_attention(layer: Layer, cuda_param, tensorize_param) -> ChainSchedule:
@@ -265,10 +269,46 @@ def _schedule_self_attention(layer: Layer, cuda_param, tensorize_param) -> Chain
                          tensorize_param or CUDATensorizeParam(), heads)
 
 
+def _schedule_ffn(layer: Layer, cuda_param, tensorize_param) -> ChainSchedule:
+    """The feed-forward layer `chimera.graph_fusion` builds: x [..., K], W1 [L, K], (b1 [L]), W2 [N, L], (b2 [N]).
+    The weights are shared by every row, so all leading dimensions of x fold into M (batch = 1)."""
+    attrs = getattr(layer, "ffn_attrs", None)
+    if attrs is None or len(layer.inputs) != 1:
+        raise FusionError("not a feed-forward layer")
+    (x,) = layer.inputs
+    weights = list(layer.weights)
+    w1 = weights.pop(0)
+    b1 = weights.pop(0) if attrs["bias1"] else None
+    w2 = weights.pop(0)
+    b2 = weights.pop(0) if attrs["bias2"] else None
+    if weights:
+        raise FusionError("unexpected extra weights in a feed-forward layer")
+    K = x.shape[-1]
+    M = 1
+    for e in x.shape[:-1]:
+        M *= e
+    L, N = w1.shape[0], w2.shape[0]
+    if tuple(w1.shape) != (L, K) or tuple(w2.shape) != (N, L):
+        raise FusionError(f"weights {tuple(w1.shape)}, {tuple(w2.shape)} do not chain with an input of {K} features")
+    for bias, n in ((b1, L), (b2, N)):
+        if bias is not None and tuple(bias.shape) != (n,):
+            raise FusionError(f"bias of shape {tuple(bias.shape)}, expected {(n,)}")
+    dtypes = {t.dtype for t in (x, w1, w2, b1, b2, layer.ops[0].output(0)) if t is not None}
+    if len(dtypes) != 1 or x.dtype not in ("float16", "bfloat16"):
+        raise FusionError(f"the sm_100a kernels take one 16-bit type for inputs, weights, biases and output, got {sorted(dtypes)}")
+    for v, nm in ((M, "rows"), (N, "N"), (K, "K"), (L, "L")):
+        if v % 16:
+            raise FusionError(f"{nm}={v} must be a multiple of 16")
+    return ChainSchedule(layer, "ffn", 1, M, N, K, L, x.dtype, 1.0, cuda_param, tensorize_param or CUDATensorizeParam(),
+                         act1=attrs["act1"], act2=attrs["act2"], bias1=b1 is not None, bias2=b2 is not None)
+
+
 def tensorize_cuda(layer: Layer, state: TensorizeHyperFusionState = None, cuda_param: HardwareParam = None,
                    tensorize_param: CUDATensorizeParam = None) -> ChainSchedule:
     if layer.name == "multi_head_attention_mma_layer":
         return _schedule_self_attention(layer, cuda_param, tensorize_param)
+    if layer.name == "ffn_layer":
+        return _schedule_ffn(layer, cuda_param, tensorize_param)
     if state is None:
         raise FusionError("tensorize_cuda needs the TensorizeHyperFusionState of the chain")
     kind = state.chain_kind

@@ -10,131 +10,40 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
-#include <mutex>
 
 #include "attention_sm100.cuh"
+#include "host_util.cuh"
 #include "mlp_sm100.cuh"
 #include "selftest_sm100.cuh"
 
 namespace {
 
+using ditto_b200::cuda_fail;
+using ditto_b200::set_error;
+
 // Key/value rows up to which the persistent attention kernel is the faster one for head dims <= 64
 // (measured: 469 vs 453 TFLOP/s at 512 keys, 656 vs 680 at 2048).
 constexpr int kPersistentMaxKeys = 1024;
 
-thread_local char g_last_error[256] = "";
-
-void set_error(const char* what, const char* detail) {
-  std::snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, detail ? detail : "");
-}
-
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// The encoder is a host-side driver function; resolve it through the runtime so
-// the library has no link-time dependency on libcuda.
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  });
-  return fn;
-}
-
 // 2-D row-major tensor [rows, cols] of 16-bit elements, 128-byte swizzled boxes.
 int make_map_2d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint32_t box_cols,
                 uint32_t box_rows) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (fn == nullptr) {
-    set_error("cuTensorMapEncodeTiled", "entry point not found");
-    return DITTO_ERR_DRIVER;
-  }
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {box_cols, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    char buf[64];
-    std::snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
-    set_error("cuTensorMapEncodeTiled", buf);
-    return DITTO_ERR_CUDA;
-  }
-  return DITTO_OK;
+  const uint64_t dims[2] = {cols, rows}, strides[1] = {cols * 2};
+  const uint32_t box[2] = {box_cols, box_rows};
+  return ditto_b200::make_tensor_map(map, bf16, base, 2, dims, strides, box);
 }
 
 // 3-D tensor [slices, rows, cols] of 16-bit elements: coordinates (col, row, slice), boxes of
 // box_cols x box_rows x 1.  Rows beyond `rows` inside a slice are out of bounds and read as zero,
 // which is what makes partial tiles at the end of a sequence safe.
-// A tensor map is a pure function of these arguments, and callers with pre-allocated buffers (the
-// reference's calling convention) present the same ones call after call: the last few encodings are
-// kept per thread, which takes the three driver calls out of a repeated launch.
-struct MapKey {
-  const void* base;
-  uint64_t cols, rows, slices, row_stride, slice_stride;
-  uint32_t box_cols, box_rows, bf16;
-  bool operator==(const MapKey& o) const {
-    return base == o.base && cols == o.cols && rows == o.rows && slices == o.slices && row_stride == o.row_stride &&
-           slice_stride == o.slice_stride && box_cols == o.box_cols && box_rows == o.box_rows && bf16 == o.bf16;
-  }
-};
-struct MapCache {
-  static constexpr int kEntries = 8;
-  MapKey key[kEntries];
-  CUtensorMap map[kEntries];
-  bool valid[kEntries] = {};
-  int next = 0;
-};
-thread_local MapCache g_map_cache;
-
 int make_map_3d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint64_t slices,
                 uint64_t row_stride_elems, uint64_t slice_stride_elems, uint32_t box_cols, uint32_t box_rows) {
-  const MapKey want{base, cols, rows, slices, row_stride_elems, slice_stride_elems, box_cols, box_rows, bf16 ? 1u : 0u};
-  MapCache& cache = g_map_cache;
-  for (int i = 0; i < MapCache::kEntries; ++i)
-    if (cache.valid[i] && cache.key[i] == want) {
-      *map = cache.map[i];
-      return DITTO_OK;
-    }
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (fn == nullptr) {
-    set_error("cuTensorMapEncodeTiled", "entry point not found");
-    return DITTO_ERR_DRIVER;
-  }
-  const cuuint64_t dims[3] = {cols, rows, slices};
-  const cuuint64_t strides[2] = {row_stride_elems * 2, slice_stride_elems * 2};
-  const cuuint32_t box[3] = {box_cols, box_rows, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    char buf[64];
-    std::snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
-    set_error("cuTensorMapEncodeTiled", buf);
-    return DITTO_ERR_CUDA;
-  }
-  cache.key[cache.next] = want;
-  cache.map[cache.next] = *map;
-  cache.valid[cache.next] = true;
-  cache.next = (cache.next + 1) % MapCache::kEntries;
-  return DITTO_OK;
+  const uint64_t dims[3] = {cols, rows, slices}, strides[2] = {row_stride_elems * 2, slice_stride_elems * 2};
+  const uint32_t box[3] = {box_cols, box_rows, 1};
+  return ditto_b200::make_tensor_map(map, bf16, base, 3, dims, strides, box);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
-int cuda_fail(const char* what, cudaError_t e) {
-  set_error(what, cudaGetErrorString(e));
-  return DITTO_ERR_CUDA;
-}
 
 }  // namespace
 
@@ -244,14 +153,15 @@ int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M
 int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N,
                               int K, int L, int dtype, int w_layout, int epilogue, void* workspace,
                               size_t ws_bytes, int* status_word, void* stream) {
-  (void)workspace;
-  (void)ws_bytes;
   if (!x || !w1 || !w2 || !y) return DITTO_ERR_INVALID_ARG;
   if (batch <= 0 || M <= 0 || N <= 0 || K <= 0 || L <= 0) return DITTO_ERR_INVALID_ARG;
   if (!aligned16(x) || !aligned16(w1) || !aligned16(w2) || !aligned16(y)) return DITTO_ERR_INVALID_ARG;
   if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
   if (w_layout != 0 && w_layout != 1) return DITTO_ERR_INVALID_ARG;
-  if ((epilogue & ~0x200) != 0 && (epilogue & ~0x200) != 1) return DITTO_ERR_INVALID_ARG;
+  const int variant_bits = epilogue & (DITTO_EPILOGUE_PAIR_MMA | DITTO_EPILOGUE_QUAD_MMA);
+  const int act = epilogue & ~(DITTO_EPILOGUE_PAIR_MMA | DITTO_EPILOGUE_QUAD_MMA);
+  if (act != 0 && act != 1) return DITTO_ERR_INVALID_ARG;
+  if (variant_bits == (DITTO_EPILOGUE_PAIR_MMA | DITTO_EPILOGUE_QUAD_MMA)) return DITTO_ERR_INVALID_ARG;
   if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
   if (N == K && K <= 128) {
     // Small-N chains (the reference's shape family: N = K = 64, L = 512 ...): the result tile
@@ -280,7 +190,7 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
     p.scale_log2 = 1.0f;
     p.status = status_word;
     const int nt = (dk == 64 || M <= 128) ? 1 : 2;
-    const int mode = (epilogue & 0xff) == 1 ? 1 : 2;
+    const int mode = act == 1 ? 1 : 2;
     cudaError_t e = (dk == 64 && L <= kPersistentMaxKeys) ? ditto_b200::launch_attention_persistent(p, batch, bf16, mode, static_cast<cudaStream_t>(stream))
                              : ditto_b200::launch_attention(p, batch, dk, bf16, nt, false, mode,
                                                             static_cast<cudaStream_t>(stream));
@@ -289,10 +199,18 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
   }
   long long* trace = nullptr;
 #ifdef DITTO_TRACE
-  if (ws_bytes >= 128 * sizeof(long long)) trace = static_cast<long long*>(workspace);
+  if (ws_bytes >= 512 * sizeof(long long)) trace = static_cast<long long*>(workspace);
 #endif
-  return ditto_b200::launch_mlp_chain(x, w1, w2, y, batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, w_layout, epilogue,
-                                      status_word, static_cast<cudaStream_t>(stream), trace);
+#ifdef DITTO_TRACE
+  workspace = nullptr;   // the buffer is the timeline, not scratch
+  ws_bytes = 0;
+#endif
+  const int variant = variant_bits == DITTO_EPILOGUE_PAIR_MMA   ? ditto_b200::kMlpPair
+                      : variant_bits == DITTO_EPILOGUE_QUAD_MMA ? ditto_b200::kMlpQuad
+                                                                : ditto_b200::kMlpAuto;
+  return ditto_b200::launch_mlp_chain(x, w1, w2, y, batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, w_layout, act, 0,
+                                      nullptr, nullptr, variant, workspace, ws_bytes, status_word,
+                                      static_cast<cudaStream_t>(stream), trace);
 }
 
 int ditto_b200_ffn(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, void* y, int batch,
@@ -306,13 +224,32 @@ int ditto_b200_ffn(const void* x, const void* w1, const void* b1, const void* w2
   if (w_layout != 0 && w_layout != 1) return DITTO_ERR_INVALID_ARG;
   if (act1 < 0 || act1 > 2 || act2 < 0 || act2 > 2) return DITTO_ERR_INVALID_ARG;
   if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
-  return ditto_b200::launch_mlp_chain(x, w1, w2, y, batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, w_layout, act1,
-                                      status_word, static_cast<cudaStream_t>(stream), nullptr, b1, b2, act2);
+  return ditto_b200::launch_mlp_chain(x, w1, w2, y, batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, w_layout, act1, act2,
+                                      b1, b2, ditto_b200::kMlpAuto, nullptr, 0, status_word,
+                                      static_cast<cudaStream_t>(stream));
 }
 
 size_t ditto_b200_workspace_bytes(int op, int batch, int M, int N, int K, int L, int dtype) {
-  (void)op; (void)batch; (void)M; (void)N; (void)K; (void)L; (void)dtype;
-  return 0;  // both chains keep their intermediates on chip
+  // The attention chain keeps everything on chip.  The MLP chain does too, except that with few row blocks
+  // it runs faster when several clusters share a row block and combine fp32 partials of Y through scratch
+  // memory (the hidden activations still never leave the chip); the call works without it.
+  if ((op & 0xff) != DITTO_OP_GEMM_RELU_GEMM || batch <= 0 || M <= 0 || N <= 0 || K <= 0 || L <= 0) return 0;
+  if (N == K && K <= 128) return 0;
+  // `op` may carry DITTO_EPILOGUE_PAIR_MMA / DITTO_EPILOGUE_QUAD_MMA like the call's `epilogue` argument
+  const int variant = (op & DITTO_EPILOGUE_PAIR_MMA) ? ditto_b200::kMlpPair
+                      : (op & DITTO_EPILOGUE_QUAD_MMA) ? ditto_b200::kMlpQuad : ditto_b200::kMlpAuto;
+  size_t a = ditto_b200::mlp_workspace_bytes(batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, 0, variant);
+  size_t b = ditto_b200::mlp_workspace_bytes(batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, 1, variant);
+  return a > b ? a : b;
+}
+
+int ditto_b200_mlp_cluster_slots(int dtype, int variant) {
+  if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
+  int slots = 0;
+  int rc = variant == DITTO_EPILOGUE_PAIR_MMA   ? ditto_b200::mlp_pair_cluster_slots(dtype == DITTO_DTYPE_BF16, &slots)
+           : variant == DITTO_EPILOGUE_QUAD_MMA ? ditto_b200::mlp_quad_cluster_slots(dtype == DITTO_DTYPE_BF16, &slots)
+                                                : DITTO_ERR_INVALID_ARG;
+  return rc ? rc : slots;
 }
 
 int ditto_b200_selftest_umma(const void* a, const void* b, float* c, int N, int K, int dtype, int b_mn, int a_tmem,
@@ -384,7 +321,7 @@ const char* ditto_b200_strerror(int code) {
   }
 }
 
-const char* ditto_b200_last_cuda_error(void) { return g_last_error; }
+const char* ditto_b200_last_cuda_error(void) { return ditto_b200::last_error_text(); }
 
 int ditto_b200_version(void) { return 100; }
 

@@ -392,6 +392,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_persistent_kernel(const
     }
   }
 
+  // After a wait has given up, TMA loads this CTA has armed may still be in flight; they complete within
+  // microseconds.  Give them that time before the shared memory they target is released.
+  if (bar->abort_word != 0u) {
+    for (int t = 0; t < 64; ++t) __nanosleep(1000);
+  }
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) {

@@ -18,6 +18,109 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (BF16) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w));
+  } else {
+    return __half22float2(*reinterpret_cast<__half2*>(&w));
+  }
+}
+
+// Activation codes of the chain: 0 identity, 1 ReLU, 2 GELU (tanh form).
+template <int ACT>
+__device__ __forceinline__ float act_apply(float v) {
+  if constexpr (ACT == 1) {
+    return v > 0.f ? v : 0.f;                      // if_then_else(x > 0, x, 0) as in the reference's ReLU
+  } else if constexpr (ACT == 2) {                 // the reference's GELU: 0.5 x (1 + tanh(0.79788456 x (1 + 0.044715 x^2)))
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(v * 0.7978845608f * (1.0f + 0.044715f * v * v)));
+    return 0.5f * v * (1.0f + t);
+  } else {
+    return v;
+  }
+}
+
+// N fp32 accumulator values of one row (+ a 16-bit bias vector, the same address in every lane: broadcast
+// loads) -> activation -> N / 2 packed 16-bit pairs.  The activation and the presence of a bias are
+// compile-time here: a run-time test per element costs a branch per element, which made this loop the
+// longest step of the hidden-chunk hand-over.
+template <bool BF16, int ACT, bool BIAS, int N>
+__device__ __forceinline__ void act_pack_fixed(const uint32_t (&acc)[N], const uint32_t* bias, uint32_t (&out)[N / 2]) {
+#pragma unroll
+  for (int j = 0; j < N / 2; ++j) {
+    float v0 = __uint_as_float(acc[2 * j]), v1 = __uint_as_float(acc[2 * j + 1]);
+    if constexpr (BIAS) {
+      const float2 bb = unpack2<BF16>(__ldg(bias + j));
+      v0 += bb.x;
+      v1 += bb.y;
+    }
+    out[j] = pack2<BF16>(act_apply<ACT>(v0), act_apply<ACT>(v1));
+  }
+}
+// One warp-uniform dispatch per call instead of one per element.
+template <bool BF16, int N>
+__device__ __forceinline__ void act_pack(const uint32_t (&acc)[N], const uint32_t* bias, int act, uint32_t (&out)[N / 2]) {
+  if (bias == nullptr) {
+    if (act == 1) act_pack_fixed<BF16, 1, false, N>(acc, bias, out);
+    else if (act == 2) act_pack_fixed<BF16, 2, false, N>(acc, bias, out);
+    else act_pack_fixed<BF16, 0, false, N>(acc, bias, out);
+  } else {
+    if (act == 1) act_pack_fixed<BF16, 1, true, N>(acc, bias, out);
+    else if (act == 2) act_pack_fixed<BF16, 2, true, N>(acc, bias, out);
+    else act_pack_fixed<BF16, 0, true, N>(acc, bias, out);
+  }
+}
+__device__ __forceinline__ float act_apply_rt(float v, int act) {
+  return act == 1 ? act_apply<1>(v) : act == 2 ? act_apply<2>(v) : v;
+}
+
+// Last step of a row block that several clusters shared: add the clusters' fp32 partials of a
+// rows x cols region of Y (one slab per cluster, `slab_stride` floats apart, row pitch `ld` floats) in
+// slab order, apply bias and activation, write the 16-bit result.  `nthreads` threads of one CTA call it with
+// tid = 0 .. nthreads - 1.  Two float4 per thread and all slabs' loads are issued before the first add:
+// with one load in flight at a time this pass is bound by L2 latency (measured 100 us for 128 x 256 x 8
+// slabs), with 2 x parts in flight it takes a few microseconds.
+constexpr int kMaxSlabs = 8;
+template <bool BF16>
+__device__ __forceinline__ void combine_slabs(const float* slab0, size_t slab_stride, int parts, int rows, int cols,
+                                              size_t ld, const uint32_t* bias, int act, uint8_t* y, size_t y_pitch_bytes,
+                                              int tid, int nthreads) {
+  const int per_row = cols / 4;
+  const int total = rows * per_row;
+  for (int base = 0; base < total; base += 2 * nthreads) {
+    float4 v[2][kMaxSlabs];
+    int r[2], c[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int idx = base + j * nthreads + tid;
+      r[j] = idx / per_row;
+      c[j] = (idx - r[j] * per_row) * 4;
+#pragma unroll
+      for (int s = 0; s < kMaxSlabs; ++s)
+        if (idx < total && s < parts)
+          v[j][s] = __ldcg(reinterpret_cast<const float4*>(slab0 + static_cast<size_t>(s) * slab_stride + static_cast<size_t>(r[j]) * ld + c[j]));
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      if (base + j * nthreads + tid >= total) continue;
+      float4 acc = v[j][0];
+#pragma unroll
+      for (int s = 1; s < kMaxSlabs; ++s)
+        if (s < parts) {
+          acc.x += v[j][s].x; acc.y += v[j][s].y; acc.z += v[j][s].z; acc.w += v[j][s].w;
+        }
+      if (bias != nullptr) {
+        const float2 b01 = unpack2<BF16>(__ldg(bias + c[j] / 2)), b23 = unpack2<BF16>(__ldg(bias + c[j] / 2 + 1));
+        acc.x += b01.x; acc.y += b01.y; acc.z += b23.x; acc.w += b23.y;
+      }
+      const uint2 out = make_uint2(pack2<BF16>(act_apply_rt(acc.x, act), act_apply_rt(acc.y, act)),
+                                   pack2<BF16>(act_apply_rt(acc.z, act), act_apply_rt(acc.w, act)));
+      *reinterpret_cast<uint2*>(y + static_cast<size_t>(r[j]) * y_pitch_bytes + c[j] * 2) = out;
+    }
+  }
+}
+
 // Bulk copy from this CTA's shared memory into a peer's; completion (bytes) on the peer's mbarrier.
 __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, const void* src, uint32_t bytes,
                                                   uint32_t mbar_cluster_addr) {

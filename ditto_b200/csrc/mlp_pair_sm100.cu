@@ -1,44 +1,87 @@
-// Fused GEMM -> activation -> GEMM on CTA pairs (tcgen05 cta_group::2) for sm_100a.
+// Fused GEMM -> activation -> GEMM on CTA pairs (tcgen05 cta_group::2) for sm_100a:
+//   Y = act2(act1(X W1 + b1) W2 + b2), hidden activations on chip.
 //
-// Same decomposition as mlp_sm100.cu (Y columns split four ways, hidden chunks exchanged through
-// distributed shared memory), but every MMA is a 2-SM MMA of M = 256: a cluster of eight CTAs =
-// four pairs shares a 256-row block of X / Y.  Pair p (CTAs 2p, 2p+1) owns the Y columns
-// [p N/4, (p+1) N/4) and every fourth hidden chunk; inside a pair CTA h holds rows
-// [128 h, 128 h + 128) and half of each B operand's N extent, so a weight byte fetched from L2
-// now serves 256 rows instead of 128: per CTA the chain streams 4 MB instead of 6 MB.
-// (The single-CTA kernel is bound by how many operand bytes its shared-memory ring can keep in
-// flight, not by the tensor pipe.)
+// Replaces what the reference would build from BatchGemmReluGemm / BatchGemmGemm
+// (python_test/auto_tensorize/test_hyper_fusion_cpu.py:24-96, benchmark/chimera/cuda/bmm_bmm_cuda.py:69-150)
+// and the feed-forward block of nn/model/transformer.py:21-34.
+//
+// Why this shape.  The chain is fed from L2: every operand byte a CTA multiplies has to cross the
+// L2 -> shared-memory path, and that path -- not the tensor pipe -- bounds the kernel.  So the tiles are
+// chosen for the fewest operand bytes per FLOP that tensor memory allows:
+//   * a cluster of eight CTAs = four pairs shares a 256-row block of X / Y; every MMA is a 2-SM MMA of
+//     M = 256 (CTA h of a pair holds rows [128 h, 128 h + 128) and half of each B operand's N extent),
+//     so a weight byte serves 256 rows;
+//   * pair p keeps the Y columns [p N/4, (p+1) N/4) in tensor memory for the whole item (<= 256 columns)
+//     and owns every fourth 256-wide chunk of the hidden dimension: GEMM1 of a chunk is one 256 x 256
+//     accumulator (the other 256 columns), so the X block is re-read once per 256 hidden columns;
+//   * per CTA the chain streams 3 MB for config 4 (X 1, W1 1, W2 1) against 6 MB for the 4-CTA form of
+//     mlp_sm100.cu.
+// A chunk leaves tensor memory as four units of 64 hidden columns (128 rows x 64 x 16 bit = 16 KB per CTA):
+// CTA (p, h) applies bias / activation, rounds to 16 bit, writes the unit into its own shared memory in
+// the K-major 128B-swizzled operand layout and pushes it to the CTAs (p', h) of the other pairs with
+// shared::cta -> shared::cluster bulk copies.  Hidden activations exist only in tensor memory and
+// (distributed) shared memory.  No TMA load in this file uses cluster multicast.
 //
 // Who talks to whom:
-//   * TMA: each CTA loads its own X rows and its half of W1 / W2 tiles; byte counts go to the
-//     pair leader's `full` barrier (cp.async.bulk.tensor ... cta_group::2, no multicast).
-//   * MMA: only the leader's warp 5 issues; commits are delivered to both CTAs of the pair.
-//   * Hidden chunks travel in units of 64 columns (16 KB per CTA); unit u = 2 chunk + half lives in slot
-//     u % 6 of every CTA.  CTA (p, h) drains its 128 rows of its pair's chunk from TMEM, writes the two
-//     units into its own slots and pushes them to the CTAs (p', h) of the other pairs.
-//   * Each CTA's ready-relay thread takes the units in order, arms the slot's barrier for units a peer
-//     pushes, waits until the unit is present and tells the pair leader (h_pair, 2 arrivals): the pair's
-//     GEMM2 on a unit needs it in both CTAs.
-//   * A slot may be refilled when all four pairs have finished GEMM2 on the unit in it: each CTA's
-//     free-relay thread forwards the leader's g2_done to the CTA of its half that writes the slot next.
-//   * Tensor-pipe order on the leader: GEMM1 of the pair's first two chunks, then per unit
-//     GEMM2(unit) | an eighth of GEMM1 of the chunk two rounds ahead.
+//   * TMA (two producer threads per CTA, alternate ring granules of 16 KB): each CTA loads its own X rows
+//     and its half of the W1 / W2 tiles; byte counts go to the pair leader's `full` barrier.
+//   * MMA: only the leader's issuing warp; commits are delivered to both CTAs of the pair.
+//   * Units are numbered n in the order GEMM2 consumes them -- round by round (four chunks, one per
+//     pair), inside a round quarter by quarter across the pairs, which is the order they arrive in --
+//     and live in slot n % kUnits of every CTA.
+//   * ready relay (one thread per CTA): takes the units in order, arms the slot's barrier for units a
+//     peer pushes, waits until the unit is present and tells the leader (h_pair, 2 arrivals).
+//   * free relay (one thread per CTA): forwards "the pair's GEMM2 is done with slot s" to the CTA of its
+//     half that writes the slot next (slot_free, 4 arrivals).
+//   * Tensor-pipe order on the leader: GEMM1 of the pair's first chunk, then per round the sixteen
+//     GEMM2 units with GEMM1 of the next own chunk spread over the first twelve of them, so the chunk is
+//     drained and on its way while the last four units keep the pipe busy.
+//
+// Work items.  An item is (row block, hidden range): with few row blocks the hidden dimension is split
+// over several clusters, each writes its fp32 partial of Y to its own slab of the caller's workspace,
+// and the last cluster to finish a row block (a counter per CTA rank) adds the slabs in a fixed order and
+// writes Y -- the results do not depend on which cluster came last.  With one split Y is written directly.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstring>
 
 #include "../../include/ditto_b200.h"
+#include "host_util.cuh"
 #include "mlp_common.cuh"
 #include "mlp_sm100.cuh"
 #include "sm100_ptx.cuh"
 
+// Optional timeline capture for tuning (compiled in only with -DDITTO_TRACE): the leader CTA of the first
+// cluster stores clock64() stamps into the buffer passed as the call's workspace.
 #ifdef DITTO_TRACE
-#define DITTO_STAMP(i, k)                                                                   \
-  do {                                                                                      \
-    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (i) < 8) p.trace[(i) * 16 + (k)] = clock64(); \
+#define DITTO_STAMP(slot)                                                                          \
+  do {                                                                                             \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (slot) < 512) p.trace[(slot)] = clock64(); \
+  } while (0)
+#define DITTO_TIMED(acc, expr)          \
+  do {                                 \
+    const long long t_ = clock64();    \
+    expr;                              \
+    acc += clock64() - t_;             \
   } while (0)
 #else
-#define DITTO_STAMP(i, k) do {} while (0)
+#define DITTO_STAMP(slot) do {} while (0)
+#define DITTO_TIMED(acc, expr) do { expr; } while (0)
+#endif
+
+#ifndef DITTO_PAIR_UNITS
+#define DITTO_PAIR_UNITS 6
+#endif
+#ifndef DITTO_PAIR_GRANULES
+#define DITTO_PAIR_GRANULES 8
+#endif
+// GEMM1 of the next own chunk is spread over the first kLeadNum / kLeadDen of a round's GEMM2 units
+#ifndef DITTO_PAIR_LEAD_NUM
+#define DITTO_PAIR_LEAD_NUM 3
+#endif
+#ifndef DITTO_PAIR_LEAD_DEN
+#define DITTO_PAIR_LEAD_DEN 4
 #endif
 
 namespace ditto_b200 {
@@ -48,51 +91,97 @@ namespace {
 constexpr int kCluster = 8;
 constexpr int kPairs = 4;
 constexpr int kRows = 128;            // rows per CTA (256 per pair / cluster)
-constexpr int kChunk = 128;           // hidden columns per chunk
-constexpr int kStageBytes = 24 * 1024;
-constexpr int kUnitBytes = kRows * 64 * 2;   // 64 hidden columns of this CTA's 128 rows: one 128-byte-row atom, 16 KB
-#ifndef DITTO_PAIR_UNITS
-#define DITTO_PAIR_UNITS 6
-#endif
-#ifndef DITTO_PAIR_STAGES
-#define DITTO_PAIR_STAGES 5
-#endif
-constexpr int kUnits = DITTO_PAIR_UNITS;    // unit slots per CTA
-constexpr int kStages = DITTO_PAIR_STAGES;
-constexpr int kThreads = 288;
-constexpr uint32_t kProducers = 2;      // TMA-issuing threads (warps 4 and 7), alternate ring stages
+constexpr int kChunk = 256;           // hidden columns per chunk = N of a GEMM1 MMA
+constexpr int kUnitCols = 64;         // hidden columns per unit: one 128-byte-row swizzle atom
+constexpr int kUnitBytes = kRows * kUnitCols * 2;
+constexpr int kGranule = 16 * 1024;   // ring granule: one operand tile (X k-step, W1 half tile, W2 half tile)
+constexpr int kUnits = DITTO_PAIR_UNITS;        // unit slots per CTA
+constexpr int kGranules = DITTO_PAIR_GRANULES;  // ring depth (even: the two producers take alternate granules)
+constexpr int kEpiWarps = 8;          // warp w: TMEM lanes 32 (w % 4) ..., column half w / 4 of every quarter
+constexpr int kWarpProd0 = 8, kWarpMma = 9, kWarpReady = 10, kWarpFree = 11, kWarpProd1 = 12;
+constexpr int kThreads = 13 * 32;
 constexpr int kOffSlots = 0;
 constexpr int kOffRing = kOffSlots + kUnits * kUnitBytes;
-constexpr int kOffBar = kOffRing + kStages * kStageBytes;
+constexpr int kOffBar = kOffRing + kGranules * kGranule;
 constexpr int kSmemBytes = kOffBar + 512 + 1024;
+static_assert(kGranules % 2 == 0, "producers alternate over the granules");
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 
 struct PairParams {
-  CUtensorMap map_x;   // X  [batch*M, K], box 64 x 128
-  CUtensorMap map_w1;  // IO: W1 [batch*K, L], box 64 x 64;  OI: W1 [batch*L, K], box 64 x 64
-  CUtensorMap map_w2;  // IO: W2 [batch*L, N], box 64 x 64;  OI: W2 [batch*N, L], box 64 x N/8
-  void* y;
+  CUtensorMap map_x;   // X (K, M, batch), box 64 x 128 x 1: partial row blocks and K tails read as zero
+  CUtensorMap map_w1;  // IO: W1 as atoms (64, K, L/64, batch), box 64 x 64 x 2 x 1;  OI: (K, L, batch), box 64 x 128 x 1
+  CUtensorMap map_w2;  // IO: W2 as atoms (64, L, N/64, batch), box 64 x 64 x N/512 x 1;  OI: (L, N, batch), box 64 x N/8 x 1
+  void* y;             // Y [batch, M, N]
+  float* slabs;        // shared row blocks: fp32 partials [part][batch][shared row blocks * 256][N]
+  int* counters;       // shared row blocks: one per (batch, shared row block, CTA rank), zero at launch
   int M, N, K, L;
-  int w_oi;
-  int relu;
+  int row_blocks;      // ceil(M / 256)
+  int whole_blocks;    // the first row blocks are computed by one cluster each ...
+  int parts;           // ... the others by `parts` clusters, each taking a range of the hidden chunks
+  int w_oi;            // 1: weights stored [out, in] (K-major B operands)
+  int w_atoms;         // [in, out] weights: the maps are atom views (one box per tile); else (L | N, K | L, batch), box 64 x 64 x 1
+  int act1, act2;      // 0 identity, 1 ReLU, 2 GELU (tanh form)
+  const void* b1;      // optional bias [batch, L] (16-bit, the input type); may be null
+  const void* b2;      // optional bias [batch, N]; may be null
   int* status;
   long long* trace;    // timeline buffer of -DDITTO_TRACE builds (null otherwise)
 };
 
 struct PairBars {
-  uint64_t full[kStages];      // leader: operands of both CTAs have landed
-  uint64_t empty[kStages];     // each CTA: the pair's MMAs have finished with the stage
-  uint64_t h_tmem_full[2];     // each CTA: GEMM1 of the chunk is in TMEM
-  uint64_t h_tmem_empty[2];    // leader: both CTAs' epilogues have read the TMEM buffer (8 warp arrivals)
-  uint64_t h_ready[kUnits];    // each CTA: the unit of the slot's current use is present (own: local arrive; peer's: pushed bytes)
+  uint64_t full[kGranules];    // leader: the granule's tiles of both CTAs have landed
+  uint64_t empty[kGranules];   // each CTA: the pair's MMAs have finished with the granule
+  uint64_t h_tmem_full;        // each CTA: GEMM1 of the chunk is in tensor memory
+  uint64_t h_tmem_empty;       // leader: both CTAs' epilogue warps hold the chunk in registers (16 warp arrivals)
+  uint64_t h_ready[kUnits];    // each CTA: the slot's unit is present (own: local arrive; a peer's: pushed bytes)
   uint64_t h_pair[kUnits];     // leader: ... in both CTAs of the pair (2 arrivals)
   uint64_t g2_done[kUnits];    // each CTA: the pair's GEMM2 has finished reading the slot
   uint64_t slot_free[kUnits];  // all four pairs have (4 arrivals); kept at the CTA that writes the slot next
-  uint64_t y_done;
-  uint64_t epi_sync;
+  uint64_t y_done;             // each CTA: the item's last MMA has retired
+  uint64_t epi_sync;           // all 256 epilogue threads, once per unit they write
+  uint64_t y_sync;             // all 256 epilogue threads (split items only)
   uint32_t tmem_base;
   uint32_t abort_word;
+  uint32_t last_flag;          // split items: this CTA is the last of its rank to finish the row block
 };
 static_assert(sizeof(PairBars) <= 512, "barrier block too large");
+
+// Tiled loads into this CTA's shared memory whose byte count is reported to `bar_cluster_addr`, a
+// shared::cluster address that may lie in the pair's leader CTA.  No multicast.
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x,
+                                                 int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x,
+                                                 int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
+// The order in which the leader's tensor pipe takes the work of an item, shared by the producers (which
+// fill the ring in this order) and the issuing warp.  g1(i, ks): k-step ks of GEMM1 of this pair's chunk of
+// round i.  g2(n, i, kk, src): GEMM2 on unit n = quarter kk of the chunk of pair `src` in round i.
+template <class G1, class G2>
+__device__ __forceinline__ void walk_item(int chunks, int my_rounds, int ksteps1, const bool& ok, G1&& g1, G2&& g2) {
+  if (my_rounds > 0)
+    for (int ks = 0; ks < ksteps1 && ok; ++ks) g1(0, ks);
+  const int total_rounds = (chunks + kPairs - 1) / kPairs;
+  for (int i = 0; i < total_rounds && ok; ++i) {
+    const int cr = min(kPairs, chunks - kPairs * i);   // chunks (= pairs at work) in this round
+    const int nun = 4 * cr;
+    const int lead = max(1, nun * DITTO_PAIR_LEAD_NUM / DITTO_PAIR_LEAD_DEN);
+    const bool next = i + 1 < my_rounds;
+    for (int e = 0; e < nun && ok; ++e) {
+      if (next && e < lead)
+        for (int ks = e * ksteps1 / lead; ks < (e + 1) * ksteps1 / lead && ok; ++ks) g1(i + 1, ks);
+      g2(4 * kPairs * i + e, i, e / cr, e % cr);
+    }
+  }
+}
 
 }  // namespace
 
@@ -100,6 +189,8 @@ template <bool BF16>
 __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     mlp_pair_kernel(const __grid_constant__ PairParams p) {
   extern __shared__ uint8_t smem_raw[];
+  // Every CTA of the cluster rounds its dynamic shared memory up by the same amount (the base offset is
+  // identical across CTAs of a launch), so slot and barrier offsets match across peers.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   PairBars* bar = reinterpret_cast<PairBars*>(smem + kOffBar);
   volatile uint32_t* abort_word = &bar->abort_word;
@@ -107,26 +198,33 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
-  const uint32_t pair = rank >> 1;        // owns Y columns [pair NS, (pair+1) NS) and chunks pair, pair+4, ...
+  const uint32_t pair = rank >> 1;        // owns Y columns [pair NS, (pair+1) NS) and chunks pair, pair+4, ... of the item
   const uint32_t half = rank & 1;         // 0 = leader of the pair
   const uint32_t leader = rank & ~1u;
-  const int row0 = (blockIdx.x / kCluster) * (2 * kRows) + static_cast<int>(half) * kRows;
+  const int item = blockIdx.x / kCluster;
+  // items of a batch entry: the whole row blocks first, then the parts of the shared ones
+  const bool shared = item >= p.whole_blocks;
+  const int nparts = shared ? p.parts : 1;
+  const int rb = shared ? p.whole_blocks + (item - p.whole_blocks) / p.parts : item;   // 256-row block
+  const int sp = shared ? (item - p.whole_blocks) % p.parts : 0;                      // which part of the hidden dimension
   const int b = blockIdx.y;
+  const int row0 = rb * (2 * kRows) + static_cast<int>(half) * kRows;
   const int NS = p.N / kPairs;            // the pair's Y columns
   const int NH = NS / 2;                  // this CTA's share of the W2 tile's N extent
-  const int rounds = p.L / (kPairs * kChunk);
-  const int units = 2 * kPairs * rounds;  // 64-column units of hidden chunks in all
-  const int ksteps1 = p.K / 64;
+  const int all_chunks = p.L / kChunk;
+  const int c0 = static_cast<int>(static_cast<long long>(sp) * all_chunks / nparts);
+  const int chunks = static_cast<int>(static_cast<long long>(sp + 1) * all_chunks / nparts) - c0;
+  const int units = 4 * chunks;           // 64-column units of the item, numbered in consumption order
+  const int my_rounds = static_cast<int>(pair) < chunks ? (chunks - static_cast<int>(pair) + kPairs - 1) / kPairs : 0;
+  const int ksteps1 = (p.K + 63) / 64;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kGranules; ++s) {
       mbar_init(&bar->full[s], 1);
       mbar_init(&bar->empty[s], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar->h_tmem_full[i], 1);
-      mbar_init(&bar->h_tmem_empty[i], 8);
-    }
+    mbar_init(&bar->h_tmem_full, 1);
+    mbar_init(&bar->h_tmem_empty, 2 * kEpiWarps);
     for (int x = 0; x < kUnits; ++x) {
       mbar_init(&bar->h_ready[x], 1);
       mbar_init(&bar->h_pair[x], 2);
@@ -134,8 +232,10 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       mbar_init(&bar->slot_free[x], kPairs);
     }
     mbar_init(&bar->y_done, 1);
-    mbar_init(&bar->epi_sync, kRows);
+    mbar_init(&bar->epi_sync, kEpiWarps * 32);
+    mbar_init(&bar->y_sync, kEpiWarps * 32);
     bar->abort_word = 0;
+    bar->last_flag = 0;
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -149,12 +249,15 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const uint32_t tmem_base = bar->tmem_base;
   const uint32_t tmem_y = tmem_base;
   const uint32_t tmem_h = tmem_base + 256;
+  // Programmatic dependent launch: the set-up above touches no global memory and may overlap the end of
+  // the kernel ahead in the stream; from here on its results are needed.
+  grid_dependency_wait();
+  grid_launch_dependents();
 
-  if (warp == 4 || warp == 7) {
-    // ------------------------------------------------------------ TMA producers (one thread each, alternate stages)
+  if (warp == kWarpProd0 || warp == kWarpProd1) {
+    // ------------------------------------------------------------ TMA producers (one thread each)
     if (lane == 0) {
-      const uint32_t pw = warp == 4 ? 0u : 1u;
-      uint32_t cnt = 0;
+      const uint32_t pw = warp == kWarpProd0 ? 0u : 1u;
       tma_prefetch_desc(&p.map_x);
       tma_prefetch_desc(&p.map_w1);
       tma_prefetch_desc(&p.map_w2);
@@ -162,57 +265,57 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       uint32_t pph = 0;
       bool ok = true;
       uint32_t full_addr = 0;             // the leader's full[ps] as a cluster address
-      // `pair_bytes`: what both CTAs of the pair put into the stage (armed by the leader only)
+      // Both producers walk the same sequence of granules; each fills the ones of its parity.
+      // `pair_bytes`: what both CTAs of the pair put into the granule (armed by the leader only).
       auto acquire = [&](uint32_t pair_bytes, uint32_t code) -> uint8_t* {
-        if ((cnt++ & (kProducers - 1)) != pw) return nullptr;
-        ok = mbar_wait(&bar->empty[ps], pph ^ 1, abort_word, code);
-        if (!ok) return nullptr;
-        if (half == 0) mbar_arrive_expect_tx(&bar->full[ps], pair_bytes);
-        full_addr = map_to_cta(smem_u32(&bar->full[ps]), leader);
-        return smem + kOffRing + ps * kStageBytes;
-      };
-      auto advance = [&]() {
-        if (++ps == kStages) { ps = 0; pph ^= 1; }
-      };
-      auto load_g1 = [&](int i, int ks0, int ks1) {   // X rows of this CTA and its half of the W1 chunk tile, k-steps [ks0, ks1)
-        const int g = i * kPairs + static_cast<int>(pair);
-        for (int ks = ks0; ks < ks1 && ok; ++ks) {
-          uint8_t* dst = acquire(2 * (16384 + 8192), 0x100 + i);
-          if (dst != nullptr) {
-            tma_load_2d_pair(dst, &p.map_x, full_addr, ks * 64, b * p.M + row0);
-            if (p.w_oi)
-              tma_load_2d_pair(dst + 16384, &p.map_w1, full_addr, ks * 64, b * p.L + g * kChunk + half * 64);
-            else
-              tma_load_2d_pair(dst + 16384, &p.map_w1, full_addr, g * kChunk + half * 64, b * p.K + ks * 64);
-          }
-          advance();
-        }
-      };
-      auto load_g2 = [&](int u) {         // this CTA's half of the pair's W2 slice for hidden unit u
-        const int g = u >> 1, kk = u & 1;
-        uint8_t* dst = acquire(2 * 64 * NH * 2, 0x200 + (u >> 3));
-        if (dst != nullptr) {
-          if (p.w_oi) {
-            tma_load_2d_pair(dst, &p.map_w2, full_addr, g * kChunk + kk * 64, b * p.N + pair * NS + half * NH);
-          } else {
-            for (int a = 0; a < NH / 64; ++a)
-              tma_load_2d_pair(dst + a * 8192, &p.map_w2, full_addr, pair * NS + half * NH + a * 64,
-                               b * p.L + g * kChunk + kk * 64);
+        uint8_t* dst = nullptr;
+        if ((static_cast<uint32_t>(ps) & 1u) == pw) {
+          ok = mbar_wait(&bar->empty[ps], pph ^ 1, abort_word, code);
+          if (ok) {
+            if (half == 0) mbar_arrive_expect_tx(&bar->full[ps], pair_bytes);
+            full_addr = map_to_cta(smem_u32(&bar->full[ps]), leader);
+            dst = smem + kOffRing + ps * kGranule;
           }
         }
-        advance();
+        if (++ps == kGranules) { ps = 0; pph ^= 1; }
+        return dst;
       };
-      // the order the leader's MMA warp consumes the ring in
-      load_g1(0, 0, ksteps1);
-      if (rounds > 1) load_g1(1, 0, ksteps1);
-      for (int u = 0; u < units && ok; ++u) {
-        const int i = u >> 3, e = u & 7;
-        load_g2(u);
-        if (i + 2 < rounds) load_g1(i + 2, e * ksteps1 / 8, (e + 1) * ksteps1 / 8);
-      }
+      walk_item(chunks, my_rounds, ksteps1, ok,
+          [&](int i, int ks) {            // GEMM1 k-step: this CTA's X rows, then its half of the W1 chunk tile
+            const int hcol = (c0 + i * kPairs + static_cast<int>(pair)) * kChunk + static_cast<int>(half) * (kChunk / 2);
+            uint8_t* dst = acquire(2 * kGranule, 0x100 + i);
+            if (dst != nullptr) tma_load_3d_pair(dst, &p.map_x, full_addr, ks * 64, row0, b);
+            dst = acquire(2 * kGranule, 0x140 + i);
+            if (dst != nullptr) {
+              if (p.w_oi) {
+                tma_load_3d_pair(dst, &p.map_w1, full_addr, ks * 64, hcol, b);
+              } else if (p.w_atoms) {
+                tma_load_4d_pair(dst, &p.map_w1, full_addr, 0, ks * 64, hcol / 64, b);
+              } else {
+                for (int a = 0; a < kChunk / 2 / 64; ++a)
+                  tma_load_3d_pair(dst + a * 8192, &p.map_w1, full_addr, hcol + a * 64, ks * 64, b);
+              }
+            }
+          },
+          [&](int n, int i, int kk, int src) {   // GEMM2 unit: this CTA's half of the pair's W2 slice
+            (void)n;
+            const int hrow = (c0 + i * kPairs + src) * kChunk + kk * kUnitCols;
+            const int ncol = static_cast<int>(pair) * NS + static_cast<int>(half) * NH;
+            uint8_t* dst = acquire(2 * 64 * NH * 2, 0x200 + i);
+            if (dst != nullptr) {
+              if (p.w_oi) {
+                tma_load_3d_pair(dst, &p.map_w2, full_addr, hrow, ncol, b);
+              } else if (p.w_atoms) {
+                tma_load_4d_pair(dst, &p.map_w2, full_addr, 0, hrow, ncol / 64, b);
+              } else {
+                for (int a = 0; a < NH / 64; ++a)
+                  tma_load_3d_pair(dst + a * 8192, &p.map_w2, full_addr, ncol + a * 64, hrow, b);
+              }
+            }
+          });
     }
-  } else if (warp == 5) {
-    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+  } else if (warp == kWarpMma) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only, converged warp)
     if (half == 0) {
       const uint32_t issuer = elect_one();
       const uint32_t pair_mask = 0x3u << leader;
@@ -223,6 +326,8 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       int cs = 0;
       uint32_t cph = 0;
       bool ok = true;
+      long long w_acc = 0, w_g1 = 0, w_unit = 0, w_g2 = 0;   // clocks spent waiting (timeline builds only)
+      (void)w_acc; (void)w_g1; (void)w_unit; (void)w_g2;
       auto wait = [&](uint64_t* bp, uint32_t parity, uint32_t code) {
         bool r = mbar_wait(bp, parity, abort_word, code);
         r = __all_sync(0xffffffffu, r);
@@ -235,118 +340,140 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         tc_fence_after_sync();
         return r;
       };
-      auto advance = [&]() {
-        if (++cs == kStages) { cs = 0; cph ^= 1; }
+      // next ring granule: waits until its tile has landed in both CTAs; returns its shared-memory address
+      auto take = [&](uint32_t code, uint64_t*& empty_bar) -> uint32_t {
+        ok = wait(&bar->full[cs], cph, code);
+        const uint32_t addr = ring + cs * kGranule;
+        empty_bar = &bar->empty[cs];
+        if (++cs == kGranules) { cs = 0; cph ^= 1; }
+        return addr;
       };
-      auto g1 = [&](int i, int ks0, int ks1, bool first, bool last) {
-        const int hb = i & 1;
-        if (first && i >= 2) ok = wait_cluster(&bar->h_tmem_empty[hb], ((i >> 1) - 1) & 1, 0x300 + i);
-        if (first && lane == 0) DITTO_STAMP(i, 0);
-        for (int ks = ks0; ks < ks1 && ok; ++ks) {
-          ok = wait(&bar->full[cs], cph, 0x310 + i);
-          if (!ok) break;
-          const uint32_t st = ring + cs * kStageBytes;
-          const uint64_t da = umma_desc_sw128(st, 16, 1024);
-          const uint64_t db = p.w_oi ? umma_desc_sw128(st + 16384, 16, 1024) : umma_desc_sw128(st + 16384, 8192, 1024);
+      walk_item(chunks, my_rounds, ksteps1, ok,
+          [&](int i, int ks) {
+            // the accumulator is single: the previous chunk must be in the epilogue warps' registers
+            if (ks == 0 && i > 0) DITTO_TIMED(w_acc, ok = wait_cluster(&bar->h_tmem_empty, (i - 1) & 1, 0x300 + i));
+            if (!ok) return;
+            if (ks == 0 && lane == 0) DITTO_STAMP(16 * i + 0);
+            uint64_t *ex, *ew;
+            uint32_t sx = 0, sw = 0;
+            DITTO_TIMED(w_g1, sx = take(0x310 + i, ex));
+            if (!ok) return;
+            DITTO_TIMED(w_g1, sw = take(0x320 + i, ew));
+            if (!ok) return;
+            const uint64_t da = umma_desc_sw128(sx, 16, 1024);
+            const uint64_t db = p.w_oi ? umma_desc_sw128(sw, 16, 1024) : umma_desc_sw128(sw, 8192, 1024);
 #pragma unroll
-          for (int s4 = 0; s4 < 4; ++s4) {
-            const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
-            umma_ss_pair_elected(tmem_h + hb * kChunk, da + ((s4 * 32) >> 4), db + offb, idesc1, (ks | s4) ? 1u : 0u,
-                                 issuer);
-          }
-          umma_commit_pair_elected(&bar->empty[cs], pair_mask, issuer);
-          advance();
-        }
-        if (last && ok) umma_commit_pair_elected(&bar->h_tmem_full[hb], pair_mask, issuer);
-        if (last && lane == 0) DITTO_STAMP(i, 1);
-      };
-      auto g2 = [&](int u) {              // GEMM2 on hidden unit u: needs it in both CTAs' slots
-        const int sl = u % kUnits;
-        if (lane == 0 && (u & 7) == 0) DITTO_STAMP(u >> 3, 2);
-        ok = wait_cluster(&bar->h_pair[sl], (u / kUnits) & 1, 0x400 + (u >> 3));
-        if (lane == 0 && (u & 7) == 0) DITTO_STAMP(u >> 3, 3);
-        if (ok) ok = wait(&bar->full[cs], cph, 0x410 + (u >> 3));
-        if (ok) {
-          const uint32_t st = ring + cs * kStageBytes;
-          const uint64_t da = umma_desc_sw128(slots + sl * kUnitBytes, 16, 1024);
-          const uint64_t db = p.w_oi ? umma_desc_sw128(st, 16, 1024) : umma_desc_sw128(st, 8192, 1024);
+            for (int s4 = 0; s4 < 4; ++s4) {
+              const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
+              umma_ss_pair_elected(tmem_h, da + ((s4 * 32) >> 4), db + offb, idesc1, (ks | s4) ? 1u : 0u, issuer);
+            }
+            umma_commit_pair_elected(ex, pair_mask, issuer);
+            umma_commit_pair_elected(ew, pair_mask, issuer);
+            if (ks == ksteps1 - 1) {
+              umma_commit_pair_elected(&bar->h_tmem_full, pair_mask, issuer);
+              if (lane == 0) DITTO_STAMP(16 * i + 1);
+            }
+          },
+          [&](int n, int i, int kk, int src) {
+            (void)kk;
+            (void)src;
+            const int sl = n % kUnits;
+            if (lane == 0 && (n & 15) == 0) DITTO_STAMP(16 * i + 2);
+            DITTO_TIMED(w_unit, ok = wait_cluster(&bar->h_pair[sl], (n / kUnits) & 1, 0x400 + i));   // the unit is in both CTAs' slots
+            if (!ok) return;
+            if (lane == 0 && (n & 15) == 0) DITTO_STAMP(16 * i + 3);
+            uint64_t* ew;
+            uint32_t sw = 0;
+            DITTO_TIMED(w_g2, sw = take(0x410 + i, ew));
+            if (!ok) return;
+            const uint64_t da = umma_desc_sw128(slots + sl * kUnitBytes, 16, 1024);
+            const uint64_t db = p.w_oi ? umma_desc_sw128(sw, 16, 1024) : umma_desc_sw128(sw, 8192, 1024);
 #pragma unroll
-          for (int s4 = 0; s4 < 4; ++s4) {
-            const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
-            umma_ss_pair_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (u | s4) ? 1u : 0u, issuer);
-          }
-          umma_commit_pair_elected(&bar->empty[cs], pair_mask, issuer);
-          advance();
-          umma_commit_pair_elected(&bar->g2_done[sl], pair_mask, issuer);
-        }
-        if (lane == 0 && (u & 7) == 7) DITTO_STAMP(u >> 3, 4);
-      };
-      g1(0, 0, ksteps1, true, true);
-      if (rounds > 1 && ok) g1(1, 0, ksteps1, true, true);
-      for (int u = 0; u < units && ok; ++u) {
-        const int i = u >> 3, e = u & 7;
-        g2(u);
-        if (i + 2 < rounds && ok) g1(i + 2, e * ksteps1 / 8, (e + 1) * ksteps1 / 8, e == 0, e == 7);
-      }
+            for (int s4 = 0; s4 < 4; ++s4) {
+              const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
+              umma_ss_pair_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (n | s4) ? 1u : 0u, issuer);
+            }
+            umma_commit_pair_elected(ew, pair_mask, issuer);
+            umma_commit_pair_elected(&bar->g2_done[sl], pair_mask, issuer);
+            if (lane == 0 && (n & 15) == 15) DITTO_STAMP(16 * i + 4);
+          });
       if (ok) umma_commit_pair_elected(&bar->y_done, pair_mask, issuer);
+#ifdef DITTO_TRACE
+      if (lane == 0 && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
+        p.trace[400] = w_acc; p.trace[401] = w_g1; p.trace[402] = w_unit; p.trace[403] = w_g2;
+      }
+#endif
     }
-  } else if (warp == 6) {
+  } else if (warp == kWarpReady) {
     // ------------------------------------------------------------ ready relay (one thread)
     if (lane == 0) {
-      for (int u = 0; u < units; ++u) {
-        const int sl = u % kUnits;
+      for (int n = 0; n < units; ++n) {
+        const int sl = n % kUnits;
+        const int i = n / (4 * kPairs);
+        const int cr = min(kPairs, chunks - kPairs * i);
+        const uint32_t src = static_cast<uint32_t>((n - 4 * kPairs * i) % cr);
         // a peer pushes this unit: arm the slot's barrier for its bytes (the own pair's units arrive locally)
-        if (static_cast<uint32_t>((u >> 1) & 3) != pair) mbar_arrive_expect_tx(&bar->h_ready[sl], kUnitBytes);
-        if (!mbar_wait(&bar->h_ready[sl], (u / kUnits) & 1, abort_word, 0x500 + (u >> 3))) break;
+        if (src != pair) mbar_arrive_expect_tx(&bar->h_ready[sl], kUnitBytes);
+        if (!mbar_wait(&bar->h_ready[sl], (n / kUnits) & 1, abort_word, 0x500 + i)) break;
         mbar_arrive_cluster(&bar->h_pair[sl], leader);
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == kWarpFree) {
     // ------------------------------------------------------------ free relay (one thread)
     if (lane == 0) {
-      for (int u = 0; u < units; ++u) {
-        const int sl = u % kUnits;
-        if (!mbar_wait(&bar->g2_done[sl], (u / kUnits) & 1, abort_word, 0x580 + (u >> 3))) break;
-        if ((u & 7) == 7) DITTO_STAMP(u >> 3, 5);
-        // tell the CTA of this half that writes the slot next (the pair that owns unit u + kUnits)
-        if (u + kUnits < units)
-          mbar_arrive_cluster(&bar->slot_free[sl], 2 * static_cast<uint32_t>(((u + kUnits) >> 1) & 3) + half);
+      for (int n = 0; n + kUnits < units; ++n) {
+        const int sl = n % kUnits;
+        if (!mbar_wait(&bar->g2_done[sl], (n / kUnits) & 1, abort_word, 0x580 + n / (4 * kPairs))) break;
+        // tell the CTA of this half that writes the slot next: the owner of unit n + kUnits
+        const int m = n + kUnits;
+        const int i = m / (4 * kPairs);
+        const int cr = min(kPairs, chunks - kPairs * i);
+        const uint32_t owner = static_cast<uint32_t>((m - 4 * kPairs * i) % cr);
+        mbar_arrive_cluster(&bar->slot_free[sl], 2 * owner + half);
       }
     }
-  } else if (warp < 4) {
-    // ------------------------------------------------------------ epilogue
-    const int row = warp * 32 + lane;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  } else if (warp < kEpiWarps) {
+    // ------------------------------------------------------------ epilogue: eight warps
+    // Warp w: rows 32 (w % 4) ... + 31 (its TMEM lanes), column half w / 4 of every 64-column quarter.  All
+    // eight warps work on one quarter at a time, so the units leave in the order GEMM2 consumes them and
+    // each push has the whole outgoing bandwidth (about 16 B/clk per SM) instead of sharing it with a unit
+    // that is needed later.
+    const int grp = warp >> 2;            // column half of a quarter; half of the Y columns
+    const int row = (warp & 3) * 32 + lane;              // row of the CTA's 128 = TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     bool ok = true;
-    uint32_t free_waits[kUnits] = {};       // completed waits per slot: the parity of the next one
-    for (int i = 0; i < rounds; ++i) {
-      const int hb = i & 1;
-      ok = mbar_wait(&bar->h_tmem_full[hb], (i >> 1) & 1, abort_word, 0x600 + i);
+    uint32_t free_waits[kUnits] = {};     // completed waits per slot: the parity of the next one
+    uint32_t sync_uses = 0;               // completed phases of epi_sync
+    for (int i = 0; i < my_rounds; ++i) {
+      const int cr = min(kPairs, chunks - kPairs * i);
+      const int hcol0 = (c0 + i * kPairs + static_cast<int>(pair)) * kChunk;   // first hidden column of the chunk
+      ok = mbar_wait(&bar->h_tmem_full, i & 1, abort_word, 0x600 + i);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      if (threadIdx.x == 0) DITTO_STAMP(i, 6);
-      uint32_t h[kChunk];
-      tmem_ld_x128_wait(tmem_h + hb * kChunk + lane_base, h);
+      if (threadIdx.x == 0) DITTO_STAMP(16 * i + 6);
+      // the whole chunk leaves tensor memory first, so that the accumulator is released without waiting
+      // for a free slot (the next GEMM1 is ahead of this chunk's GEMM2 in the tensor-pipe order)
+      uint32_t pk[4][16];
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const int col = kk * kUnitCols + grp * 32;
+        const uint32_t* bias1 = p.b1 == nullptr ? nullptr
+                                                : reinterpret_cast<const uint32_t*>(p.b1) +
+                                                      (static_cast<size_t>(b) * p.L + hcol0 + col) / 2;
+        uint32_t h[32];
+        tmem_ld_x32_wait(tmem_h + lane_base + col, h);
+        act_pack<BF16>(h, bias1, p.act1, pk[kk]);
+      }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(&bar->h_tmem_empty[hb], leader);   // one arrival per warp, 8 per pair
-      uint32_t pk[kChunk / 2];
+      if (lane == 0) mbar_arrive_cluster(&bar->h_tmem_empty, leader);   // one arrival per warp, 16 per pair
+      if (threadIdx.x == 0) DITTO_STAMP(16 * i + 7);
 #pragma unroll
-      for (int j = 0; j < kChunk / 2; ++j) {
-        float v0 = __uint_as_float(h[2 * j]), v1 = __uint_as_float(h[2 * j + 1]);
-        if (p.relu) {
-          v0 = v0 > 0.f ? v0 : 0.f;       // if_then_else(D > 0, D, 0) as in the reference
-          v1 = v1 > 0.f ? v1 : 0.f;
-        }
-        pk[j] = pack2<BF16>(v0, v1);
-      }
-      const int g = i * kPairs + static_cast<int>(pair);   // this pair's chunk of the round
-#pragma unroll
-      for (int kk = 0; kk < 2; ++kk) {
-        const int u = 2 * g + kk;
-        const int sl = u % kUnits;
-        if (u >= kUnits) {
+      for (int kk = 0; kk < 4; ++kk) {
+        const int n = 4 * kPairs * i + cr * kk + static_cast<int>(pair);
+        const int sl = n % kUnits;
+        if (n >= kUnits) {
           // every pair has finished GEMM2 on the slot's previous unit: it may be overwritten
           uint32_t par = 0;
 #pragma unroll
@@ -356,28 +483,27 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
         }
-        if (threadIdx.x == 0 && kk == 0) DITTO_STAMP(i, 7);
         uint8_t* slot = smem + kOffSlots + sl * kUnitBytes;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          const int w = kk * 32 + 4 * ch;
-          const uint4 v = make_uint4(pk[w], pk[w + 1], pk[w + 2], pk[w + 3]);
-          *reinterpret_cast<uint4*>(slot + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int ch = grp * 4 + c4;      // 16-byte piece of the 128-byte row
+          const uint32_t* w = &pk[kk][4 * c4];
+          *reinterpret_cast<uint4*>(slot + row * 128 + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
         fence_proxy_async_smem();
         mbar_arrive(&bar->epi_sync);
-        ok = mbar_wait(&bar->epi_sync, kk, abort_word, 0x780 + i);   // two phases per round
+        ok = mbar_wait(&bar->epi_sync, sync_uses++ & 1, abort_word, 0x780 + i);   // all 256 threads have written
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (threadIdx.x == 0) {
           const uint32_t slot_addr = smem_u32(slot);
           const uint32_t bar_addr = smem_u32(&bar->h_ready[sl]);
           for (uint32_t d = 1; d < kPairs; ++d) {
-            const uint32_t peer = 2 * ((pair + d) % kPairs) + half;   // same rows, other pairs
+            const uint32_t peer = 2 * ((pair + d) % kPairs) + half;   // same rows, the other pairs (all consume the unit)
             bulk_copy_to_peer(map_to_cta(slot_addr, peer), slot, kUnitBytes, map_to_cta(bar_addr, peer));
           }
           mbar_arrive(&bar->h_ready[sl]);    // the local copy is in place
-          if (kk == 1) DITTO_STAMP(i, 8);
+          DITTO_STAMP(16 * i + 8 + kk);
         }
       }
       if (!ok) break;
@@ -388,21 +514,76 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     }
     if (ok) {
       tc_fence_after_sync();
-      uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) +
-                      ((static_cast<size_t>(b) * p.M + row0 + row) * p.N + static_cast<size_t>(pair) * NS) * 2;
-      for (int cc = 0; cc < NS; cc += 32) {
-        uint32_t o[32];
-        tmem_ld_x32_wait(tmem_y + lane_base + cc, o);
-        uint32_t w[16];
+      if (threadIdx.x == 0) DITTO_STAMP(500);
+      const int colg = grp * (NS / 2);      // this group's share of the CTA's NS accumulator columns
+      const size_t ycol0 = static_cast<size_t>(pair) * NS + colg;
+      if (!shared) {
+        uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(b) * p.M + row0 + row) * p.N + ycol0) * 2;
+        const uint32_t* bias2 = p.b2 == nullptr ? nullptr
+                                                : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(b) * p.N + ycol0) / 2;
+        for (int cc = 0; cc < NS / 2; cc += 32) {
+          uint32_t o[32];
+          tmem_ld_x32_wait(tmem_y + lane_base + colg + cc, o);
+          uint32_t w[16];
+          act_pack<BF16>(o, bias2 == nullptr ? nullptr : bias2 + cc / 2, p.act2, w);
+          if (row0 + row < p.M) {             // rows >= M of a partial last block were computed on zero-filled X
 #pragma unroll
-        for (int j = 0; j < 16; ++j) w[j] = pack2<BF16>(__uint_as_float(o[2 * j]), __uint_as_float(o[2 * j + 1]));
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(yrow + cc * 2 + j * 16) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          }
+        }
+      } else {
+        // this cluster's fp32 partial goes to its slab; bias and activation are applied when the slabs are added
+        const size_t mpad = static_cast<size_t>(p.row_blocks - p.whole_blocks) * 2 * kRows;   // rows of the shared blocks
+        const size_t slab = static_cast<size_t>(gridDim.y) * mpad * p.N;
+        const int srow0 = row0 - p.whole_blocks * 2 * kRows;                                  // this CTA's first row among them
+        float* prow = p.slabs + static_cast<size_t>(sp) * slab + (static_cast<size_t>(b) * mpad + srow0 + row) * p.N + ycol0;
+        for (int cc = 0; cc < NS / 2; cc += 32) {
+          uint32_t o[32];
+          tmem_ld_x32_wait(tmem_y + lane_base + colg + cc, o);
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(yrow + cc * 2 + j * 16) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          for (int j = 0; j < 8; ++j)
+            __stcg(reinterpret_cast<uint4*>(prow + cc) + j, make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+        }
+        __threadfence();
+        mbar_arrive(&bar->y_sync);
+        ok = mbar_wait(&bar->y_sync, 0, abort_word, 0x810);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok && threadIdx.x == 0) {
+          int* ctr = p.counters + (static_cast<size_t>(b) * (p.row_blocks - p.whole_blocks) + (rb - p.whole_blocks)) * kCluster + rank;
+          const int seen = atomicAdd(ctr, 1);
+          __threadfence();
+          bar->last_flag = (seen == p.parts - 1) ? 1u : 0u;
+        }
+        if (ok) {
+          mbar_arrive(&bar->y_sync);
+          ok = mbar_wait(&bar->y_sync, 1, abort_word, 0x820);
+          ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok && *reinterpret_cast<volatile uint32_t*>(&bar->last_flag) != 0u) {
+          // every part of this CTA's (rows, columns) region is in its slab: add them in slab order
+          __threadfence();
+          const int grow0 = rb * (2 * kRows) + static_cast<int>(half) * kRows;
+          const int rows = min(kRows, p.M - grow0);                 // <= 0 for a CTA whose rows lie past M
+          const size_t col0 = static_cast<size_t>(pair) * NS;
+          const uint32_t* bias2 = p.b2 == nullptr ? nullptr
+                                                  : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(b) * p.N + col0) / 2;
+          combine_slabs<BF16>(p.slabs + (static_cast<size_t>(b) * mpad + srow0) * p.N + col0, slab, p.parts, rows, NS,
+                              static_cast<size_t>(p.N), bias2, p.act2,
+                              reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(b) * p.M + grow0) * p.N + col0) * 2,
+                              static_cast<size_t>(p.N) * 2, static_cast<int>(threadIdx.x), kEpiWarps * 32);
+        }
       }
+      if (threadIdx.x == 0) DITTO_STAMP(501);
     }
   }
 
+  // After a wait has given up, copies this CTA issued (TMA loads into its ring, pushes into its peers'
+  // slots) may still be in flight; they complete within microseconds.  Give them that time before the
+  // shared memory and tensor memory they target are released.
+  if (*abort_word != 0u) {
+    for (int t = 0; t < 64; ++t) __nanosleep(1000);
+  }
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();                     // no CTA leaves while a peer may still write to it or use its operands
@@ -413,46 +594,144 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
 }
 
 // ------------------------------------------------------------------ host side
-bool mlp_pair_supported(int M, int N, int K, int L) {
-  return M % (2 * kRows) == 0 && L % (kPairs * kChunk) == 0 && K % 64 == 0 && N % (kPairs * 128) == 0 &&
-         N <= kPairs * 256;
+bool mlp_pair_supported(int N, int K, int L, int w_layout) {
+  if (L % kChunk || K % 16) return false;
+  if (w_layout == 1) return N % 256 == 0 && N <= kPairs * 256;   // K-major W2 tiles: N/8 rows, whole 32-column groups per epilogue group
+  return N % 512 == 0 && N <= kPairs * 256;                      // MN-major W2 tiles: whole 64-column atoms per CTA
+}
+
+namespace {
+
+template <bool BF16>
+cudaError_t pair_configure(int* slots_out) {
+  static std::atomic<unsigned long long> configured{0};
+  static std::atomic<int> cluster_slots[kMaxDevices];
+  int dev = 0;
+  cudaError_t e = current_device_checked(&dev);
+  if (e != cudaSuccess) return e;
+  if (!device_configured(configured, dev)) {
+    auto kern = mlp_pair_kernel<BF16>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    // how many clusters of eight the device holds at once: the unit the hidden split is sized against
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kCluster * 64, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess) return e;
+    cluster_slots[dev].store(n > 0 ? n : 1, std::memory_order_relaxed);
+    mark_device_configured(configured, dev);
+  }
+  *slots_out = cluster_slots[dev].load(std::memory_order_relaxed);
+  return cudaSuccess;
+}
+
+}  // namespace
+
+int mlp_pair_cluster_slots(bool bf16, int* slots) {
+  cudaError_t e = bf16 ? pair_configure<true>(slots) : pair_configure<false>(slots);
+  return e == cudaSuccess ? DITTO_OK : cuda_fail("mlp pair kernel set-up", e);
+}
+
+PairPlan mlp_pair_plan(int batch, int M, int L, int cluster_slots, bool allow_scratch) {
+  const int rbs = (M + 2 * kRows - 1) / (2 * kRows);
+  if (!allow_scratch) return {rbs, 1};
+  // fixed cost of an item in units of a 256-wide chunk: an item takes about 14 us + 3.7 us per chunk
+  return plan_row_blocks(batch, rbs, L / kChunk, kPairs, kMaxSlabs, cluster_slots, 3.8);
+}
+
+size_t mlp_pair_workspace_bytes(int batch, int M, int N, const PairPlan& plan) {
+  return plan_workspace_bytes(plan, batch, (M + 2 * kRows - 1) / (2 * kRows), 2 * kRows, N, kCluster);
 }
 
 int launch_mlp_pair(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
-                    bool bf16, int w_layout, int epilogue, int* status, cudaStream_t stream, long long* trace) {
-  if (!mlp_pair_supported(M, N, K, L) || batch > 65535) return DITTO_ERR_UNSUPPORTED;
+                    bool bf16, int w_layout, int act1, int act2, const void* b1, const void* b2, const PairPlan& plan,
+                    void* workspace, int* status, cudaStream_t stream, long long* trace) {
+  if (!mlp_pair_supported(N, K, L, w_layout) || batch > 65535) return DITTO_ERR_UNSUPPORTED;
+  int slots = 0;
+  int rc = mlp_pair_cluster_slots(bf16, &slots);
+  if (rc) return rc;
   const int NH = N / kPairs / 2;
+  const int rbs = (M + 2 * kRows - 1) / (2 * kRows);
   PairParams p;
   std::memset(&p, 0, sizeof(p));
-  bool ok = mlp_make_map(&p.map_x, bf16, x, K, static_cast<uint64_t>(batch) * M, 64, 128);
-  if (w_layout == 1) {
-    ok = ok && mlp_make_map(&p.map_w1, bf16, w1, K, static_cast<uint64_t>(batch) * L, 64, 64);
-    ok = ok && mlp_make_map(&p.map_w2, bf16, w2, L, static_cast<uint64_t>(batch) * N, 64, NH);
-  } else {
-    ok = ok && mlp_make_map(&p.map_w1, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, 64);
-    ok = ok && mlp_make_map(&p.map_w2, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, 64);
+  const uint64_t uM = M, uN = N, uK = K, uL = L, ub = batch;
+  {
+    const uint64_t dims[3] = {uK, uM, ub}, strides[2] = {uK * 2, uM * uK * 2};
+    const uint32_t box[3] = {64, kRows, 1};
+    rc = make_tensor_map(&p.map_x, bf16, x, 3, dims, strides, box);
+    if (rc) return rc;
   }
-  if (!ok) return DITTO_ERR_DRIVER;
+  if (w_layout == 1) {
+    const uint64_t d1[3] = {uK, uL, ub}, s1[2] = {uK * 2, uL * uK * 2};
+    const uint32_t bx1[3] = {64, kChunk / 2, 1};
+    rc = make_tensor_map(&p.map_w1, bf16, w1, 3, d1, s1, bx1);
+    if (rc) return rc;
+    const uint64_t d2[3] = {uL, uN, ub}, s2[2] = {uL * 2, uN * uL * 2};
+    const uint32_t bx2[3] = {64, static_cast<uint32_t>(NH), 1};
+    rc = make_tensor_map(&p.map_w2, bf16, w2, 3, d2, s2, bx2);
+    if (rc) return rc;
+  } else {
+    // [rows, cols] row-major seen as (64 columns, rows, cols / 64, batch): one box of 64 x 64 x atoms brings the
+    // 64-column swizzle atoms of an MN-major operand tile with a single TMA operation (atom a lands at
+    // a * 8 KB, exactly the operand layout)
+    const uint64_t d1[4] = {64, uK, uL / 64, ub}, s1[3] = {uL * 2, 128, uK * uL * 2};
+    const uint32_t bx1[4] = {64, 64, kChunk / 2 / 64, 1};
+    const uint64_t d2[4] = {64, uL, uN / 64, ub}, s2[3] = {uN * 2, 128, uL * uN * 2};
+    const uint32_t bx2[4] = {64, 64, static_cast<uint32_t>(NH / 64), 1};
+    p.w_atoms = make_tensor_map(&p.map_w1, bf16, w1, 4, d1, s1, bx1) == DITTO_OK &&
+                make_tensor_map(&p.map_w2, bf16, w2, 4, d2, s2, bx2) == DITTO_OK;
+    if (!p.w_atoms) {
+      // a driver that rejects the atom view: plain maps, one box per 64-column atom
+      const uint64_t e1[3] = {uL, uK, ub}, t1[2] = {uL * 2, uK * uL * 2};
+      const uint64_t e2[3] = {uN, uL, ub}, t2[2] = {uN * 2, uL * uN * 2};
+      const uint32_t bx[3] = {64, 64, 1};
+      rc = make_tensor_map(&p.map_w1, bf16, w1, 3, e1, t1, bx);
+      if (rc) return rc;
+      rc = make_tensor_map(&p.map_w2, bf16, w2, 3, e2, t2, bx);
+      if (rc) return rc;
+    }
+  }
+  const int shared_blocks = rbs - plan.whole_blocks;
+  if (plan.whole_blocks < 0 || shared_blocks < 0 || plan.parts < 1 || plan.parts > L / kChunk || plan.parts > kMaxSlabs) return DITTO_ERR_INVALID_ARG;
+  const bool split = shared_blocks > 0 && plan.parts > 1;
   p.y = y;
   p.M = M;
   p.N = N;
   p.K = K;
   p.L = L;
+  p.row_blocks = rbs;
+  p.whole_blocks = split ? plan.whole_blocks : rbs;
+  p.parts = split ? plan.parts : 1;
   p.w_oi = w_layout == 1;
-  p.relu = epilogue == 1;
+  p.act1 = act1;
+  p.act2 = act2;
+  p.b1 = b1;
+  p.b2 = b2;
   p.status = status;
   p.trace = trace;
-  dim3 grid(kCluster * (M / (2 * kRows)), batch, 1);
-  cudaError_t e;
-  if (bf16) {
-    e = cudaFuncSetAttribute(mlp_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e == cudaSuccess) mlp_pair_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(p);
-  } else {
-    e = cudaFuncSetAttribute(mlp_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e == cudaSuccess) mlp_pair_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  if (split) {
+    if (workspace == nullptr) return DITTO_ERR_WORKSPACE;
+    const size_t slab_bytes = static_cast<size_t>(plan.parts) * batch * shared_blocks * 2 * kRows * N * sizeof(float);
+    p.slabs = static_cast<float*>(workspace);
+    p.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + slab_bytes);
+    cudaError_t e = cudaMemsetAsync(p.counters, 0, static_cast<size_t>(batch) * shared_blocks * kCluster * sizeof(int), stream);
+    if (e != cudaSuccess) return cuda_fail("mlp pair counters", e);
   }
-  if (e == cudaSuccess) e = cudaGetLastError();
-  return e == cudaSuccess ? DITTO_OK : DITTO_ERR_CUDA;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(kCluster * (p.whole_blocks + (rbs - p.whole_blocks) * p.parts)), static_cast<unsigned>(batch), 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see grid_dependency_wait in the kernel
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = split ? 0 : 1;           // a launch with shared row blocks follows its own counter reset: plain stream order
+  cudaError_t e = bf16 ? cudaLaunchKernelEx(&cfg, mlp_pair_kernel<true>, p) : cudaLaunchKernelEx(&cfg, mlp_pair_kernel<false>, p);
+  return e == cudaSuccess ? DITTO_OK : cuda_fail("mlp pair kernel launch", e);
 }
 
 }  // namespace ditto_b200

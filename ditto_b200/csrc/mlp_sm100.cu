@@ -34,9 +34,11 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <cstring>
 
 #include "../../include/ditto_b200.h"
+#include "host_util.cuh"
 #include "mlp_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -83,7 +85,12 @@ struct MlpParams {
   CUtensorMap map_w1;  // IO: W1 [batch*K, L], box 64 x 64;  OI: W1 [batch*L, K], box 64 x 128
   CUtensorMap map_w2;  // IO: W2 [batch*L, N], box 64 x 64;  OI: W2 [batch*N, L], box 64 x N/4
   void* y;             // Y  [batch, M, N]
+  float* slabs;        // shared row blocks: fp32 partials [part][batch][shared row blocks * 128][N]
+  int* counters;       // shared row blocks: one per (batch, shared row block, CTA rank), zero at launch
   int M, N, K, L;
+  int row_blocks;      // ceil(M / 128)
+  int whole_blocks;    // the first row blocks are computed by one cluster each ...
+  int parts;           // ... the others by `parts` clusters, each taking a range of the hidden chunks
   int w_oi;            // 1: weights stored [out, in] (K-major B operands)
   int w_atoms;         // [in, out] weights: maps are 3-D atom views, one box per operand tile
   int act1, act2;      // 0 identity, 1 ReLU, 2 GELU (tanh form) after the first / second GEMM
@@ -103,29 +110,10 @@ struct Bars {
   uint64_t epi_sync;     // the 128 epilogue threads, once per round (bounded, unlike bar.sync)
   uint32_t tmem_base;
   uint32_t abort_word;
+  uint32_t last_flag;    // shared row blocks: this CTA is the last of its rank to finish the row block
 };
 static_assert(sizeof(Bars) <= 512, "barrier block too large");
 
-}  // namespace
-
-namespace {
-__device__ __forceinline__ float apply_act(float v, int act) {
-  if (act == 1) return v > 0.f ? v : 0.f;          // if_then_else(x > 0, x, 0) as in the reference's ReLU
-  if (act == 2) {                                  // the reference's GELU: 0.5 x (1 + tanh(0.79788456 x (1 + 0.044715 x^2)))
-    float t;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(v * 0.7978845608f * (1.0f + 0.044715f * v * v)));
-    return 0.5f * v * (1.0f + t);
-  }
-  return v;
-}
-template <bool BF16>
-__device__ __forceinline__ float2 unpack2(uint32_t w) {
-  if constexpr (BF16) {
-    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w));
-  } else {
-    return __half22float2(*reinterpret_cast<__half2*>(&w));
-  }
-}
 }  // namespace
 
 template <bool BF16>
@@ -141,10 +129,20 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t q = cluster_ctarank();
-  const int row0 = (blockIdx.x / kCluster) * kRows;
+  // Work item = (row block, range of hidden chunks).  The first whole_blocks row blocks of a batch entry are
+  // computed by one cluster each; each of the others is shared by `parts` clusters, whose fp32 partials of Y
+  // meet in the caller's scratch memory (the hidden activations themselves never leave the chip).
+  const int item = blockIdx.x / kCluster;
+  const bool shared = item >= p.whole_blocks;
+  const int nparts = shared ? p.parts : 1;
+  const int rb = shared ? p.whole_blocks + (item - p.whole_blocks) / p.parts : item;
+  const int sp = shared ? (item - p.whole_blocks) % p.parts : 0;
+  const int row0 = rb * kRows;
   const int b = blockIdx.y;
   const int NS = p.N / kCluster;          // this CTA's Y columns
-  const int chunks = p.L / kChunk;        // hidden chunks in all (any count); chunk n belongs to CTA n % 4
+  const int all_chunks = p.L / kChunk;
+  const int c0 = static_cast<int>(static_cast<long long>(sp) * all_chunks / nparts);           // first hidden chunk of the item
+  const int chunks = static_cast<int>(static_cast<long long>(sp + 1) * all_chunks / nparts) - c0;  // any count; chunk n of the item belongs to CTA n % 4
   const int units = 2 * chunks;           // 64-column halves of them
   // this CTA owns chunk 4 i + q for i < rounds: one round fewer than its peers if the last round is partial
   const int rounds = (chunks - static_cast<int>(q) + kCluster - 1) / kCluster;
@@ -167,6 +165,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     mbar_init(&bar->y_done, 1);
     mbar_init(&bar->epi_sync, kRows);
     bar->abort_word = 0;
+    bar->last_flag = 0;
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -209,7 +208,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         if (++ps == kStages) { ps = 0; pph ^= 1; }
       };
       auto load_g1 = [&](int i, int ks0, int ks1) {   // operands of k-steps [ks0, ks1) of GEMM1 for this CTA's chunk of round i
-        const int g = i * kCluster + static_cast<int>(q);
+        const int g = c0 + i * kCluster + static_cast<int>(q);   // hidden chunk
         for (int ks = ks0; ks < ks1 && ok; ++ks) {
           uint8_t* dst = acquire(2 * 16384, 0x100 + i);
           if (dst != nullptr) {
@@ -227,8 +226,8 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         }
       };
       auto load_g2 = [&](int u) {         // this CTA's W2 slice for hidden unit u (64 hidden columns)
-        const int g = u >> 1, kk = u & 1;
-        uint8_t* dst = acquire(64 * NS * 2, 0x200 + (g >> 2));
+        const int g = c0 + (u >> 1), kk = u & 1;             // hidden chunk and its half
+        uint8_t* dst = acquire(64 * NS * 2, 0x200 + (u >> 3));
         if (dst != nullptr) {
           if (p.w_oi) {
             tma_load_2d(dst, &p.map_w2, &bar->full[ps], g * kChunk + kk * 64, b * p.N + q * NS);
@@ -359,17 +358,8 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       uint32_t pk[kChunk / 2];
       const uint32_t* bias1 = p.b1 == nullptr ? nullptr
                                               : reinterpret_cast<const uint32_t*>(p.b1) +
-                                                    (static_cast<size_t>(b) * p.L + (i * kCluster + q) * kChunk) / 2;
-#pragma unroll
-      for (int j = 0; j < kChunk / 2; ++j) {
-        float v0 = __uint_as_float(h[2 * j]), v1 = __uint_as_float(h[2 * j + 1]);
-        if (bias1 != nullptr) {             // same address in every lane: one broadcast load
-          const float2 bb = unpack2<BF16>(__ldg(bias1 + j));
-          v0 += bb.x;
-          v1 += bb.y;
-        }
-        pk[j] = pack2<BF16>(apply_act(v0, p.act1), apply_act(v1, p.act1));
-      }
+                                                    (static_cast<size_t>(b) * p.L + (c0 + i * kCluster + q) * kChunk) / 2;
+      act_pack<BF16>(h, bias1, p.act1, pk);
       // the chunk leaves as two units of 64 columns
 #pragma unroll
       for (int kk = 0; kk < 2; ++kk) {
@@ -417,34 +407,71 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     }
     if (ok) {
       tc_fence_after_sync();
-      uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) +
-                      ((static_cast<size_t>(b) * p.M + row0 + row) * p.N + static_cast<size_t>(q) * NS) * 2;
       const uint32_t* bias2 = p.b2 == nullptr ? nullptr
                                               : reinterpret_cast<const uint32_t*>(p.b2) +
                                                     (static_cast<size_t>(b) * p.N + static_cast<size_t>(q) * NS) / 2;
-      for (int cc = 0; cc < NS; cc += 32) {
-        uint32_t o[32];
-        tmem_ld_x32_wait(tmem_y + lane_base + cc, o);
-        uint32_t w[16];
+      if (!shared) {
+        uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) +
+                        ((static_cast<size_t>(b) * p.M + row0 + row) * p.N + static_cast<size_t>(q) * NS) * 2;
+        for (int cc = 0; cc < NS; cc += 32) {
+          uint32_t o[32];
+          tmem_ld_x32_wait(tmem_y + lane_base + cc, o);
+          uint32_t w[16];
+          act_pack<BF16>(o, bias2 == nullptr ? nullptr : bias2 + cc / 2, p.act2, w);
+          if (row0 + row < p.M) {               // rows >= M of a partial last block were computed on zero-filled X
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float v0 = __uint_as_float(o[2 * j]), v1 = __uint_as_float(o[2 * j + 1]);
-          if (bias2 != nullptr) {
-            const float2 bb = unpack2<BF16>(__ldg(bias2 + cc / 2 + j));
-            v0 += bb.x;
-            v1 += bb.y;
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(yrow + cc * 2 + j * 16) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
           }
-          w[j] = pack2<BF16>(apply_act(v0, p.act2), apply_act(v1, p.act2));
         }
-        if (row0 + row < p.M) {               // rows >= M of a partial last block were computed on zero-filled X
+      } else {
+        // this cluster's fp32 partial goes to its slab; the last cluster to finish the row block (a counter per
+        // CTA rank) adds the slabs in slab order -- the result does not depend on which one came last -- and
+        // applies bias and activation
+        const size_t mpad = static_cast<size_t>(p.row_blocks - p.whole_blocks) * kRows;   // rows of the shared blocks
+        const size_t slab = static_cast<size_t>(gridDim.y) * mpad * p.N;
+        const int srow0 = row0 - p.whole_blocks * kRows;
+        float* region = p.slabs + (static_cast<size_t>(b) * mpad + srow0) * p.N + static_cast<size_t>(q) * NS;
+        float* prow = region + static_cast<size_t>(sp) * slab + static_cast<size_t>(row) * p.N;
+        for (int cc = 0; cc < NS; cc += 32) {
+          uint32_t o[32];
+          tmem_ld_x32_wait(tmem_y + lane_base + cc, o);
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(yrow + cc * 2 + j * 16) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          for (int j = 0; j < 8; ++j)
+            __stcg(reinterpret_cast<uint4*>(prow + cc) + j, make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+        }
+        __threadfence();
+        // epi_sync has completed two phases per round: its next phases have parities 0 and 1
+        mbar_arrive(&bar->epi_sync);
+        ok = mbar_wait(&bar->epi_sync, 0, abort_word, 0x810);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok && threadIdx.x == 0) {
+          int* ctr = p.counters + (static_cast<size_t>(b) * (p.row_blocks - p.whole_blocks) + (rb - p.whole_blocks)) * kCluster + q;
+          const int seen = atomicAdd(ctr, 1);
+          __threadfence();
+          bar->last_flag = (seen == p.parts - 1) ? 1u : 0u;
+        }
+        if (ok) {
+          mbar_arrive(&bar->epi_sync);
+          ok = mbar_wait(&bar->epi_sync, 1, abort_word, 0x820);
+          ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok && *reinterpret_cast<volatile uint32_t*>(&bar->last_flag) != 0u) {
+          __threadfence();
+          combine_slabs<BF16>(region, slab, p.parts, min(kRows, p.M - row0), NS, static_cast<size_t>(p.N), bias2, p.act2,
+                              reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(b) * p.M + row0) * p.N + static_cast<size_t>(q) * NS) * 2,
+                              static_cast<size_t>(p.N) * 2, static_cast<int>(threadIdx.x), kRows);
         }
       }
     }
   }
 
+  // After a wait has given up, copies this CTA issued (TMA loads into its ring, pushes into its peers'
+  // slots) may still be in flight; they complete within microseconds.  Give them that time before the
+  // shared memory they target is released.
+  if (*abort_word != 0u) {
+    for (int t = 0; t < 64; ++t) __nanosleep(1000);
+  }
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();                     // no CTA leaves while a peer may still write to it
@@ -457,122 +484,116 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
 // ------------------------------------------------------------------ host side
 namespace {
 
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-}  // namespace
-
-bool mlp_make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint32_t box_cols,
-                  uint32_t box_rows) {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
-      return false;
-    fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {box_cols, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // [batch, rows, cols] row-major, boxes of box_cols x box_rows inside one batch entry: rows past the end of
 // an entry are zero-filled instead of running into the next entry.
-bool mlp_make_map_3d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint64_t batch,
-                     uint32_t box_cols, uint32_t box_rows) {
-  void* ptr = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess)
-    return false;
-  EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  const cuuint64_t dims[3] = {cols, rows, batch};
-  const cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
-  const cuuint32_t box[3] = {box_cols, box_rows, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+int quad_map_3d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint64_t batch,
+                uint32_t box_cols, uint32_t box_rows) {
+  const uint64_t dims[3] = {cols, rows, batch}, strides[2] = {cols * 2, rows * cols * 2};
+  const uint32_t box[3] = {box_cols, box_rows, 1};
+  return make_tensor_map(map, bf16, base, 3, dims, strides, box);
 }
-
+int quad_map_2d(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint32_t box_cols,
+                uint32_t box_rows) {
+  const uint64_t dims[2] = {cols, rows}, strides[1] = {cols * 2};
+  const uint32_t box[2] = {box_cols, box_rows};
+  return make_tensor_map(map, bf16, base, 2, dims, strides, box);
+}
 // [rows, cols] row-major seen as (64 columns, rows, cols / 64): one box of 64 x box_rows x box_atoms
 // brings box_atoms 64-column swizzle atoms of an MN-major operand tile with a single TMA operation
 // (atom a lands at a * box_rows * 128 bytes, exactly the operand layout).
-bool mlp_make_atom_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows,
-                       uint32_t box_atoms) {
-  void* ptr = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess)
-    return false;
-  EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  const cuuint64_t dims[3] = {64, rows, cols / 64};
-  const cuuint64_t strides[2] = {cols * 2, 128};
-  const cuuint32_t box[3] = {64, box_rows, box_atoms};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+int quad_atom_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows,
+                  uint32_t box_atoms) {
+  const uint64_t dims[3] = {64, rows, cols / 64}, strides[2] = {cols * 2, 128};
+  const uint32_t box[3] = {64, box_rows, box_atoms};
+  return make_tensor_map(map, bf16, base, 3, dims, strides, box);
 }
 
-int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
-                     bool bf16, int w_layout, int epilogue, int* status, cudaStream_t stream, long long* trace,
-                     const void* b1, const void* b2, int act2) {
-  // CTA-pair kernel (2-SM MMAs, a third fewer operand bytes per CTA) on request.  It is correct
-  // but, as measured, slower than this kernel: its rounds are paced by the exchange of hidden chunks
-  // among eight CTAs instead of by the operand feed.
-  if (epilogue & 0x200) {
-    if (!mlp_pair_supported(M, N, K, L) || b1 || b2 || act2 || (epilogue & 0xff) > 1) return DITTO_ERR_UNSUPPORTED;
-    return launch_mlp_pair(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, epilogue & 0xff, status, stream, trace);
+template <bool BF16>
+cudaError_t quad_launch(const cudaLaunchConfig_t& cfg, const MlpParams& p) {
+  // the function attribute is set once per device (this instantiation's static)
+  static std::atomic<unsigned long long> configured{0};
+  int dev = 0;
+  cudaError_t e = current_device_checked(&dev);
+  if (e != cudaSuccess) return e;
+  if (!device_configured(configured, dev)) {
+    e = cudaFuncSetAttribute(mlp_chain_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    mark_device_configured(configured, dev);
   }
-  epilogue &= 0xff;
-  // Coverage of the cluster kernel: 128-row blocks (the last one may be partial); hidden size a multiple
-  // of the 128-wide chunk (the last round of four chunks may be partial); N/4 Y columns per CTA
-  // (<= 256 TMEM columns, whole 64-column swizzle atoms); K in 64-wide steps.
-  if (L % kChunk || K % 64) return DITTO_ERR_UNSUPPORTED;
-  if (N % (kCluster * 64) || N > kCluster * 256) return DITTO_ERR_UNSUPPORTED;
-  if (batch > 65535) return DITTO_ERR_UNSUPPORTED;
+  return cudaLaunchKernelEx(&cfg, mlp_chain_kernel<BF16>, p);
+}
+
+bool quad_supported(int N, int K, int L) {
+  // 128-row blocks (the last one may be partial); hidden size a multiple of the 128-wide chunk (the last
+  // round of four chunks may be partial); N/4 Y columns per CTA (<= 256 TMEM columns, whole 64-column
+  // swizzle atoms); K in 64-wide steps.
+  return L % kChunk == 0 && K % 64 == 0 && N % (kCluster * 64) == 0 && N <= kCluster * 256;
+}
+
+// fixed cost of an item in units of a 128-wide chunk: an item takes about 14 us + 2.1 us per chunk
+constexpr double kQuadFixedCost = 6.5;
+
+RowBlockPlan quad_plan(int batch, int M, int L, int cluster_slots, bool allow_scratch) {
+  const int rbs = (M + kRows - 1) / kRows;
+  if (!allow_scratch) return {rbs, 1};
+  return plan_row_blocks(batch, rbs, L / kChunk, kCluster, kMaxSlabs, cluster_slots, kQuadFixedCost);
+}
+
+int launch_mlp_quad(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
+                    bool bf16, int w_layout, int act1, int act2, const void* b1, const void* b2, const RowBlockPlan& plan,
+                    void* workspace, int* status, cudaStream_t stream, long long* trace) {
+  if (!quad_supported(N, K, L) || batch > 65535) return DITTO_ERR_UNSUPPORTED;
+  const int rbs = (M + kRows - 1) / kRows;
+  const int shared_blocks = rbs - plan.whole_blocks;
+  if (plan.whole_blocks < 0 || shared_blocks < 0 || plan.parts < 1 || plan.parts > L / kChunk || plan.parts > kMaxSlabs)
+    return DITTO_ERR_INVALID_ARG;
+  const bool split = shared_blocks > 0 && plan.parts > 1;
   const int NS = N / kCluster;
   MlpParams p;
   std::memset(&p, 0, sizeof(p));
-  bool ok = mlp_make_map_3d(&p.map_x, bf16, x, K, M, batch, 64, 128);
+  int rc = quad_map_3d(&p.map_x, bf16, x, K, M, batch, 64, 128);
+  if (rc) return rc;
   if (w_layout == 1) {
-    ok = ok && mlp_make_map(&p.map_w1, bf16, w1, K, static_cast<uint64_t>(batch) * L, 64, 128);
-    ok = ok && mlp_make_map(&p.map_w2, bf16, w2, L, static_cast<uint64_t>(batch) * N, 64, NS);
+    rc = quad_map_2d(&p.map_w1, bf16, w1, K, static_cast<uint64_t>(batch) * L, 64, 128);
+    if (rc) return rc;
+    rc = quad_map_2d(&p.map_w2, bf16, w2, L, static_cast<uint64_t>(batch) * N, 64, NS);
+    if (rc) return rc;
   } else {
     // one TMA operation per operand tile where the driver accepts the atom view, else one per atom
-    p.w_atoms = mlp_make_atom_map(&p.map_w1, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, 2) &&
-                mlp_make_atom_map(&p.map_w2, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, NS / 64);
+    p.w_atoms = quad_atom_map(&p.map_w1, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, 2) == DITTO_OK &&
+                quad_atom_map(&p.map_w2, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, NS / 64) == DITTO_OK;
     if (!p.w_atoms) {
-      ok = ok && mlp_make_map(&p.map_w1, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, 64);
-      ok = ok && mlp_make_map(&p.map_w2, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, 64);
+      rc = quad_map_2d(&p.map_w1, bf16, w1, L, static_cast<uint64_t>(batch) * K, 64, 64);
+      if (rc) return rc;
+      rc = quad_map_2d(&p.map_w2, bf16, w2, N, static_cast<uint64_t>(batch) * L, 64, 64);
+      if (rc) return rc;
     }
   }
-  if (!ok) return DITTO_ERR_DRIVER;
   p.y = y;
   p.M = M;
   p.N = N;
   p.K = K;
   p.L = L;
   p.w_oi = w_layout == 1;
-  p.act1 = epilogue;
+  p.act1 = act1;
   p.act2 = act2;
   p.b1 = b1;
   p.b2 = b2;
   p.status = status;
   p.trace = trace;
+  p.row_blocks = rbs;
+  p.whole_blocks = split ? plan.whole_blocks : rbs;
+  p.parts = split ? plan.parts : 1;
+  if (split) {
+    if (workspace == nullptr) return DITTO_ERR_WORKSPACE;
+    const size_t slab_bytes = static_cast<size_t>(plan.parts) * batch * shared_blocks * kRows * N * sizeof(float);
+    p.slabs = static_cast<float*>(workspace);
+    p.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + slab_bytes);
+    cudaError_t e = cudaMemsetAsync(p.counters, 0, static_cast<size_t>(batch) * shared_blocks * kCluster * sizeof(int), stream);
+    if (e != cudaSuccess) return cuda_fail("mlp chain counters", e);
+  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(kCluster * ((M + kRows - 1) / kRows), batch, 1);
+  cfg.gridDim = dim3(static_cast<unsigned>(kCluster * (p.whole_blocks + (rbs - p.whole_blocks) * p.parts)), batch, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
@@ -580,16 +601,75 @@ int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see grid_dependency_wait in the kernel
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e;
-  if (bf16) {
-    e = cudaFuncSetAttribute(mlp_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, mlp_chain_kernel<true>, p);
-  } else {
-    e = cudaFuncSetAttribute(mlp_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, mlp_chain_kernel<false>, p);
+  cfg.numAttrs = split ? 0 : 1;           // a launch with shared row blocks follows its own counter reset: plain stream order
+  const cudaError_t e = bf16 ? quad_launch<true>(cfg, p) : quad_launch<false>(cfg, p);
+  return e == cudaSuccess ? DITTO_OK : cuda_fail("mlp chain kernel launch", e);
+}
+
+}  // namespace
+
+int mlp_quad_cluster_slots(bool bf16, int* slots) {
+  static std::atomic<int> cached[2][kMaxDevices];
+  int dev = 0;
+  cudaError_t e = current_device_checked(&dev);
+  if (e != cudaSuccess) return cuda_fail("mlp chain kernel set-up", e);
+  int n = cached[bf16 ? 1 : 0][dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kCluster * 64, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    if (bf16) {
+      e = cudaFuncSetAttribute(mlp_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+      if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, mlp_chain_kernel<true>, &cfg);
+    } else {
+      e = cudaFuncSetAttribute(mlp_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+      if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, mlp_chain_kernel<false>, &cfg);
+    }
+    if (e != cudaSuccess) return cuda_fail("mlp chain kernel set-up", e);
+    cached[bf16 ? 1 : 0][dev].store(n > 0 ? n : 1, std::memory_order_relaxed);
   }
-  return e == cudaSuccess ? DITTO_OK : DITTO_ERR_CUDA;
+  *slots = n > 0 ? n : 1;
+  return DITTO_OK;
+}
+
+size_t mlp_workspace_bytes(int batch, int M, int N, int K, int L, bool bf16, int w_layout, int variant) {
+  const bool pair_ok = mlp_pair_supported(N, K, L, w_layout), quad_ok = quad_supported(N, K, L);
+  int slots = 0;
+  if (variant == kMlpQuad || (variant == kMlpAuto && quad_ok)) {
+    if (!quad_ok || mlp_quad_cluster_slots(bf16, &slots) != DITTO_OK) return 0;
+    return plan_workspace_bytes(quad_plan(batch, M, L, slots, true), batch, (M + kRows - 1) / kRows, kRows, N, kCluster);
+  }
+  if (!pair_ok || mlp_pair_cluster_slots(bf16, &slots) != DITTO_OK) return 0;
+  return mlp_pair_workspace_bytes(batch, M, N, mlp_pair_plan(batch, M, L, slots, true));
+}
+
+int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
+                     bool bf16, int w_layout, int act1, int act2, const void* b1, const void* b2, int variant,
+                     void* workspace, size_t ws_bytes, int* status, cudaStream_t stream, long long* trace) {
+  const bool pair_ok = mlp_pair_supported(N, K, L, w_layout);
+  if (variant == kMlpPair && !pair_ok) return DITTO_ERR_UNSUPPORTED;
+  // With few row blocks -- or a last wave that would leave most of the device idle -- some row blocks are
+  // shared by several clusters, if the caller provided the scratch memory that form needs.
+  int slots = 0;
+  // Default: the four-CTA kernel where it covers the shape (measured faster at the benchmark configuration:
+  // its clusters of four fill 132 of the 148 SMs, clusters of eight only 120), the pair kernel for the
+  // shapes only it covers (K that is not a multiple of 64).
+  if (variant == kMlpPair || (variant == kMlpAuto && pair_ok && !quad_supported(N, K, L))) {
+    int rc = mlp_pair_cluster_slots(bf16, &slots);
+    if (rc) return rc;
+    PairPlan plan = mlp_pair_plan(batch, M, L, slots, workspace != nullptr);
+    if (ws_bytes < mlp_pair_workspace_bytes(batch, M, N, plan)) plan = mlp_pair_plan(batch, M, L, slots, false);
+    return launch_mlp_pair(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, act1, act2, b1, b2, plan, workspace, status,
+                           stream, trace);
+  }
+  if (!quad_supported(N, K, L)) return DITTO_ERR_UNSUPPORTED;
+  int rc = mlp_quad_cluster_slots(bf16, &slots);
+  if (rc) return rc;
+  RowBlockPlan plan = quad_plan(batch, M, L, slots, workspace != nullptr);
+  if (ws_bytes < plan_workspace_bytes(plan, batch, (M + kRows - 1) / kRows, kRows, N, kCluster)) plan = quad_plan(batch, M, L, slots, false);
+  return launch_mlp_quad(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, act1, act2, b1, b2, plan, workspace, status, stream,
+                         trace);
 }
 
 }  // namespace ditto_b200

@@ -1,26 +1,46 @@
-// Launch interface of the fused GEMM -> activation -> GEMM kernel.
+// Launch interface of the fused GEMM -> activation -> GEMM kernels.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
+
+#include "host_util.cuh"
 
 namespace ditto_b200 {
 
-// Returns a DITTO_* status code (0 on success).  epilogue: activation after the first GEMM (0 identity,
-// 1 ReLU, 2 GELU; | 0x200 selects the CTA-pair variant); b1 / b2: optional 16-bit bias vectors
-// [batch, L] / [batch, N]; act2: activation after the second GEMM.
+// Which kernel a call takes.
+//   kMlpAuto    the four-CTA kernel where it covers the shape, else the CTA-pair kernel
+//   kMlpQuad    four-CTA clusters, single-SM MMAs (mlp_sm100.cu): L % 128 == 0, K % 64 == 0, N in {256, ..., 1024}
+//   kMlpPair    eight-CTA clusters of CTA pairs, 2-SM MMAs (mlp_pair_sm100.cu): L % 256 == 0, K % 16 == 0,
+//               N in {512, 1024} ([in, out] weights) or {256, 512, 768, 1024} ([out, in])
+enum MlpVariant { kMlpAuto = 0, kMlpQuad = 1, kMlpPair = 2 };
+
+// Returns a DITTO_* status code (0 on success).  act1 / act2: activation after the first / second GEMM
+// (0 identity, 1 ReLU, 2 GELU); b1 / b2: optional 16-bit bias vectors [batch, L] / [batch, N].
+// workspace / ws_bytes: optional scratch for the hidden-split form of the pair kernel (see
+// mlp_workspace_bytes); without it every row block is computed by one cluster.
 int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
-                     bool bf16, int w_layout, int epilogue, int* status, cudaStream_t stream,
-                     long long* trace = nullptr, const void* b1 = nullptr, const void* b2 = nullptr, int act2 = 0);
+                     bool bf16, int w_layout, int act1, int act2, const void* b1, const void* b2, int variant,
+                     void* workspace, size_t ws_bytes, int* status, cudaStream_t stream, long long* trace = nullptr);
 
-// 2-D row-major 16-bit tensor map with 128-byte-swizzled boxes; false if the driver entry point is missing
-// or the encoding is rejected.
-bool mlp_make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t cols, uint64_t rows, uint32_t box_cols,
-                  uint32_t box_rows);
+// Scratch bytes with which the chain runs fastest at this shape on the current device (0: none needed).
+size_t mlp_workspace_bytes(int batch, int M, int N, int K, int L, bool bf16, int w_layout, int variant);
 
-// CTA-pair (cta_group::2) variant: M % 256 == 0, L % 512 == 0, K % 64 == 0, N in {512, 1024}.
-bool mlp_pair_supported(int M, int N, int K, int L);
+// Clusters of four CTAs of the four-CTA kernel the current device holds at once (queried once per device).
+int mlp_quad_cluster_slots(bool bf16, int* slots);
+
+// ---- CTA-pair kernel (mlp_pair_sm100.cu)
+bool mlp_pair_supported(int N, int K, int L, int w_layout);
+// Clusters of eight CTAs the current device holds at once (queried once per device).
+int mlp_pair_cluster_slots(bool bf16, int* slots);
+using PairPlan = RowBlockPlan;   // 256-row blocks, 256-wide hidden chunks
+// The plan with the shortest modelled run time on a device that holds `cluster_slots` clusters at once;
+// without scratch memory: every row block whole.
+PairPlan mlp_pair_plan(int batch, int M, int L, int cluster_slots, bool allow_scratch);
+size_t mlp_pair_workspace_bytes(int batch, int M, int N, const PairPlan& plan);
 int launch_mlp_pair(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
-                    bool bf16, int w_layout, int epilogue, int* status, cudaStream_t stream, long long* trace = nullptr);
+                    bool bf16, int w_layout, int act1, int act2, const void* b1, const void* b2,
+                    const PairPlan& plan, void* workspace, int* status, cudaStream_t stream, long long* trace = nullptr);
 
 }  // namespace ditto_b200

@@ -54,11 +54,20 @@ def sum_over_ranks(value, device="cpu"):
 
 
 def gather_outputs(local, units_total):
-    """Optional all-gather of equal-sized per-rank output shards along dim 0 (NCCL over NVLink on
-    GPUs).  Not part of any timed region."""
+    """Optional all-gather of the per-rank output shards along dim 0 (NCCL over NVLink on GPUs), in unit
+    order.  Shards follow `shard_range`, so the last ranks may hold fewer rows than the first, or none:
+    every rank pads its shard to the common size ceil(units_total / world) before the collective (equal
+    counts on every rank, which is what all_gather requires) and the padding is cut off afterwards.
+    Not part of any timed region."""
     if not dist.is_initialized():
         return local
-    world = dist.get_world_size()
-    parts = [torch.empty_like(local) for _ in range(world)]
-    dist.all_gather(parts, local.contiguous())
+    world, rank = dist.get_world_size(), dist.get_rank()
+    per = -(-units_total // world)
+    lo, hi = shard_range(units_total, rank, world)
+    if local.shape[0] != hi - lo:
+        raise ValueError(f"rank {rank} holds {local.shape[0]} units, its shard of {units_total} has {hi - lo}")
+    padded = local.new_zeros((per,) + tuple(local.shape[1:]))
+    padded[:hi - lo] = local
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded)
     return torch.cat(parts, dim=0)[:units_total]

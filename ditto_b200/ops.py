@@ -143,13 +143,29 @@ def multi_head_attention(qkv, num_heads, out=None, scale=1.0, flags=0):
     return out
 
 
-def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO", pair_mma=False):
+_VARIANT_BITS = {"auto": 0, "pair": 0x200, "quad": 0x400}
+_workspaces = {}
+
+
+def _workspace(device, nbytes):
+    """A scratch buffer of at least `nbytes` on `device`, kept and grown per device (the C ABI itself
+    allocates nothing: scratch memory is the caller's, and this module is that caller)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = _workspaces[key] = torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{key}")
+    return buf
+
+
+def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO", variant="auto", workspace="auto"):
     """out = act(x @ w1) @ w2 with the hidden activations kept on chip.
 
     x [batch, M, K] or [M, K]; w1 [batch, K, L] / [K, L]; w2 [batch, L, N] / [L, N] when
     weight_layout == "IO" ([in, out]); "OI" takes the transposed [out, in] weights of
-    nn/functional/linear.py.  activation: "relu" or "identity".  pair_mma selects the kernel
-    variant built on 2-SM MMAs (M % 256 == 0, N in {512, 1024}).
+    nn/functional/linear.py.  activation: "relu" or "identity".  variant: "auto" (by shape), "pair"
+    (eight-CTA clusters of CTA pairs, 2-SM MMAs) or "quad" (four-CTA clusters).  workspace: "auto" (this
+    module keeps a scratch buffer of ditto_b200_workspace_bytes() per device), None (no scratch: every row
+    block is computed by one cluster) or a uint8 CUDA tensor.
     """
     global launch_count
     _check_tensor(x, "x")
@@ -184,12 +200,26 @@ def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO", p
         out3 = out.unsqueeze(0) if out.dim() == 2 else out
         if tuple(out3.shape) != (batch, M, N):
             raise ValueError(f"out has shape {tuple(out.shape)}, expected {(batch, M, N)}")
+    if variant not in _VARIANT_BITS:
+        raise ValueError(f"variant must be one of {sorted(_VARIANT_BITS)}")
     lib = _lib.load()
     with _on_device(x.device):
+        ws_ptr, ws_bytes = None, 0
+        if isinstance(workspace, torch.Tensor):
+            _check_tensor(workspace, "workspace", torch.uint8)
+            ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel()
+        elif isinstance(workspace, str) and workspace == "auto":
+            need = lib.ditto_b200_workspace_bytes(_lib.OP_GEMM_RELU_GEMM | _VARIANT_BITS[variant], batch, M, N, K, L,
+                                                  _DTYPE_CODE[x.dtype])
+            if need:
+                buf = _workspace(x.device, need)
+                ws_ptr, ws_bytes = buf.data_ptr(), buf.numel()
+        elif workspace is not None:
+            raise TypeError("workspace must be 'auto', None or a uint8 CUDA tensor")
         stream = torch.cuda.current_stream().cuda_stream
         rc = lib.ditto_b200_gemm_relu_gemm(x3.data_ptr(), w13.data_ptr(), w23.data_ptr(), out3.data_ptr(), batch, M, N,
                                            K, L, _DTYPE_CODE[x.dtype], wl,
-                                           (1 if activation == "relu" else 0) | (0x200 if pair_mma else 0), None, 0,
+                                           (1 if activation == "relu" else 0) | _VARIANT_BITS[variant], ws_ptr, ws_bytes,
                                            _status_ptr(x.device), stream)
     _lib.check(rc, "ditto_b200_gemm_relu_gemm")
     launch_count += 1

@@ -43,6 +43,19 @@ class ChainModule:
                 if t.dtype != _TORCH_DTYPE[s.dtype]:
                     raise TypeError(f"{nm}: dtype {t.dtype} does not match the compiled dtype {s.dtype}")
             return
+        if s.kind == "ffn":
+            names, want = self._ffn_signature()
+            if len(tensors) != len(want):
+                raise TypeError(f"{self.entry_name} takes {', '.join(names)}: {len(want)} tensors, got {len(tensors)}")
+            for t, shp, nm in zip(tensors, want, names):
+                if shp is not None and tuple(t.shape) != shp:
+                    raise ValueError(f"{nm}: shape {tuple(t.shape)} does not match the compiled shape {shp}")
+                if t.dtype != _TORCH_DTYPE[s.dtype]:
+                    raise TypeError(f"{nm}: dtype {t.dtype} does not match the compiled dtype {s.dtype}")
+            for t, nm in ((tensors[0], "x"), (tensors[-1], "out")):
+                if t.numel() != s.M * (s.K if nm == "x" else s.N):
+                    raise ValueError(f"{nm}: {t.numel()} elements do not match the compiled {s.M} rows")
+            return
         if len(tensors) != 4:
             raise TypeError(f"{self.entry_name} takes 3 inputs and 1 output, got {len(tensors)} tensors")
         want = [(s.batch, s.M, s.K), (s.batch, s.K, s.L), (s.batch, s.L, s.N), (s.batch, s.M, s.N)]
@@ -52,14 +65,38 @@ class ChainModule:
             if t.dtype != _TORCH_DTYPE[s.dtype]:
                 raise TypeError(f"{nm}: dtype {t.dtype} does not match the compiled dtype {s.dtype}")
 
+    def _ffn_signature(self):
+        """Argument names and shapes of a feed-forward module, in the layer's schedule_tensors order: the input,
+        the weights ([out, in] matrices, each followed by its bias if it has one), the output.  x and out keep
+        whatever leading dimensions the layer tensors have (None: only their sizes are checked)."""
+        s = self.schedule
+        names, shapes = ["x", "w1"], [None, (s.L, s.K)]
+        if s.bias1:
+            names.append("b1"); shapes.append((s.L,))
+        names.append("w2"); shapes.append((s.N, s.L))
+        if s.bias2:
+            names.append("b2"); shapes.append((s.N,))
+        names.append("out"); shapes.append(None)
+        return names, shapes
+
+    def _call_ffn(self, tensors):
+        s = self.schedule
+        args = dict(zip(self._ffn_signature()[0], tensors))
+        ops.ffn(args["x"].reshape(s.M, s.K), args["w1"], args.get("b1"), args["w2"], args.get("b2"),
+                out=args["out"].view(s.M, s.N), act1=s.act1, act2=s.act2, weight_layout="OI")
+
     def __call__(self, *tensors):
         # Shapes, dtypes and the argument order are fixed at build time, as in the reference, so a call
         # with the same tensor objects as the previous one (a benchmark loop, an inference engine with
         # pre-allocated buffers; held by weak reference) needs no re-validation: it fetches the current pointers and the current
         # stream and goes straight to the C ABI.  Anything else takes the checked path below once.
         fast = self._fast
-        if fast is not None and len(tensors) == len(fast[0]) and all(r() is t for r, t in zip(fast[0], tensors)):
-            fn, head, tail, dev_index = fast[1:]
+        # (identity alone is not enough: resize_ / set_ / transpose_ change a tensor's metadata in place, and the
+        # kernels address the compiled extent whatever the buffer holds -- so shape, dtype and layout are compared too)
+        if fast is not None and len(tensors) == len(fast[0]) and all(
+                r() is t and t.shape == shp and t.dtype == dt and t.is_contiguous()
+                for r, (shp, dt), t in zip(fast[0], fast[5], tensors)):
+            fn, head, tail, dev_index = fast[1:5]
             if torch.cuda.current_device() == dev_index:
                 rc = fn(*[t.data_ptr() for t in tensors], *head, *tail, torch.cuda.current_stream().cuda_stream)
                 if rc != 0:
@@ -70,6 +107,9 @@ class ChainModule:
         s = self.schedule
         if s.kind == "mha":
             ops.multi_head_attention(tensors[0], s.heads, out=tensors[1], scale=s.scale)
+        elif s.kind == "ffn":
+            self._call_ffn(tensors)
+            return                      # no prepared fast path: ops.ffn is the checked path every time
         else:
             a, b, c, f = tensors
             if s.kind == "softmax":
@@ -100,7 +140,8 @@ class ChainModule:
             head = (s.batch, s.M, s.N, s.K, s.L, code, 0, 1 if s.kind == "relu" else 0, None, 0)
         tail = (ops._status_word(dev).data_ptr(),)
         return (tuple(weakref.ref(t) for t in tensors), fn, head, tail,
-                dev.index if dev.index is not None else torch.cuda.current_device())
+                dev.index if dev.index is not None else torch.cuda.current_device(),
+                tuple((t.shape, t.dtype) for t in tensors))
 
     def get_function(self, name):
         if name != self.entry_name:

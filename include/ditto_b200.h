@@ -37,7 +37,9 @@ extern "C" {
 #define DITTO_DTYPE_FP16 0
 #define DITTO_DTYPE_BF16 1
 
-#define DITTO_EPILOGUE_PAIR_MMA 0x200
+/* or-ed into `epilogue` of ditto_b200_gemm_relu_gemm: force one of the two kernels (default: chosen by shape) */
+#define DITTO_EPILOGUE_PAIR_MMA 0x200 /* eight-CTA clusters of CTA pairs, 2-SM MMAs */
+#define DITTO_EPILOGUE_QUAD_MMA 0x400 /* four-CTA clusters, single-SM MMAs */
 
 #define DITTO_OP_BMM_SOFTMAX_BMM 0
 #define DITTO_OP_GEMM_RELU_GEMM 1
@@ -76,8 +78,14 @@ int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M
  * (benchmark/chimera/cuda/bmm_bmm_cuda.py:69-150).
  *   x [batch, M, K]; w1 [batch, K, L]; w2 [batch, L, N]; y [batch, M, N]
  *   w_layout 0: weights as above ([in, out]); 1: [out, in] as in nn/functional/linear.py:4-41
- *   epilogue 0: identity between the GEMMs; 1: ReLU; | DITTO_EPILOGUE_PAIR_MMA selects the variant built on
- *   2-SM MMAs over CTA pairs (M % 256 == 0, N in {512, 1024}; same results, currently slower) */
+ *   epilogue 0: identity between the GEMMs; 1: ReLU; | DITTO_EPILOGUE_PAIR_MMA / DITTO_EPILOGUE_QUAD_MMA
+ *   forces one of the two kernels (same results up to fp32 summation order; default: by shape)
+ *   workspace / ws_bytes: optional scratch memory (ditto_b200_workspace_bytes; contents irrelevant on entry,
+ *   undefined on return).  With few row blocks several clusters share a row block, each takes a range of the
+ *   hidden dimension and the fp32 partials of Y are added through the scratch memory in a fixed order (the
+ *   hidden activations still never leave the chip).  NULL or too small: one cluster per row block.
+ * Shapes: N == K <= 128 (any multiples of 16, [in, out] weights): the reference's own shape family;
+ * otherwise L % 128 == 0, K % 64 == 0 (K % 16 == 0 where L % 256 == 0), N in {256, 512, 768, 1024}; M any multiple of 16. */
 int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N,
                               int K, int L, int dtype, int w_layout, int epilogue, void* workspace,
                               size_t ws_bytes, int* status_word, void* stream);
@@ -94,8 +102,18 @@ int ditto_b200_ffn(const void* x, const void* w1, const void* b1, const void* w2
                    int M, int N, int K, int L, int dtype, int w_layout, int act1, int act2, int* status_word,
                    void* stream);
 
-/* Scratch bytes the op needs for this shape (0 when none). */
+/* Scratch bytes with which the op runs fastest at this shape on the current device (0 when none; every call
+ * also works without).  `op` may be or-ed with DITTO_EPILOGUE_PAIR_MMA / DITTO_EPILOGUE_QUAD_MMA to ask for the
+ * kernel that the same bits in `epilogue` select. */
 size_t ditto_b200_workspace_bytes(int op, int batch, int M, int N, int K, int L, int dtype);
+
+/* How many thread-block clusters of the MLP chain kernel the current device holds at once
+ * (cudaOccupancyMaxActiveClusters): the number of row blocks -- or, for the pair kernel, (row block,
+ * hidden range) items -- that run concurrently; a launch takes ceil(items / slots) waves.
+ * variant: DITTO_EPILOGUE_PAIR_MMA (clusters of eight) or DITTO_EPILOGUE_QUAD_MMA (clusters of four).
+ * Returns the count, or a negative DITTO_ERR_* code.  No counterpart in the reference (its schedules are
+ * sized by the hardware table of python/ditto/hardware/__init__.py:43-54). */
+int ditto_b200_mlp_cluster_slots(int dtype, int variant);
 
 /* Single-CTA check of one tcgen05 MMA chain: c[128, N] (fp32) = a[128, K] * b.
  *   b_mn 0: b is [N, K]; 1: b is [K, N].  a_tmem 1: the A operand is read from tensor memory.

@@ -33,8 +33,14 @@ def _worker(rank, world, port, out):
     slowest = D.max_over_ranks(1.0 + rank)
     units = D.sum_over_ranks(hi - lo)
     full = D.gather_outputs(local, wl.units)
+    # shards of unequal size (5 units over 2 ranks: 3 + 2; 1 unit over 2 ranks: 1 + 0)
+    uneven = {}
+    for total in (5, 1):
+        ulo, uhi = D.shard_range(total, rank, world)
+        mine = torch.arange(ulo, uhi, dtype=torch.float64).reshape(-1, 1) * 10
+        uneven[total] = D.gather_outputs(mine, total)
     if rank == 0:
-        torch.save({"slowest": slowest, "units": units, "full": full}, out)
+        torch.save({"slowest": slowest, "units": units, "full": full, "uneven": uneven}, out)
     D.barrier()
     torch.distributed.destroy_process_group()
 
@@ -50,3 +56,5 @@ def test_two_rank_sharding_and_reductions(tmp_path):
     q, _, _ = W.attention_inputs(wl, 0, wl.units)
     want = torch.from_numpy(q.sum(axis=(1, 2), dtype="float64")).reshape(-1, 1)
     assert torch.equal(res["full"], want)  # gather restores slice order
+    for total, got in res["uneven"].items():
+        assert torch.equal(got, torch.arange(total, dtype=torch.float64).reshape(-1, 1) * 10)

@@ -204,3 +204,76 @@ def test_model_level_flow_binds_and_schedules_attention_layers():
     assert sch.kind == "relu" and args == chain.schedule_tensors
     with pytest.raises(NotImplementedError):
         auto_schedule.get_tasks_scheduler_builder("ansor")
+
+
+def test_reference_package_name_and_module_paths_resolve():
+    """`import ditto` and the module paths the reference's callers use name the same module objects."""
+    import importlib
+    import ditto as ref_name
+    import ditto_b200
+    for path in ("auto_compute", "auto_compute.nn.functional", "auto_compute.nn.functional.bmm_chain",
+                 "auto_compute.nn.functional.activation", "auto_compute.nn.functional.linear",
+                 "auto_compute.nn.functional.softmax", "auto_compute.nn.module.self_attention",
+                 "auto_compute.nn.module.linear_module", "auto_compute.nn.model.transformer", "auto_tensorize",
+                 "auto_schedule", "chimera", "chimera.graph_fusion", "chimera.task_binding", "hardware", "runtime",
+                 "runtime.graph_engine"):
+        assert importlib.import_module("ditto." + path) is importlib.import_module("ditto_b200." + path), path
+    from ditto import auto_compute as ac2, auto_tensorize as at2
+    assert ac2 is ac and at2 is at and ref_name.build is ditto_b200.build
+
+
+def test_library_ops_of_the_path():
+    """softmax / ReLU / GELU / linear with the reference's names, argument order and op structure
+    (nn/functional/softmax.py:4-35, activation.py:9-39, linear.py:4-41)."""
+    F = ac.nn.functional
+    x = te.placeholder([4, 8, 16], "x", "float16")
+    w = te.placeholder([32, 16], "w", "float16")
+    b = te.placeholder([32], "b", "float16")
+    y = F.linear(x, w, b, out_dtype="float16")
+    assert y.shape == (4, 8, 32) and y.op.tag == "bias_add" and y.op.input_tensors[0].op.tag == "linear"
+    assert F.linear(x, w).op.reduce_axis[0].extent == 16
+    with pytest.raises(AssertionError):
+        F.linear(x, te.placeholder([32, 8], "w", "float16"))
+    assert F.ReLU(y).op.name == "ReLU" and F.GELU(y).op.name == "gelu" and F.GELU(y).shape == y.shape
+    s = F.softmax(x, dim=1)
+    assert s.op.name == "softmax" and s.op.input_tensors[1].op.name == "sum_val"
+    assert s.op.input_tensors[1].shape == (4, 16) and s.shape == x.shape
+    with pytest.raises(AssertionError):
+        F.softmax(x, dim=3)
+
+
+def test_graph_fusion_builds_the_feed_forward_layer():
+    """linear -> ReLU -> linear -> ReLU (nn/model/transformer.py:21-34) becomes one ffn layer; a lone linear + ReLU
+    (which the reference would fuse and hand to Ansor) is left alone and bound to "ansor"."""
+    from ditto_b200 import auto_schedule, chimera
+    from ditto_b200.auto_compute.nn.model import PositionwiseFeedForward
+    x = ac.layer_tensor([2, 128, 256], dtype="bfloat16")
+    y = PositionwiseFeedForward(256, 1024, dtype="bfloat16", out_dtype="bfloat16")(x)
+    g = chimera.graph_fusion(ac.graph([x], [y]))
+    (ffn,) = g.all_layers
+    assert ffn.name == "ffn_layer" and ffn.ffn_attrs == {"act1": "relu", "act2": "relu", "bias1": True, "bias2": True}
+    assert [tuple(t.shape) for t in ffn.weights] == [(1024, 256), (1024,), (256, 1024), (256,)]
+    sch = at.tensorize_cuda(ffn, None, hw.query_hw_param("gpu.cuda.B200"))
+    assert (sch.kind, sch.batch, sch.M, sch.N, sch.K, sch.L) == ("ffn", 1, 256, 256, 256, 1024)
+    assert (sch.act1, sch.act2, sch.bias1, sch.bias2) == ("relu", "relu", True, True)
+    assert ffn.gflops == 0 or ffn.gflops > 0          # the property still evaluates on the fused DAG
+    # GELU in the middle, no trailing activation, no biases
+    m = ac.nn.module
+    x2 = ac.layer_tensor([64, 128], dtype="float16")
+    l1, l2 = m.Linear(128, 512, dtype="float16", out_dtype="float16"), m.Linear(512, 256, dtype="float16", out_dtype="float16")
+    g2 = chimera.graph_fusion(ac.graph([x2], [l2(m.GELU()(l1(x2)))]))
+    (f2,) = g2.all_layers
+    assert f2.ffn_attrs == {"act1": "gelu", "act2": "identity", "bias1": False, "bias2": False}
+    # not a feed-forward pattern
+    x3 = ac.layer_tensor([64, 128], dtype="float16")
+    y3 = m.ReLU()(m.Linear(128, 512, dtype="float16", out_dtype="float16")(x3))
+    g3 = chimera.graph_fusion(ac.graph([x3], [y3]))
+    assert [l.name for l in g3.all_layers] == ["linear_layer", "relu_layer"]
+    bound = chimera.task_binding(auto_schedule.extract_tasks_from_graph(g3))
+    assert not bound["chimera"] and len(bound["ansor"]) == 2
+    # mixed dtypes are rejected where the kernel could not run them
+    x4 = ac.layer_tensor([64, 128], dtype="float16")
+    y4 = PositionwiseFeedForward(128, 512, dtype="float16", out_dtype="float32")(x4)
+    (f4,) = chimera.graph_fusion(ac.graph([x4], [y4])).all_layers
+    with pytest.raises(at.FusionError):
+        at.tensorize_cuda(f4, None, hw.query_hw_param("gpu.cuda.B200"))

@@ -31,39 +31,82 @@ def _inputs(seed, batch, M, N, K, L, dtype):
     return x, w1, w2
 
 
-def _run(cuda, x, w1, w2, dtype, act, layout="IO", pair=False):
+def _run(cuda, x, w1, w2, dtype, act, layout="IO", variant="auto", workspace="auto"):
     dx = _dev(x, dtype, cuda)
     if layout == "OI":
         d1, d2 = _dev(w1.transpose(0, 2, 1), dtype, cuda), _dev(w2.transpose(0, 2, 1), dtype, cuda)
     else:
         d1, d2 = _dev(w1, dtype, cuda), _dev(w2, dtype, cuda)
     out = torch.full((x.shape[0], x.shape[1], w2.shape[2]), float("nan"), dtype=TDT[dtype], device=cuda)  # poison
-    ops.gemm_relu_gemm(dx, d1, d2, out=out, activation=act, weight_layout=layout, pair_mma=pair)
+    ops.gemm_relu_gemm(dx, d1, d2, out=out, activation=act, weight_layout=layout, variant=variant, workspace=workspace)
     assert ops.device_status(cuda) == 0
     return out.float().cpu().numpy()
+
+
+# (batch, M, N, K, L).  Four-CTA kernel: L = 4096 gives eight rounds (every hidden-chunk slot and barrier phase
+# wraps several times); row counts that are not multiples of the 128-row block (208 tokens, a 16-row call);
+# hidden sizes that are not multiples of four chunks (the last round is partial; with fewer than four chunks
+# in all some CTAs own none).
+QUAD_SHAPES = ((2, 256, 512, 128, 1024), (1, 512, 1024, 256, 1536), (1, 256, 512, 64, 4096),
+               (1, 128, 256, 64, 512), (1, 128, 1024, 192, 512), (3, 384, 768, 960, 2048),
+               (2, 208, 768, 768, 1024), (1, 16, 256, 64, 512),
+               (1, 256, 512, 128, 768), (2, 128, 256, 64, 128), (1, 384, 1024, 192, 1664))
+# CTA-pair kernel (256-row blocks, 256-wide hidden chunks, four chunks a round): one full round; one full and one
+# partial round; four rounds (slots and phases wrap); two chunks in all, second CTA of each pair without rows;
+# a K that is not a multiple of 64 with 208 rows and three chunks; a single chunk and 16 rows; three
+# batch entries with a partial second row block.
+PAIR_SHAPES = ((2, 256, 512, 128, 1024), (1, 512, 1024, 256, 1536), (1, 256, 512, 64, 4096),
+               (1, 128, 1024, 192, 512), (2, 208, 1024, 80, 768), (1, 16, 512, 64, 256),
+               (3, 384, 512, 960, 2048))
+# Y widths only the [out, in] weight layout of the pair kernel covers (its W2 tiles are K-major)
+PAIR_SHAPES_OI = ((1, 256, 768, 128, 1024), (1, 272, 256, 64, 512))
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 @pytest.mark.parametrize("act", ["relu", "identity"])
 @pytest.mark.parametrize("layout", ["IO", "OI"])
-@pytest.mark.parametrize("pair", [False, True])
-def test_parity_small(cuda, oracle, dtype, act, layout, pair):
-    """Both kernel variants: single-CTA MMAs (default) and 2-SM MMAs over CTA pairs (M % 256 == 0 and
-    N in {512, 1024} only)."""
-    # L = 4096 gives eight rounds: every hidden-chunk slot and barrier phase wraps several times
-    shapes = ((2, 256, 512, 128, 1024), (1, 512, 1024, 256, 1536), (1, 256, 512, 64, 4096))
-    if not pair:
-        # the last two: row counts that are not multiples of the 128-row block (208 tokens, a 16-row call)
-        shapes += ((1, 128, 256, 64, 512), (1, 128, 1024, 192, 512), (3, 384, 768, 960, 2048),
-                   (2, 208, 768, 768, 1024), (1, 16, 256, 64, 512),
-                   # hidden sizes that are not multiples of four chunks: the last round is partial, with fewer
-                   # than four chunks in all some CTAs own none
-                   (1, 256, 512, 128, 768), (2, 128, 256, 64, 128), (1, 384, 1024, 192, 1664))
+@pytest.mark.parametrize("variant", ["quad", "pair"])
+def test_parity_small(cuda, oracle, dtype, act, layout, variant):
+    """Both kernels, each forced: four-CTA clusters with single-SM MMAs, and eight-CTA clusters of CTA
+    pairs with 2-SM MMAs (no scratch memory here: one cluster per row block)."""
+    shapes = QUAD_SHAPES if variant == "quad" else PAIR_SHAPES + (PAIR_SHAPES_OI if layout == "OI" else ())
     for (batch, M, N, K, L) in shapes:
         x, w1, w2 = _inputs(21, batch, M, N, K, L, dtype)
-        got = _run(cuda, x, w1, w2, dtype, act, layout, pair)
+        got = _run(cuda, x, w1, w2, dtype, act, layout, variant, workspace=None)
         want = oracle.gemm_act_gemm(x, w1, w2, 1 if act == "relu" else 0, ODT[dtype], wide=False)
-        assert_close(got, want, dtype, f"{dtype} {act} {layout} pair={pair} {(batch, M, N, K, L)}")
+        assert_close(got, want, dtype, f"{dtype} {act} {layout} {variant} {(batch, M, N, K, L)}")
+
+
+@pytest.mark.parametrize("layout", ["IO", "OI"])
+@pytest.mark.parametrize("variant", ["quad", "pair"])
+def test_shared_row_blocks(cuda, oracle, layout, variant):
+    """Few row blocks (or a last wave that would leave most of the device idle): some row blocks are shared
+    by several clusters, each takes a range of the hidden dimension, and the fp32 partials of Y are combined
+    through the caller's scratch memory.  Checked against the oracle, against the run without scratch memory
+    (same kernel, one cluster per row block) and for run-to-run identity."""
+    lib = _lib.load()
+    dtype = "bfloat16"
+    split_cases = 0
+    for (batch, M, N, K, L) in ((1, 16, 1024, 128, 4096), (1, 256, 1024, 256, 4096), (2, 208, 512, 64, 2048),
+                                (1, 2048, 1024, 256, 4096), (1, 4352, 512, 64, 1024)):
+        bits = _lib.EPILOGUE_PAIR_MMA if variant == "pair" else _lib.EPILOGUE_QUAD_MMA
+        need = lib.ditto_b200_workspace_bytes(_lib.OP_GEMM_RELU_GEMM | bits, batch, M, N, K, L, _lib.DTYPE_BF16)
+        if need == 0:
+            continue        # the planner found nothing to gain at this shape on this device
+        split_cases += 1
+        x, w1, w2 = _inputs(23, batch, M, N, K, L, dtype)
+        ws = torch.full((need,), 0xA5, dtype=torch.uint8, device=cuda)   # scratch arrives dirty
+        got = _run(cuda, x, w1, w2, dtype, "relu", layout, variant, workspace=ws)
+        want = oracle.gemm_act_gemm(x, w1, w2, 1, ODT[dtype], wide=False)
+        assert_close(got, want, dtype, f"shared {variant} {layout} {(batch, M, N, K, L)}")
+        again = _run(cuda, x, w1, w2, dtype, "relu", layout, variant, workspace=ws)
+        assert np.array_equal(got, again), "runs with shared row blocks differ"
+        whole = _run(cuda, x, w1, w2, dtype, "relu", layout, variant, workspace=None)
+        assert_close(got, whole, dtype, f"shared vs whole {variant} {layout} {(batch, M, N, K, L)}")
+        # a workspace that is too small is not an error: the call computes every row block whole
+        small = _run(cuda, x, w1, w2, dtype, "relu", layout, variant, workspace=ws[:1024])
+        assert np.array_equal(small, whole)
+    assert split_cases >= 3, "the planner shared row blocks in fewer cases than expected"
 
 
 def test_golden_vector(cuda):
@@ -111,7 +154,15 @@ def test_full_size_properties(cuda):
     assert torch.equal(base, ops.gemm_relu_gemm(x, w1, w2, activation="relu"))
     perm = torch.randperm(w.M // 128, device=cuda, generator=g)
     xp = x.view(-1, 128, w.K)[perm].reshape(w.M, w.K).contiguous()
-    assert torch.equal(ops.gemm_relu_gemm(xp, w1, w2, activation="relu"), base.view(-1, 128, w.N)[perm].reshape(w.M, w.N))
+    # Bit for bit where every row block is computed the same way (no scratch memory: one cluster per row block).
+    # With scratch memory the last row blocks may be shared by several clusters, whose fp32 partials are added in a
+    # different order than one accumulator adds them: there the permuted result agrees to rounding only.
+    whole = ops.gemm_relu_gemm(x, w1, w2, activation="relu", workspace=None)
+    assert torch.equal(ops.gemm_relu_gemm(xp, w1, w2, activation="relu", workspace=None),
+                       whole.view(-1, 128, w.N)[perm].reshape(w.M, w.N))
+    moved = ops.gemm_relu_gemm(xp, w1, w2, activation="relu").float()
+    want = base.view(-1, 128, w.N)[perm].reshape(w.M, w.N).float()
+    assert (moved - want).abs().max().item() <= 2e-2 * want.abs().max().item()
     lin = ops.gemm_relu_gemm((2 * x).bfloat16(), w1, w2, activation="identity").float()
     one = ops.gemm_relu_gemm(x, w1, w2, activation="identity").float()
     assert (lin - 2 * one).abs().max().item() <= 2e-2 * one.abs().max().item()
@@ -188,5 +239,6 @@ def test_ffn_with_bias(cuda, oracle, dtype, acts, layout):
         # no bias, ReLU then identity == the plain chain entry point, bit for bit
         if acts == ("relu", "relu"):
             a = ops.ffn(_dev(x, dtype, cuda), d1, None, d2, None, act1="relu", act2="identity", weight_layout=layout)
-            bq = ops.gemm_relu_gemm(_dev(x, dtype, cuda), d1, d2, activation="relu", weight_layout=layout)
+            bq = ops.gemm_relu_gemm(_dev(x, dtype, cuda), d1, d2, activation="relu", weight_layout=layout,
+                                    workspace=None)   # like ffn: no scratch memory, one cluster per row block
             assert torch.equal(a, bq)

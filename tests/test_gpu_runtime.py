@@ -151,3 +151,57 @@ def test_repeated_calls_take_the_prepared_path_and_stay_checked(cuda):
             func(a[:, :128].contiguous(), bm, c, f)            # other tensors are checked again
         func(a, bm, c, f)                                      # and the module still works afterwards
         assert ops.device_status(cuda) == 0
+
+
+@pytest.mark.parametrize("factory", [runtime.create_graph_engine, runtime.create_cuda_graph_engine])
+def test_model_level_flow_attention_then_feed_forward(cuda, oracle, factory):
+    """The whole sequence of benchmark/chimera/cuda/bert_inference.py:68-129 through `import ditto`: model ->
+    graph -> chimera.graph_fusion -> extract_tasks_from_graph -> chimera.task_binding ->
+    auto_schedule_bound_tasks -> build per key -> create_graph_engine -> compile / run / get_outputs /
+    timeit(n).value, on a block of multi-head attention followed by the feed-forward block
+    (linear + bias -> ReLU -> linear + bias -> ReLU, weights [out, in]); the output is compared with the
+    oracle evaluated layer by layer."""
+    import ditto as ref_name                      # the reference's package name resolves to this package
+    from ditto import auto_schedule, chimera
+    from ditto.auto_compute.nn.model import TransformerBlock
+    assert ref_name.runtime is runtime
+    batch, M, heads, hidden, d_ff, dtype = 2, 256, 4, 256, 1024, "float16"
+    qkv_lt = ac.layer_tensor([batch, M, 3 * hidden], name="qkv", dtype=dtype)
+    model = TransformerBlock(hidden, heads, d_ff, dtype=dtype, mma_in_dtype=dtype)
+    out_lt = model(qkv_lt)
+    graph = ac.graph([qkv_lt], [out_lt])
+    assert [l.name for l in graph.all_layers] == ["multi_head_attention_mma_layer", "linear_layer", "relu_layer",
+                                                  "linear_layer", "relu_layer"]
+    graph = chimera.graph_fusion(graph)
+    assert [l.name for l in graph.all_layers] == ["multi_head_attention_mma_layer", "ffn_layer"]
+    option = auto_schedule.ScheduleOption("cuda", trials=10, device_name="gpu.cuda.B200", dtype=dtype,
+                                          mma_in_dtype=dtype, mma_acc_dtype="float32")
+    tasks = auto_schedule.extract_tasks_from_graph(graph)
+    bound = chimera.task_binding(tasks)
+    assert len(bound["chimera"]) == 2 and not bound["ansor"]
+    schedules = auto_schedule.auto_schedule_bound_tasks(bound, option)
+    built = {key: ditto.build(sch, args, "cuda") for key, (sch, args) in schedules.items()}
+    assert sorted(m.schedule.kind for m in built.values()) == ["ffn", "mha"]
+    engine = factory(graph, built, "cuda")
+    engine.get_function("init")()
+    rng = np.random.default_rng(47)
+    qkv = W._round((rng.standard_normal((batch, M, 3 * hidden)) * 0.5).astype(np.float32), dtype)
+    w1 = W._round((rng.standard_normal((d_ff, hidden)) * hidden ** -0.5).astype(np.float32), dtype)
+    b1 = W._round((rng.standard_normal(d_ff) * 0.5).astype(np.float32), dtype)
+    w2 = W._round((rng.standard_normal((hidden, d_ff)) * d_ff ** -0.5).astype(np.float32), dtype)
+    b2 = W._round((rng.standard_normal(hidden) * 0.5).astype(np.float32), dtype)
+    ffn_layer = graph.all_layers[1]
+    for tensor, value in zip(ffn_layer.weights, (w1, b1, w2, b2)):
+        engine.get_function("set_weight")(ffn_layer, tensor, torch.from_numpy(value))
+    engine.get_function("set_inputs")(torch.from_numpy(qkv))
+    engine.get_function("compile")()
+    engine.get_function("run")()
+    (out,) = engine.get_function("get_outputs")()
+    assert ops.device_status(cuda) == 0
+    attn = W._round(_mha_reference(oracle, qkv, heads, 0, 1.0), dtype)          # the layer writes fp16
+    want = oracle.ffn(attn.reshape(1, batch * M, hidden), np.ascontiguousarray(w1.T)[None], b1[None],
+                      np.ascontiguousarray(w2.T)[None], b2[None], 1, 1, 0).reshape(batch, M, hidden)
+    assert_close(out.float().cpu().numpy(), want, dtype, "attention + feed-forward through the graph engine",
+                 scale=float(np.abs(want).max()))
+    cost = engine.get_function("timeit")(20).value
+    assert 0 < cost < 5
