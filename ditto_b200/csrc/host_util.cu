@@ -109,7 +109,7 @@ int make_tensor_map(CUtensorMap* map, bool bf16, const void* base, int rank, con
 }
 
 RowBlockPlan plan_row_blocks(int batch, int row_blocks, int chunks, int min_chunks, int max_parts, int cluster_slots,
-                             double fixed_cost) {
+                             double fixed_cost, double shared_cost) {
   RowBlockPlan best = {row_blocks, 1};
   if (cluster_slots <= 1 || chunks < 2 * min_chunks || max_parts < 2) return best;
   if (static_cast<long long>(batch) * row_blocks > 4096) return best;   // large problems: nothing to gain at the tail
@@ -117,7 +117,7 @@ RowBlockPlan plan_row_blocks(int batch, int row_blocks, int chunks, int min_chun
   // shapes are kept per thread (a plan is a pure function of the arguments).
   struct Memo {
     int batch, row_blocks, chunks, min_chunks, max_parts, slots;
-    double fixed;
+    double fixed, shared;
     RowBlockPlan plan;
     bool valid;
   };
@@ -127,7 +127,7 @@ RowBlockPlan plan_row_blocks(int batch, int row_blocks, int chunks, int min_chun
   for (int i = 0; i < kMemo; ++i) {
     const Memo& m = memo[i];
     if (m.valid && m.batch == batch && m.row_blocks == row_blocks && m.chunks == chunks && m.min_chunks == min_chunks &&
-        m.max_parts == max_parts && m.slots == cluster_slots && m.fixed == fixed_cost)
+        m.max_parts == max_parts && m.slots == cluster_slots && m.fixed == fixed_cost && m.shared == shared_cost)
       return m.plan;
   }
   constexpr int kMaxSlots = 160;
@@ -156,15 +156,14 @@ RowBlockPlan plan_row_blocks(int batch, int row_blocks, int chunks, int min_chun
   for (int parts = 2; parts <= limit; ++parts) {
     const int max_shared = row_blocks < slots ? row_blocks : slots;
     for (int sh = 1; sh <= max_shared; ++sh) {
-      // the partials' round trip through scratch memory and the last cluster's extra pass have to be worth it
-      const double t = makespan(sh, parts) + 0.5 * fixed_cost;
+      const double t = makespan(sh, parts) + shared_cost;
       if (t < best_t * 0.97) {
         best_t = t;
         best = {row_blocks - sh, parts};
       }
     }
   }
-  memo[memo_next] = {batch, row_blocks, chunks, min_chunks, max_parts, cluster_slots, fixed_cost, best, true};
+  memo[memo_next] = {batch, row_blocks, chunks, min_chunks, max_parts, cluster_slots, fixed_cost, shared_cost, best, true};
   memo_next = (memo_next + 1) % kMemo;
   return best;
 }

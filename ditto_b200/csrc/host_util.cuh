@@ -37,9 +37,11 @@ struct RowBlockPlan {
 // The plan with the shortest modelled run time on a device that holds `cluster_slots` clusters at once.
 // Clusters are dispatched in item order to whichever place frees up first; an item's duration is modelled as
 // its hidden chunks plus `fixed_cost` (start-up and write-out, in chunk units, from timelines of the kernel).
+// `shared_cost` is what sharing adds to the run (the partials' round trip through scratch memory, the last
+// cluster's combining pass, the counter reset in front of the launch), in the same units.
 // A part never gets fewer than `min_chunks` chunks nor are there more than `max_parts` parts.
 RowBlockPlan plan_row_blocks(int batch, int row_blocks, int chunks, int min_chunks, int max_parts, int cluster_slots,
-                             double fixed_cost);
+                             double fixed_cost, double shared_cost);
 // Scratch bytes of a plan: parts slabs of fp32 [batch][shared rows][N] and one counter per (batch, shared
 // row block, CTA of the cluster).
 size_t plan_workspace_bytes(const RowBlockPlan& plan, int batch, int row_blocks, int rows_per_block, int N,

@@ -78,35 +78,35 @@ __device__ __forceinline__ float act_apply_rt(float v, int act) {
 // Last step of a row block that several clusters shared: add the clusters' fp32 partials of a
 // rows x cols region of Y (one slab per cluster, `slab_stride` floats apart, row pitch `ld` floats) in
 // slab order, apply bias and activation, write the 16-bit result.  `nthreads` threads of one CTA call it with
-// tid = 0 .. nthreads - 1.  Two float4 per thread and all slabs' loads are issued before the first add:
-// with one load in flight at a time this pass is bound by L2 latency (measured 100 us for 128 x 256 x 8
-// slabs), with 2 x parts in flight it takes a few microseconds.
+// tid = 0 .. nthreads - 1.  Every thread issues the loads of J float4 positions in all P slabs before the
+// first add: with one load in flight at a time this pass is bound by L2 latency (measured 100 us for
+// 128 x 256 x 8 slabs), with J x P = 16 in flight it takes a few microseconds.
 constexpr int kMaxSlabs = 8;
-template <bool BF16>
-__device__ __forceinline__ void combine_slabs(const float* slab0, size_t slab_stride, int parts, int rows, int cols,
-                                              size_t ld, const uint32_t* bias, int act, uint8_t* y, size_t y_pitch_bytes,
-                                              int tid, int nthreads) {
+template <bool BF16, int J, int P>
+__device__ __forceinline__ void combine_slabs_fixed(const float* slab0, size_t slab_stride, int parts, int rows, int cols,
+                                                    size_t ld, const uint32_t* bias, int act, uint8_t* y,
+                                                    size_t y_pitch_bytes, int tid, int nthreads) {
   const int per_row = cols / 4;
   const int total = rows * per_row;
-  for (int base = 0; base < total; base += 2 * nthreads) {
-    float4 v[2][kMaxSlabs];
-    int r[2], c[2];
+  for (int base = 0; base < total; base += J * nthreads) {
+    float4 v[J][P];
+    int r[J], c[J];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < J; ++j) {
       const int idx = base + j * nthreads + tid;
       r[j] = idx / per_row;
       c[j] = (idx - r[j] * per_row) * 4;
 #pragma unroll
-      for (int s = 0; s < kMaxSlabs; ++s)
+      for (int s = 0; s < P; ++s)
         if (idx < total && s < parts)
           v[j][s] = __ldcg(reinterpret_cast<const float4*>(slab0 + static_cast<size_t>(s) * slab_stride + static_cast<size_t>(r[j]) * ld + c[j]));
     }
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < J; ++j) {
       if (base + j * nthreads + tid >= total) continue;
       float4 acc = v[j][0];
 #pragma unroll
-      for (int s = 1; s < kMaxSlabs; ++s)
+      for (int s = 1; s < P; ++s)
         if (s < parts) {
           acc.x += v[j][s].x; acc.y += v[j][s].y; acc.z += v[j][s].z; acc.w += v[j][s].w;
         }
@@ -119,6 +119,17 @@ __device__ __forceinline__ void combine_slabs(const float* slab0, size_t slab_st
       *reinterpret_cast<uint2*>(y + static_cast<size_t>(r[j]) * y_pitch_bytes + c[j] * 2) = out;
     }
   }
+}
+template <bool BF16>
+__device__ __forceinline__ void combine_slabs(const float* slab0, size_t slab_stride, int parts, int rows, int cols,
+                                              size_t ld, const uint32_t* bias, int act, uint8_t* y, size_t y_pitch_bytes,
+                                              int tid, int nthreads) {
+  if (parts <= 2)
+    combine_slabs_fixed<BF16, 8, 2>(slab0, slab_stride, parts, rows, cols, ld, bias, act, y, y_pitch_bytes, tid, nthreads);
+  else if (parts <= 4)
+    combine_slabs_fixed<BF16, 4, 4>(slab0, slab_stride, parts, rows, cols, ld, bias, act, y, y_pitch_bytes, tid, nthreads);
+  else
+    combine_slabs_fixed<BF16, 2, kMaxSlabs>(slab0, slab_stride, parts, rows, cols, ld, bias, act, y, y_pitch_bytes, tid, nthreads);
 }
 
 // Bulk copy from this CTA's shared memory into a peer's; completion (bytes) on the peer's mbarrier.

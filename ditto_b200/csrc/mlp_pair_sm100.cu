@@ -555,24 +555,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           __threadfence();
           bar->last_flag = (seen == p.parts - 1) ? 1u : 0u;
         }
-        if (ok) {
-          mbar_arrive(&bar->y_sync);
-          ok = mbar_wait(&bar->y_sync, 1, abort_word, 0x820);
-          ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok && *reinterpret_cast<volatile uint32_t*>(&bar->last_flag) != 0u) {
-          // every part of this CTA's (rows, columns) region is in its slab: add them in slab order
-          __threadfence();
-          const int grow0 = rb * (2 * kRows) + static_cast<int>(half) * kRows;
-          const int rows = min(kRows, p.M - grow0);                 // <= 0 for a CTA whose rows lie past M
-          const size_t col0 = static_cast<size_t>(pair) * NS;
-          const uint32_t* bias2 = p.b2 == nullptr ? nullptr
-                                                  : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(b) * p.N + col0) / 2;
-          combine_slabs<BF16>(p.slabs + (static_cast<size_t>(b) * mpad + srow0) * p.N + col0, slab, p.parts, rows, NS,
-                              static_cast<size_t>(p.N), bias2, p.act2,
-                              reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(b) * p.M + grow0) * p.N + col0) * 2,
-                              static_cast<size_t>(p.N) * 2, static_cast<int>(threadIdx.x), kEpiWarps * 32);
-        }
+        // (the combining pass runs below, on all threads of the CTA, once the other warps are done too)
       }
       if (threadIdx.x == 0) DITTO_STAMP(501);
     }
@@ -586,6 +569,21 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (shared && bar->last_flag != 0u && bar->abort_word == 0u) {
+    // Every part of this CTA's (rows, columns) region of a shared row block is in its slab, and this
+    // cluster was the last to get there: add the slabs in slab order, apply bias and activation, write Y.
+    // All warps take part -- the pass is bound by how many loads the CTA keeps in flight.
+    __threadfence();
+    const size_t mpad = static_cast<size_t>(p.row_blocks - p.whole_blocks) * 2 * kRows;
+    const size_t slab = static_cast<size_t>(gridDim.y) * mpad * p.N;
+    const size_t col0 = static_cast<size_t>(pair) * NS;
+    const uint32_t* bias2 = p.b2 == nullptr ? nullptr
+                                            : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(b) * p.N + col0) / 2;
+    combine_slabs<BF16>(p.slabs + (static_cast<size_t>(b) * mpad + (row0 - p.whole_blocks * 2 * kRows)) * p.N + col0, slab,
+                        p.parts, min(kRows, p.M - row0), NS, static_cast<size_t>(p.N), bias2, p.act2,
+                        reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(b) * p.M + row0) * p.N + col0) * 2,
+                        static_cast<size_t>(p.N) * 2, static_cast<int>(threadIdx.x), kThreads);
+  }
   cluster_sync_all();                     // no CTA leaves while a peer may still write to it or use its operands
   if (warp == 0) {
     tmem_dealloc_pair(tmem_base, 512);
@@ -638,8 +636,8 @@ int mlp_pair_cluster_slots(bool bf16, int* slots) {
 PairPlan mlp_pair_plan(int batch, int M, int L, int cluster_slots, bool allow_scratch) {
   const int rbs = (M + 2 * kRows - 1) / (2 * kRows);
   if (!allow_scratch) return {rbs, 1};
-  // fixed cost of an item in units of a 256-wide chunk: an item takes about 14 us + 3.7 us per chunk
-  return plan_row_blocks(batch, rbs, L / kChunk, kPairs, kMaxSlabs, cluster_slots, 3.8);
+  // in units of a 256-wide chunk: an item takes about 14 us + 3.7 us per chunk, sharing adds about 20 us
+  return plan_row_blocks(batch, rbs, L / kChunk, kPairs, kMaxSlabs, cluster_slots, 3.8, 5.5);
 }
 
 size_t mlp_pair_workspace_bytes(int batch, int M, int N, const PairPlan& plan) {

@@ -441,7 +441,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
             __stcg(reinterpret_cast<uint4*>(prow + cc) + j, make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
         }
         __threadfence();
-        // epi_sync has completed two phases per round: its next phases have parities 0 and 1
+        // epi_sync has completed two phases per round: its next phase has parity 0
         mbar_arrive(&bar->epi_sync);
         ok = mbar_wait(&bar->epi_sync, 0, abort_word, 0x810);
         ok = __all_sync(0xffffffffu, ok);
@@ -451,17 +451,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           __threadfence();
           bar->last_flag = (seen == p.parts - 1) ? 1u : 0u;
         }
-        if (ok) {
-          mbar_arrive(&bar->epi_sync);
-          ok = mbar_wait(&bar->epi_sync, 1, abort_word, 0x820);
-          ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok && *reinterpret_cast<volatile uint32_t*>(&bar->last_flag) != 0u) {
-          __threadfence();
-          combine_slabs<BF16>(region, slab, p.parts, min(kRows, p.M - row0), NS, static_cast<size_t>(p.N), bias2, p.act2,
-                              reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(b) * p.M + row0) * p.N + static_cast<size_t>(q) * NS) * 2,
-                              static_cast<size_t>(p.N) * 2, static_cast<int>(threadIdx.x), kRows);
-        }
+        // (the combining pass runs below, on all threads of the CTA, once the other warps are done too)
       }
     }
   }
@@ -474,6 +464,21 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (shared && bar->last_flag != 0u && bar->abort_word == 0u) {
+    // Every part of this CTA's (rows, columns) region of a shared row block is in its slab, and this
+    // cluster was the last to get there: add the slabs in slab order, apply bias and activation, write Y.
+    // All warps take part -- the pass is bound by how many loads the CTA keeps in flight.
+    __threadfence();
+    const size_t mpad = static_cast<size_t>(p.row_blocks - p.whole_blocks) * kRows;
+    const size_t slab = static_cast<size_t>(gridDim.y) * mpad * p.N;
+    const size_t col0 = static_cast<size_t>(q) * NS;
+    const uint32_t* bias2 = p.b2 == nullptr ? nullptr
+                                            : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(b) * p.N + col0) / 2;
+    combine_slabs<BF16>(p.slabs + (static_cast<size_t>(b) * mpad + (row0 - p.whole_blocks * kRows)) * p.N + col0, slab, p.parts,
+                        min(kRows, p.M - row0), NS, static_cast<size_t>(p.N), bias2, p.act2,
+                        reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(b) * p.M + row0) * p.N + col0) * 2,
+                        static_cast<size_t>(p.N) * 2, static_cast<int>(threadIdx.x), kThreads);
+  }
   cluster_sync_all();                     // no CTA leaves while a peer may still write to it
   if (warp == 0) {
     tmem_dealloc(tmem_base, 512);
@@ -530,13 +535,13 @@ bool quad_supported(int N, int K, int L) {
   return L % kChunk == 0 && K % 64 == 0 && N % (kCluster * 64) == 0 && N <= kCluster * 256;
 }
 
-// fixed cost of an item in units of a 128-wide chunk: an item takes about 14 us + 2.1 us per chunk
-constexpr double kQuadFixedCost = 6.5;
+// in units of a 128-wide chunk: an item takes about 14 us + 2.1 us per chunk, sharing adds about 17 us
+constexpr double kQuadFixedCost = 6.5, kQuadSharedCost = 8.0;
 
 RowBlockPlan quad_plan(int batch, int M, int L, int cluster_slots, bool allow_scratch) {
   const int rbs = (M + kRows - 1) / kRows;
   if (!allow_scratch) return {rbs, 1};
-  return plan_row_blocks(batch, rbs, L / kChunk, kCluster, kMaxSlabs, cluster_slots, kQuadFixedCost);
+  return plan_row_blocks(batch, rbs, L / kChunk, kCluster, kMaxSlabs, cluster_slots, kQuadFixedCost, kQuadSharedCost);
 }
 
 int launch_mlp_quad(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,

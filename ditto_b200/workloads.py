@@ -120,3 +120,54 @@ def chain_inputs(w: Workload):
     b = _round(_draw((base, 1), (w.batch, w.K, w.L), w.dist), w.dtype)
     c = _round(_draw((base, 2), (w.batch, w.L, w.N), w.dist), w.dtype)
     return a, b, c
+
+
+# ------------------------------------------------------------------ the same seeding, drawn on the GPU
+# Config 5 holds 805 M input values; drawing them with numpy takes minutes.  The benchmark therefore draws
+# its inputs on the device, with the same rule -- one seed per slice / per 128-row block / per weight
+# matrix, `1000 * cfg + index` -- so that a unit's data does not depend on the number of GPUs or on which
+# rank generates it.  (The values differ from the numpy ones above: another generator.  Parity tests use
+# the numpy inputs; the benchmark checks its own inputs against the oracle after copying them back.)
+def device_seed(w: Workload, index: int, tensor: int):
+    return (1000 * w.cfg + index) * 8 + tensor
+
+
+def _device_draw(torch, seed, shape, w, device, std=1.0):
+    g = torch.Generator(device=device).manual_seed(seed)
+    tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[w.dtype]
+    if w.dist == "uniform":
+        return (torch.rand(*shape, device=device, generator=g) * 2 - 1).to(tdt)
+    return (torch.randn(*shape, device=device, generator=g) * std).to(tdt)
+
+
+def device_attention_inputs(w: Workload, lo: int, hi: int, device):
+    """Q [n, M, K], K [n, L, K], V [n, L, N] of slices [lo, hi) as device tensors in the storage type."""
+    import torch
+    tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[w.dtype]
+    n = hi - lo
+    q = torch.empty(n, w.M, w.K, dtype=tdt, device=device)
+    k = torch.empty(n, w.L, w.K, dtype=tdt, device=device)
+    v = torch.empty(n, w.L, w.N, dtype=tdt, device=device)
+    for i in range(lo, hi):
+        q[i - lo] = _device_draw(torch, device_seed(w, i, 0), (w.M, w.K), w, device)
+        k[i - lo] = _device_draw(torch, device_seed(w, i, 1), (w.L, w.K), w, device)
+        v[i - lo] = _device_draw(torch, device_seed(w, i, 2), (w.L, w.N), w, device)
+    return q, k, v
+
+
+def device_mlp_inputs(w: Workload, lo: int, hi: int, device):
+    """X rows of 128-row blocks [lo, hi) as a device tensor [(hi - lo) * 128, K]."""
+    import torch
+    tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[w.dtype]
+    x = torch.empty((hi - lo) * 128, w.K, dtype=tdt, device=device)
+    for b in range(lo, hi):
+        x[(b - lo) * 128:(b - lo + 1) * 128] = _device_draw(torch, device_seed(w, b, 0), (128, w.K), w, device)
+    return x
+
+
+def device_mlp_weights(w: Workload, device):
+    """W1 [K, L] ~ N(0, 1/K), W2 [L, N] ~ N(0, 1/L): the same on every rank."""
+    import torch
+    w1 = _device_draw(torch, device_seed(w, 0, 5), (w.K, w.L), w, device, w.K ** -0.5)
+    w2 = _device_draw(torch, device_seed(w, 0, 6), (w.L, w.N), w, device, w.L ** -0.5)
+    return w1, w2

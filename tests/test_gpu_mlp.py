@@ -106,7 +106,7 @@ def test_shared_row_blocks(cuda, oracle, layout, variant):
         # a workspace that is too small is not an error: the call computes every row block whole
         small = _run(cuda, x, w1, w2, dtype, "relu", layout, variant, workspace=ws[:1024])
         assert np.array_equal(small, whole)
-    assert split_cases >= 3, "the planner shared row blocks in fewer cases than expected"
+    assert split_cases >= 2, "the planner shared row blocks in fewer cases than expected"
 
 
 def test_golden_vector(cuda):
