@@ -25,6 +25,7 @@ FLAG_ONE_TILE = 2
 FLAG_TWO_TILES = 4
 EPILOGUE_PAIR_MMA = 0x200
 EPILOGUE_QUAD_MMA = 0x400
+EPILOGUE_WIDE_MMA = 0x800
 
 EXPORTS = (
     "ditto_b200_bmm_softmax_bmm",
@@ -36,6 +37,7 @@ EXPORTS = (
     "ditto_b200_selftest_umma",
     "ditto_b200_selftest_umma_pair",
     "ditto_b200_selftest_wait_limit",
+    "ditto_b200_check_status",
     "ditto_b200_strerror",
     "ditto_b200_last_cuda_error",
     "ditto_b200_version",
@@ -90,6 +92,8 @@ def load():
     lib.ditto_b200_selftest_umma_pair.restype = i
     lib.ditto_b200_selftest_wait_limit.argtypes = [i, vp, vp]
     lib.ditto_b200_selftest_wait_limit.restype = i
+    lib.ditto_b200_check_status.argtypes = [vp, vp, ctypes.POINTER(ctypes.c_int)]
+    lib.ditto_b200_check_status.restype = i
     lib.ditto_b200_strerror.argtypes = [i]
     lib.ditto_b200_strerror.restype = ctypes.c_char_p
     lib.ditto_b200_last_cuda_error.argtypes = []

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libditto_b200.so")
-SOURCES = ["api.cu", "host_util.cu", "attention_sm100.cu", "attention_persistent_sm100.cu", "mlp_sm100.cu", "mlp_pair_sm100.cu", "selftest_sm100.cu"]
+SOURCES = ["api.cu", "host_util.cu", "attention_sm100.cu", "attention_persistent_sm100.cu", "mlp_sm100.cu", "mlp_wide_sm100.cu", "mlp_pair_sm100.cu", "selftest_sm100.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--use_fast_math",

@@ -158,10 +158,11 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
   if (!aligned16(x) || !aligned16(w1) || !aligned16(w2) || !aligned16(y)) return DITTO_ERR_INVALID_ARG;
   if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
   if (w_layout != 0 && w_layout != 1) return DITTO_ERR_INVALID_ARG;
-  const int variant_bits = epilogue & (DITTO_EPILOGUE_PAIR_MMA | DITTO_EPILOGUE_QUAD_MMA);
-  const int act = epilogue & ~(DITTO_EPILOGUE_PAIR_MMA | DITTO_EPILOGUE_QUAD_MMA);
+  constexpr int kVariantMask = DITTO_EPILOGUE_PAIR_MMA | DITTO_EPILOGUE_QUAD_MMA | DITTO_EPILOGUE_WIDE_MMA;
+  const int variant_bits = epilogue & kVariantMask;
+  const int act = epilogue & ~kVariantMask;
   if (act != 0 && act != 1) return DITTO_ERR_INVALID_ARG;
-  if (variant_bits == (DITTO_EPILOGUE_PAIR_MMA | DITTO_EPILOGUE_QUAD_MMA)) return DITTO_ERR_INVALID_ARG;
+  if (variant_bits & (variant_bits - 1)) return DITTO_ERR_INVALID_ARG;   // at most one kernel can be named
   if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
   if (N == K && K <= 128) {
     // Small-N chains (the reference's shape family: N = K = 64, L = 512 ...): the result tile
@@ -207,6 +208,7 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
 #endif
   const int variant = variant_bits == DITTO_EPILOGUE_PAIR_MMA   ? ditto_b200::kMlpPair
                       : variant_bits == DITTO_EPILOGUE_QUAD_MMA ? ditto_b200::kMlpQuad
+                      : variant_bits == DITTO_EPILOGUE_WIDE_MMA ? ditto_b200::kMlpWide
                                                                 : ditto_b200::kMlpAuto;
   return ditto_b200::launch_mlp_chain(x, w1, w2, y, batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, w_layout, act, 0,
                                       nullptr, nullptr, variant, workspace, ws_bytes, status_word,
@@ -236,8 +238,10 @@ size_t ditto_b200_workspace_bytes(int op, int batch, int M, int N, int K, int L,
   if ((op & 0xff) != DITTO_OP_GEMM_RELU_GEMM || batch <= 0 || M <= 0 || N <= 0 || K <= 0 || L <= 0) return 0;
   if (N == K && K <= 128) return 0;
   // `op` may carry DITTO_EPILOGUE_PAIR_MMA / DITTO_EPILOGUE_QUAD_MMA like the call's `epilogue` argument
-  const int variant = (op & DITTO_EPILOGUE_PAIR_MMA) ? ditto_b200::kMlpPair
-                      : (op & DITTO_EPILOGUE_QUAD_MMA) ? ditto_b200::kMlpQuad : ditto_b200::kMlpAuto;
+  const int variant = (op & DITTO_EPILOGUE_PAIR_MMA)   ? ditto_b200::kMlpPair
+                      : (op & DITTO_EPILOGUE_QUAD_MMA) ? ditto_b200::kMlpQuad
+                      : (op & DITTO_EPILOGUE_WIDE_MMA) ? ditto_b200::kMlpWide
+                                                       : ditto_b200::kMlpAuto;
   size_t a = ditto_b200::mlp_workspace_bytes(batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, 0, variant);
   size_t b = ditto_b200::mlp_workspace_bytes(batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, 1, variant);
   return a > b ? a : b;
@@ -248,6 +252,7 @@ int ditto_b200_mlp_cluster_slots(int dtype, int variant) {
   int slots = 0;
   int rc = variant == DITTO_EPILOGUE_PAIR_MMA   ? ditto_b200::mlp_pair_cluster_slots(dtype == DITTO_DTYPE_BF16, &slots)
            : variant == DITTO_EPILOGUE_QUAD_MMA ? ditto_b200::mlp_quad_cluster_slots(dtype == DITTO_DTYPE_BF16, &slots)
+           : variant == DITTO_EPILOGUE_WIDE_MMA ? ditto_b200::mlp_wide_cluster_slots(dtype == DITTO_DTYPE_BF16, &slots)
                                                 : DITTO_ERR_INVALID_ARG;
   return rc ? rc : slots;
 }
@@ -306,6 +311,21 @@ int ditto_b200_selftest_wait_limit(int code, int* status_word, void* stream) {
   cudaError_t e = ditto_b200::launch_wait_limit_selftest(code, status_word, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail("selftest_wait_limit launch", e);
   return DITTO_OK;
+}
+
+int ditto_b200_check_status(int* status_word, void* stream, int* code_out) {
+  if (status_word == nullptr) return DITTO_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int value = 0;
+  cudaError_t e = cudaMemcpyAsync(&value, status_word, sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return cuda_fail("check_status", e);
+  if (code_out != nullptr) *code_out = value;
+  if (value == 0) return DITTO_OK;
+  e = cudaMemsetAsync(status_word, 0, sizeof(int), st);       // ready for the next calls
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return cuda_fail("check_status", e);
+  return DITTO_ERR_TIMEOUT;
 }
 
 const char* ditto_b200_strerror(int code) {

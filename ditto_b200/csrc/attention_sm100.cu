@@ -38,6 +38,11 @@
 
 #include "sm100_ptx.cuh"
 
+// 1: the softmax evaluates its exponentials two at a time on packed 16-bit arguments (see ex2_packed)
+#ifndef DITTO_PACKED_EX2
+#define DITTO_PACKED_EX2 0
+#endif
+
 // Optional timeline capture for tuning (compiled in only with -DDITTO_TRACE): CTA (0,0) stores
 // clock64() stamps of its first iterations into the buffer passed as the call's workspace.
 #ifdef DITTO_TRACE
@@ -451,7 +456,14 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
         for (int i = 0; i < kFirst; ++i) {
           if (w0 + i < w1) {
             float p0 = __uint_as_float(sv[2 * (w0 + i)]), p1 = __uint_as_float(sv[2 * (w0 + i) + 1]);
-            if constexpr (MODE == kModeSoftmax) {
+            if constexpr (MODE == kModeSoftmax && DITTO_PACKED_EX2 != 0) {
+              // one special-function instruction for the pair; the sum takes the rounded values the MMA will see
+              pk[i] = ex2_packed<BF16>(fmaf(p0, c, -mc), fmaf(p1, c, -mc));
+              const float2 pf = BF16 ? unpack_bf16x2(pk[i]) : unpack_f16x2(pk[i]);
+              sum0 += pf.x;
+              sum1 += pf.y;
+              continue;
+            } else if constexpr (MODE == kModeSoftmax) {
               p0 = ex2_approx(fmaf(p0, c, -mc));
               p1 = ex2_approx(fmaf(p1, c, -mc));
             } else if constexpr (MODE == kModeRelu) {

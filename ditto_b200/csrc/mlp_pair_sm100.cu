@@ -23,9 +23,14 @@
 // (distributed) shared memory.  No TMA load in this file uses cluster multicast.
 //
 // Who talks to whom:
-//   * TMA (two producer threads per CTA, alternate ring granules of 16 KB): each CTA loads its own X rows
-//     and its half of the W1 / W2 tiles; byte counts go to the pair leader's `full` barrier.
-//   * MMA: only the leader's issuing warp; commits are delivered to both CTAs of the pair.
+//   * TMA: each CTA loads its own X rows and its half of the W1 / W2 tiles, in 16 KB granules; byte counts go
+//     to the pair leader's barrier of the granule.  GEMM1's granules (X and W1 alternate, two per k-step) have
+//     their own ring and two producer threads per CTA (alternate granules); GEMM2's (one W2 tile per hidden
+//     unit) a second ring and one producer.
+//   * MMA: only the leader issues, with one warp per GEMM; commits are delivered to both CTAs of the pair.
+//     An issuing warp pays a few hundred clocks per k-step for the barrier waits, the MMAs and the commits,
+//     about what the MMAs take to execute: a single warp issuing both GEMMs in a fixed interleaving made the
+//     issue cost and the tensor work add up instead of overlap.
 //   * Units are numbered n in the order GEMM2 consumes them -- round by round (four chunks, one per
 //     pair), inside a round quarter by quarter across the pairs, which is the order they arrive in --
 //     and live in slot n % kUnits of every CTA.
@@ -33,9 +38,8 @@
 //     peer pushes, waits until the unit is present and tells the leader (h_pair, 2 arrivals).
 //   * free relay (one thread per CTA): forwards "the pair's GEMM2 is done with slot s" to the CTA of its
 //     half that writes the slot next (slot_free, 4 arrivals).
-//   * Tensor-pipe order on the leader: GEMM1 of the pair's first chunk, then per round the sixteen
-//     GEMM2 units with GEMM1 of the next own chunk spread over the first twelve of them, so the chunk is
-//     drained and on its way while the last four units keep the pipe busy.
+//   * The GEMM1 accumulator is single: the next chunk's GEMM1 starts once the epilogue warps hold the previous
+//     chunk in registers (they drain the whole chunk before they wait for free slots).
 //
 // Work items.  An item is (row block, hidden range): with few row blocks the hidden dimension is split
 // over several clusters, each writes its fp32 partial of Y to its own slab of the caller's workspace,
@@ -73,17 +77,12 @@
 #ifndef DITTO_PAIR_UNITS
 #define DITTO_PAIR_UNITS 6
 #endif
-#ifndef DITTO_PAIR_GRANULES
-#define DITTO_PAIR_GRANULES 8
+#ifndef DITTO_PAIR_G1_GRANULES
+#define DITTO_PAIR_G1_GRANULES 5
 #endif
-// GEMM1 of the next own chunk is spread over the first kLeadNum / kLeadDen of a round's GEMM2 units
-#ifndef DITTO_PAIR_LEAD_NUM
-#define DITTO_PAIR_LEAD_NUM 3
+#ifndef DITTO_PAIR_W2_GRANULES
+#define DITTO_PAIR_W2_GRANULES 3
 #endif
-#ifndef DITTO_PAIR_LEAD_DEN
-#define DITTO_PAIR_LEAD_DEN 4
-#endif
-
 namespace ditto_b200 {
 
 namespace {
@@ -96,15 +95,17 @@ constexpr int kUnitCols = 64;         // hidden columns per unit: one 128-byte-r
 constexpr int kUnitBytes = kRows * kUnitCols * 2;
 constexpr int kGranule = 16 * 1024;   // ring granule: one operand tile (X k-step, W1 half tile, W2 half tile)
 constexpr int kUnits = DITTO_PAIR_UNITS;        // unit slots per CTA
-constexpr int kGranules = DITTO_PAIR_GRANULES;  // ring depth (even: the two producers take alternate granules)
+constexpr int kG1Granules = DITTO_PAIR_G1_GRANULES;   // GEMM1 ring: X and W1 tiles alternate, two per k-step
+constexpr int kW2Granules = DITTO_PAIR_W2_GRANULES;   // GEMM2 ring: one W2 tile per hidden unit
 constexpr int kEpiWarps = 8;          // warp w: TMEM lanes 32 (w % 4) ..., column half w / 4 of every quarter
-constexpr int kWarpProd0 = 8, kWarpMma = 9, kWarpReady = 10, kWarpFree = 11, kWarpProd1 = 12;
-constexpr int kThreads = 13 * 32;
+constexpr int kWarpProdG1a = 8, kWarpMmaG1 = 9, kWarpReady = 10, kWarpFree = 11, kWarpProdG1b = 12, kWarpMmaG2 = 13,
+              kWarpProdW2 = 14;
+constexpr int kThreads = 15 * 32;
 constexpr int kOffSlots = 0;
-constexpr int kOffRing = kOffSlots + kUnits * kUnitBytes;
-constexpr int kOffBar = kOffRing + kGranules * kGranule;
+constexpr int kOffG1Ring = kOffSlots + kUnits * kUnitBytes;
+constexpr int kOffW2Ring = kOffG1Ring + kG1Granules * kGranule;
+constexpr int kOffBar = kOffW2Ring + kW2Granules * kGranule;
 constexpr int kSmemBytes = kOffBar + 512 + 1024;
-static_assert(kGranules % 2 == 0, "producers alternate over the granules");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 
 struct PairParams {
@@ -128,8 +129,9 @@ struct PairParams {
 };
 
 struct PairBars {
-  uint64_t full[kGranules];    // leader: the granule's tiles of both CTAs have landed
-  uint64_t empty[kGranules];   // each CTA: the pair's MMAs have finished with the granule
+  uint64_t g1full[kG1Granules];   // leader: the granule's tiles of both CTAs have landed
+  uint64_t g1empty[kG1Granules];  // each CTA: the pair's MMAs have finished with the granule
+  uint64_t w2full[kW2Granules], w2empty[kW2Granules];
   uint64_t h_tmem_full;        // each CTA: GEMM1 of the chunk is in tensor memory
   uint64_t h_tmem_empty;       // leader: both CTAs' epilogue warps hold the chunk in registers (16 warp arrivals)
   uint64_t h_ready[kUnits];    // each CTA: the slot's unit is present (own: local arrive; a peer's: pushed bytes)
@@ -160,27 +162,6 @@ __device__ __forceinline__ void tma_load_4d_pair(void* dst, const CUtensorMap* m
       "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
-}
-
-// The order in which the leader's tensor pipe takes the work of an item, shared by the producers (which
-// fill the ring in this order) and the issuing warp.  g1(i, ks): k-step ks of GEMM1 of this pair's chunk of
-// round i.  g2(n, i, kk, src): GEMM2 on unit n = quarter kk of the chunk of pair `src` in round i.
-template <class G1, class G2>
-__device__ __forceinline__ void walk_item(int chunks, int my_rounds, int ksteps1, const bool& ok, G1&& g1, G2&& g2) {
-  if (my_rounds > 0)
-    for (int ks = 0; ks < ksteps1 && ok; ++ks) g1(0, ks);
-  const int total_rounds = (chunks + kPairs - 1) / kPairs;
-  for (int i = 0; i < total_rounds && ok; ++i) {
-    const int cr = min(kPairs, chunks - kPairs * i);   // chunks (= pairs at work) in this round
-    const int nun = 4 * cr;
-    const int lead = max(1, nun * DITTO_PAIR_LEAD_NUM / DITTO_PAIR_LEAD_DEN);
-    const bool next = i + 1 < my_rounds;
-    for (int e = 0; e < nun && ok; ++e) {
-      if (next && e < lead)
-        for (int ks = e * ksteps1 / lead; ks < (e + 1) * ksteps1 / lead && ok; ++ks) g1(i + 1, ks);
-      g2(4 * kPairs * i + e, i, e / cr, e % cr);
-    }
-  }
 }
 
 }  // namespace
@@ -219,9 +200,13 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const int ksteps1 = (p.K + 63) / 64;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kGranules; ++s) {
-      mbar_init(&bar->full[s], 1);
-      mbar_init(&bar->empty[s], 1);
+    for (int s = 0; s < kG1Granules; ++s) {
+      mbar_init(&bar->g1full[s], 1);
+      mbar_init(&bar->g1empty[s], 1);
+    }
+    for (int s = 0; s < kW2Granules; ++s) {
+      mbar_init(&bar->w2full[s], 1);
+      mbar_init(&bar->w2empty[s], 1);
     }
     mbar_init(&bar->h_tmem_full, 1);
     mbar_init(&bar->h_tmem_empty, 2 * kEpiWarps);
@@ -254,80 +239,97 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   grid_dependency_wait();
   grid_launch_dependents();
 
-  if (warp == kWarpProd0 || warp == kWarpProd1) {
-    // ------------------------------------------------------------ TMA producers (one thread each)
+  if (warp == kWarpProdG1a || warp == kWarpProdG1b) {
+    // ------------------------------------------------------------ GEMM1 operand producers (one thread each)
+    // GEMM1 takes two granules per k-step: this CTA's 128 x 64 piece of X, then its half (64 x 128) of the W1
+    // tile.  One thread gets a TMA box out every few hundred clocks; the two producers take alternate granules.
     if (lane == 0) {
-      const uint32_t pw = warp == kWarpProd0 ? 0u : 1u;
+      const int pw = warp == kWarpProdG1a ? 0 : 1;
       tma_prefetch_desc(&p.map_x);
       tma_prefetch_desc(&p.map_w1);
+      int ps = 0, cnt = 0;
+      uint32_t pph = 0;
+      bool ok = true;
+      uint32_t full_addr = 0;             // the leader's barrier of the granule as a cluster address
+      // `mine`: this producer's turn.  The leader arms the barrier with what both CTAs of the pair put in.
+      auto acquire = [&](uint32_t code) -> uint8_t* {
+        uint8_t* dst = nullptr;
+        if ((cnt & 1) == pw) {
+          ok = mbar_wait(&bar->g1empty[ps], pph ^ 1, abort_word, code);
+          if (ok) {
+            if (half == 0) mbar_arrive_expect_tx(&bar->g1full[ps], 2 * kGranule);
+            full_addr = map_to_cta(smem_u32(&bar->g1full[ps]), leader);
+            dst = smem + kOffG1Ring + ps * kGranule;
+          }
+        }
+        ++cnt;
+        if (++ps == kG1Granules) { ps = 0; pph ^= 1; }
+        return dst;
+      };
+      for (int i = 0; i < my_rounds && ok; ++i) {
+        const int hcol = (c0 + i * kPairs + static_cast<int>(pair)) * kChunk + static_cast<int>(half) * (kChunk / 2);
+        for (int ks = 0; ks < ksteps1 && ok; ++ks) {
+          uint8_t* dst = acquire(0x100 + i);
+          if (dst != nullptr) tma_load_3d_pair(dst, &p.map_x, full_addr, ks * 64, row0, b);
+          if (!ok) break;
+          dst = acquire(0x140 + i);
+          if (dst != nullptr) {
+            if (p.w_oi) {
+              tma_load_3d_pair(dst, &p.map_w1, full_addr, ks * 64, hcol, b);
+            } else if (p.w_atoms) {
+              tma_load_4d_pair(dst, &p.map_w1, full_addr, 0, ks * 64, hcol / 64, b);
+            } else {
+              for (int a = 0; a < kChunk / 2 / 64; ++a)
+                tma_load_3d_pair(dst + a * 8192, &p.map_w1, full_addr, hcol + a * 64, ks * 64, b);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == kWarpProdW2) {
+    // ------------------------------------------------------------ GEMM2 operand producer (one thread)
+    // One granule per hidden unit, in the order GEMM2 consumes the units: this CTA's half of the pair's W2 tile.
+    if (lane == 0) {
       tma_prefetch_desc(&p.map_w2);
       int ps = 0;
       uint32_t pph = 0;
-      bool ok = true;
-      uint32_t full_addr = 0;             // the leader's full[ps] as a cluster address
-      // Both producers walk the same sequence of granules; each fills the ones of its parity.
-      // `pair_bytes`: what both CTAs of the pair put into the granule (armed by the leader only).
-      auto acquire = [&](uint32_t pair_bytes, uint32_t code) -> uint8_t* {
-        uint8_t* dst = nullptr;
-        if ((static_cast<uint32_t>(ps) & 1u) == pw) {
-          ok = mbar_wait(&bar->empty[ps], pph ^ 1, abort_word, code);
-          if (ok) {
-            if (half == 0) mbar_arrive_expect_tx(&bar->full[ps], pair_bytes);
-            full_addr = map_to_cta(smem_u32(&bar->full[ps]), leader);
-            dst = smem + kOffRing + ps * kGranule;
-          }
+      const int ncol = static_cast<int>(pair) * NS + static_cast<int>(half) * NH;
+      for (int n = 0; n < units; ++n) {
+        const int i = n / (4 * kPairs);
+        const int cr = min(kPairs, chunks - kPairs * i);
+        const int e = n - 4 * kPairs * i;
+        const int hrow = (c0 + i * kPairs + e % cr) * kChunk + (e / cr) * kUnitCols;
+        if (!mbar_wait(&bar->w2empty[ps], pph ^ 1, abort_word, 0x200 + i)) break;
+        if (half == 0) mbar_arrive_expect_tx(&bar->w2full[ps], static_cast<uint32_t>(2 * 64 * NH * 2));
+        const uint32_t full_addr = map_to_cta(smem_u32(&bar->w2full[ps]), leader);
+        uint8_t* dst = smem + kOffW2Ring + ps * kGranule;
+        if (p.w_oi) {
+          tma_load_3d_pair(dst, &p.map_w2, full_addr, hrow, ncol, b);
+        } else if (p.w_atoms) {
+          tma_load_4d_pair(dst, &p.map_w2, full_addr, 0, hrow, ncol / 64, b);
+        } else {
+          for (int a = 0; a < NH / 64; ++a)
+            tma_load_3d_pair(dst + a * 8192, &p.map_w2, full_addr, ncol + a * 64, hrow, b);
         }
-        if (++ps == kGranules) { ps = 0; pph ^= 1; }
-        return dst;
-      };
-      walk_item(chunks, my_rounds, ksteps1, ok,
-          [&](int i, int ks) {            // GEMM1 k-step: this CTA's X rows, then its half of the W1 chunk tile
-            const int hcol = (c0 + i * kPairs + static_cast<int>(pair)) * kChunk + static_cast<int>(half) * (kChunk / 2);
-            uint8_t* dst = acquire(2 * kGranule, 0x100 + i);
-            if (dst != nullptr) tma_load_3d_pair(dst, &p.map_x, full_addr, ks * 64, row0, b);
-            dst = acquire(2 * kGranule, 0x140 + i);
-            if (dst != nullptr) {
-              if (p.w_oi) {
-                tma_load_3d_pair(dst, &p.map_w1, full_addr, ks * 64, hcol, b);
-              } else if (p.w_atoms) {
-                tma_load_4d_pair(dst, &p.map_w1, full_addr, 0, ks * 64, hcol / 64, b);
-              } else {
-                for (int a = 0; a < kChunk / 2 / 64; ++a)
-                  tma_load_3d_pair(dst + a * 8192, &p.map_w1, full_addr, hcol + a * 64, ks * 64, b);
-              }
-            }
-          },
-          [&](int n, int i, int kk, int src) {   // GEMM2 unit: this CTA's half of the pair's W2 slice
-            (void)n;
-            const int hrow = (c0 + i * kPairs + src) * kChunk + kk * kUnitCols;
-            const int ncol = static_cast<int>(pair) * NS + static_cast<int>(half) * NH;
-            uint8_t* dst = acquire(2 * 64 * NH * 2, 0x200 + i);
-            if (dst != nullptr) {
-              if (p.w_oi) {
-                tma_load_3d_pair(dst, &p.map_w2, full_addr, hrow, ncol, b);
-              } else if (p.w_atoms) {
-                tma_load_4d_pair(dst, &p.map_w2, full_addr, 0, hrow, ncol / 64, b);
-              } else {
-                for (int a = 0; a < NH / 64; ++a)
-                  tma_load_3d_pair(dst + a * 8192, &p.map_w2, full_addr, ncol + a * 64, hrow, b);
-              }
-            }
-          });
+        if (++ps == kW2Granules) { ps = 0; pph ^= 1; }
+      }
     }
-  } else if (warp == kWarpMma) {
-    // ------------------------------------------------------------ MMA issuer (leader CTA only, converged warp)
+  } else if (warp == kWarpMmaG1) {
+    // ------------------------------------------------------------ GEMM1 issuer (leader CTA only, converged warp)
+    // Each issuing warp pays a few hundred clocks per k-step for the barrier waits, the four MMAs and the
+    // commits -- about what the MMAs take to execute.  One warp issuing both GEMMs spent as long issuing as
+    // the tensor pipe needs for the work; with a warp per GEMM the issue cost of one hides behind the other's
+    // tensor work, and whichever GEMM has its operands is issued (no fixed interleaving).
     if (half == 0) {
       const uint32_t issuer = elect_one();
       const uint32_t pair_mask = 0x3u << leader;
       const uint32_t idesc1 = umma_idesc_f16(BF16, 2 * kRows, kChunk, false, p.w_oi == 0);
-      const uint32_t idesc2 = umma_idesc_f16(BF16, 2 * kRows, NS, false, p.w_oi == 0);
-      const uint32_t ring = smem_u32(smem + kOffRing);
-      const uint32_t slots = smem_u32(smem + kOffSlots);
+      const uint32_t ring = smem_u32(smem + kOffG1Ring);
       int cs = 0;
       uint32_t cph = 0;
       bool ok = true;
-      long long w_acc = 0, w_g1 = 0, w_unit = 0, w_g2 = 0;   // clocks spent waiting (timeline builds only)
-      (void)w_acc; (void)w_g1; (void)w_unit; (void)w_g2;
+      long long w_acc = 0, w_g1 = 0;      // clocks spent waiting (timeline builds only)
+      (void)w_acc; (void)w_g1;
       auto wait = [&](uint64_t* bp, uint32_t parity, uint32_t code) {
         bool r = mbar_wait(bp, parity, abort_word, code);
         r = __all_sync(0xffffffffu, r);
@@ -340,67 +342,95 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         tc_fence_after_sync();
         return r;
       };
-      // next ring granule: waits until its tile has landed in both CTAs; returns its shared-memory address
+      // next granule of the ring: waits until its tile has landed in both CTAs; returns its shared-memory address
       auto take = [&](uint32_t code, uint64_t*& empty_bar) -> uint32_t {
-        ok = wait(&bar->full[cs], cph, code);
+        ok = wait(&bar->g1full[cs], cph, code);
         const uint32_t addr = ring + cs * kGranule;
-        empty_bar = &bar->empty[cs];
-        if (++cs == kGranules) { cs = 0; cph ^= 1; }
+        empty_bar = &bar->g1empty[cs];
+        if (++cs == kG1Granules) { cs = 0; cph ^= 1; }
         return addr;
       };
-      walk_item(chunks, my_rounds, ksteps1, ok,
-          [&](int i, int ks) {
-            // the accumulator is single: the previous chunk must be in the epilogue warps' registers
-            if (ks == 0 && i > 0) DITTO_TIMED(w_acc, ok = wait_cluster(&bar->h_tmem_empty, (i - 1) & 1, 0x300 + i));
-            if (!ok) return;
-            if (ks == 0 && lane == 0) DITTO_STAMP(16 * i + 0);
-            uint64_t *ex, *ew;
-            uint32_t sx = 0, sw = 0;
-            DITTO_TIMED(w_g1, sx = take(0x310 + i, ex));
-            if (!ok) return;
-            DITTO_TIMED(w_g1, sw = take(0x320 + i, ew));
-            if (!ok) return;
-            const uint64_t da = umma_desc_sw128(sx, 16, 1024);
-            const uint64_t db = p.w_oi ? umma_desc_sw128(sw, 16, 1024) : umma_desc_sw128(sw, 8192, 1024);
+      for (int i = 0; i < my_rounds && ok; ++i) {
+        // the accumulator is single: the previous chunk must be in the epilogue warps' registers
+        if (i > 0) DITTO_TIMED(w_acc, ok = wait_cluster(&bar->h_tmem_empty, (i - 1) & 1, 0x300 + i));
+        if (lane == 0) DITTO_STAMP(16 * i + 0);
+        for (int ks = 0; ks < ksteps1 && ok; ++ks) {
+          uint64_t *ex = nullptr, *ew = nullptr;
+          uint32_t sx = 0, sw = 0;
+          DITTO_TIMED(w_g1, sx = take(0x310 + i, ex));
+          if (!ok) break;
+          DITTO_TIMED(w_g1, sw = take(0x320 + i, ew));
+          if (!ok) break;
+          const uint64_t da = umma_desc_sw128(sx, 16, 1024);
+          const uint64_t db = p.w_oi ? umma_desc_sw128(sw, 16, 1024) : umma_desc_sw128(sw, 8192, 1024);
 #pragma unroll
-            for (int s4 = 0; s4 < 4; ++s4) {
-              const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
-              umma_ss_pair_elected(tmem_h, da + ((s4 * 32) >> 4), db + offb, idesc1, (ks | s4) ? 1u : 0u, issuer);
-            }
-            umma_commit_pair_elected(ex, pair_mask, issuer);
-            umma_commit_pair_elected(ew, pair_mask, issuer);
-            if (ks == ksteps1 - 1) {
-              umma_commit_pair_elected(&bar->h_tmem_full, pair_mask, issuer);
-              if (lane == 0) DITTO_STAMP(16 * i + 1);
-            }
-          },
-          [&](int n, int i, int kk, int src) {
-            (void)kk;
-            (void)src;
-            const int sl = n % kUnits;
-            if (lane == 0 && (n & 15) == 0) DITTO_STAMP(16 * i + 2);
-            DITTO_TIMED(w_unit, ok = wait_cluster(&bar->h_pair[sl], (n / kUnits) & 1, 0x400 + i));   // the unit is in both CTAs' slots
-            if (!ok) return;
-            if (lane == 0 && (n & 15) == 0) DITTO_STAMP(16 * i + 3);
-            uint64_t* ew;
-            uint32_t sw = 0;
-            DITTO_TIMED(w_g2, sw = take(0x410 + i, ew));
-            if (!ok) return;
-            const uint64_t da = umma_desc_sw128(slots + sl * kUnitBytes, 16, 1024);
-            const uint64_t db = p.w_oi ? umma_desc_sw128(sw, 16, 1024) : umma_desc_sw128(sw, 8192, 1024);
+          for (int s4 = 0; s4 < 4; ++s4) {
+            const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
+            umma_ss_pair_elected(tmem_h, da + ((s4 * 32) >> 4), db + offb, idesc1, (ks | s4) ? 1u : 0u, issuer);
+          }
+          umma_commit_pair_elected(ex, pair_mask, issuer);
+          umma_commit_pair_elected(ew, pair_mask, issuer);
+        }
+        if (ok) umma_commit_pair_elected(&bar->h_tmem_full, pair_mask, issuer);
+        if (lane == 0) DITTO_STAMP(16 * i + 1);
+      }
+#ifdef DITTO_TRACE
+      if (lane == 0 && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
+        p.trace[400] = w_acc; p.trace[401] = w_g1; p.trace[404] = clock64();
+      }
+#endif
+    }
+  } else if (warp == kWarpMmaG2) {
+    // ------------------------------------------------------------ GEMM2 issuer (leader CTA only, converged warp)
+    if (half == 0) {
+      const uint32_t issuer = elect_one();
+      const uint32_t pair_mask = 0x3u << leader;
+      const uint32_t idesc2 = umma_idesc_f16(BF16, 2 * kRows, NS, false, p.w_oi == 0);
+      const uint32_t ring = smem_u32(smem + kOffW2Ring);
+      const uint32_t slots = smem_u32(smem + kOffSlots);
+      int cs = 0;
+      uint32_t cph = 0;
+      bool ok = true;
+      long long w_unit = 0, w_g2 = 0;
+      (void)w_unit; (void)w_g2;
+      auto wait = [&](uint64_t* bp, uint32_t parity, uint32_t code) {
+        bool r = mbar_wait(bp, parity, abort_word, code);
+        r = __all_sync(0xffffffffu, r);
+        tc_fence_after_sync();
+        return r;
+      };
+      auto wait_cluster = [&](uint64_t* bp, uint32_t parity, uint32_t code) {
+        bool r = mbar_wait_cluster(bp, parity, abort_word, code);
+        r = __all_sync(0xffffffffu, r);
+        tc_fence_after_sync();
+        return r;
+      };
+      for (int n = 0; n < units && ok; ++n) {
+        const int sl = n % kUnits;
+        const int i = n / (4 * kPairs);
+        if (lane == 0 && (n & 15) == 0) DITTO_STAMP(16 * i + 2);
+        DITTO_TIMED(w_unit, ok = wait_cluster(&bar->h_pair[sl], (n / kUnits) & 1, 0x400 + i));   // the unit is in both CTAs' slots
+        if (!ok) break;
+        if (lane == 0 && (n & 15) == 0) DITTO_STAMP(16 * i + 3);
+        DITTO_TIMED(w_g2, ok = wait(&bar->w2full[cs], cph, 0x410 + i));
+        if (!ok) break;
+        const uint32_t sw = ring + cs * kGranule;
+        const uint64_t da = umma_desc_sw128(slots + sl * kUnitBytes, 16, 1024);
+        const uint64_t db = p.w_oi ? umma_desc_sw128(sw, 16, 1024) : umma_desc_sw128(sw, 8192, 1024);
 #pragma unroll
-            for (int s4 = 0; s4 < 4; ++s4) {
-              const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
-              umma_ss_pair_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (n | s4) ? 1u : 0u, issuer);
-            }
-            umma_commit_pair_elected(ew, pair_mask, issuer);
-            umma_commit_pair_elected(&bar->g2_done[sl], pair_mask, issuer);
-            if (lane == 0 && (n & 15) == 15) DITTO_STAMP(16 * i + 4);
-          });
+        for (int s4 = 0; s4 < 4; ++s4) {
+          const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
+          umma_ss_pair_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (n | s4) ? 1u : 0u, issuer);
+        }
+        umma_commit_pair_elected(&bar->w2empty[cs], pair_mask, issuer);
+        umma_commit_pair_elected(&bar->g2_done[sl], pair_mask, issuer);
+        if (++cs == kW2Granules) { cs = 0; cph ^= 1; }
+        if (lane == 0 && (n & 15) == 15) DITTO_STAMP(16 * i + 4);
+      }
       if (ok) umma_commit_pair_elected(&bar->y_done, pair_mask, issuer);
 #ifdef DITTO_TRACE
       if (lane == 0 && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
-        p.trace[400] = w_acc; p.trace[401] = w_g1; p.trace[402] = w_unit; p.trace[403] = w_g2;
+        p.trace[402] = w_unit; p.trace[403] = w_g2; p.trace[405] = clock64();
       }
 #endif
     }

@@ -35,6 +35,7 @@
 #include <cuda_fp16.h>
 
 #include <atomic>
+#include <cstdio>
 #include <cstring>
 
 #include "../../include/ditto_b200.h"
@@ -49,8 +50,20 @@
   do {                                                                                      \
     if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (i) < 8) p.trace[(i) * 16 + (k)] = clock64(); \
   } while (0)
+#define DITTO_TIMED(acc, expr)          \
+  do {                                 \
+    const long long t_ = clock64();    \
+    expr;                              \
+    acc += clock64() - t_;             \
+  } while (0)
 #else
 #define DITTO_STAMP(i, k) do {} while (0)
+#define DITTO_TIMED(acc, expr) do { expr; } while (0)
+#endif
+
+// 1: calls that do not name a kernel take the 256-wide-chunk kernel where it covers the shape
+#ifndef DITTO_MLP_DEFAULT_WIDE
+#define DITTO_MLP_DEFAULT_WIDE 1
 #endif
 
 #ifndef DITTO_MLP_UNITS
@@ -259,6 +272,8 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     int cs = 0;
     uint32_t cph = 0;
     bool ok = true;
+    long long w_acc = 0, w_g1 = 0, w_unit = 0, w_g2 = 0;   // clocks spent waiting (timeline builds only)
+    (void)w_acc; (void)w_g1; (void)w_unit; (void)w_g2;
     auto wait = [&](uint64_t* bp, uint32_t parity, uint32_t code) {
       bool r = mbar_wait(bp, parity, abort_word, code);
       r = __all_sync(0xffffffffu, r);
@@ -271,10 +286,10 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     // GEMM1 of this CTA's chunk of round i, k-steps [ks0, ks1); `first` / `last`: the part that starts / ends the chunk
     auto g1 = [&](int i, int ks0, int ks1, bool first, bool last) {
       const int hb = i & 1;
-      if (first && i >= 2) ok = wait(&bar->h_tmem_empty[hb], ((i >> 1) - 1) & 1, 0x300 + i);
+      if (first && i >= 2) DITTO_TIMED(w_acc, ok = wait(&bar->h_tmem_empty[hb], ((i >> 1) - 1) & 1, 0x300 + i));
       if (first && lane == 0) DITTO_STAMP(i, 0);
       for (int ks = ks0; ks < ks1 && ok; ++ks) {
-        ok = wait(&bar->full[cs], cph, 0x310 + i);
+        DITTO_TIMED(w_g1, ok = wait(&bar->full[cs], cph, 0x310 + i));
         if (!ok) break;
         const uint32_t st = ring + cs * kStageBytes;
         const uint64_t da = umma_desc_sw128(st, 16, 1024);
@@ -298,9 +313,9 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         mbar_arrive_expect_tx(&bar->h_ready[sl], kUnitBytes);   // a peer pushes this unit; the owner's own copy arrives locally
       __syncwarp();
       if (lane == 0 && (u & 7) == 0) DITTO_STAMP(u >> 3, 2);
-      ok = wait(&bar->h_ready[sl], (u / kUnits) & 1, 0x400 + (u >> 3));
+      DITTO_TIMED(w_unit, ok = wait(&bar->h_ready[sl], (u / kUnits) & 1, 0x400 + (u >> 3)));
       if (lane == 0 && (u & 1) == 0) DITTO_STAMP(u >> 3, 9 + ((u >> 1) & 3));
-      if (ok) ok = wait(&bar->full[cs], cph, 0x410 + (u >> 3));
+      if (ok) DITTO_TIMED(w_g2, ok = wait(&bar->full[cs], cph, 0x410 + (u >> 3)));
       if (ok) {
         const uint32_t st = ring + cs * kStageBytes;
         const uint64_t da = umma_desc_sw128(slots + sl * kUnitBytes, 16, 1024);
@@ -326,6 +341,11 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       if (i + 2 < rounds && ok) g1(i + 2, e * ksteps1 / 8, (e + 1) * ksteps1 / 8, e == 0, e == 7);
     }
     if (ok) umma_commit_elected(&bar->y_done, issuer);
+#ifdef DITTO_TRACE
+    if (lane == 0 && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
+      p.trace[200] = w_acc; p.trace[201] = w_g1; p.trace[202] = w_unit; p.trace[203] = w_g2; p.trace[204] = clock64();
+    }
+#endif
   } else if (warp == 6) {
     // ------------------------------------------------------------ relay (one thread)
     if (lane == 0) {
@@ -638,43 +658,66 @@ int mlp_quad_cluster_slots(bool bf16, int* slots) {
   return DITTO_OK;
 }
 
+// Which kernel an "auto" call takes: the 256-wide-chunk kernel where it covers the shape (measured fastest at
+// the benchmark configuration), the 128-wide one for hidden sizes that are only multiples of 128, the pair
+// kernel for what neither covers.
+static int resolve_variant(int variant, int N, int K, int L, int w_layout) {
+  if (variant != kMlpAuto) return variant;
+  if (DITTO_MLP_DEFAULT_WIDE && mlp_wide_supported(N, K, L)) return kMlpWide;
+  if (quad_supported(N, K, L)) return kMlpQuad;
+  if (mlp_wide_supported(N, K, L)) return kMlpWide;
+  if (mlp_pair_supported(N, K, L, w_layout)) return kMlpPair;
+  return kMlpQuad;
+}
+
 size_t mlp_workspace_bytes(int batch, int M, int N, int K, int L, bool bf16, int w_layout, int variant) {
-  const bool pair_ok = mlp_pair_supported(N, K, L, w_layout), quad_ok = quad_supported(N, K, L);
   int slots = 0;
-  if (variant == kMlpQuad || (variant == kMlpAuto && quad_ok)) {
-    if (!quad_ok || mlp_quad_cluster_slots(bf16, &slots) != DITTO_OK) return 0;
-    return plan_workspace_bytes(quad_plan(batch, M, L, slots, true), batch, (M + kRows - 1) / kRows, kRows, N, kCluster);
+  switch (resolve_variant(variant, N, K, L, w_layout)) {
+    case kMlpWide:
+      if (!mlp_wide_supported(N, K, L) || mlp_wide_cluster_slots(bf16, &slots) != DITTO_OK) return 0;
+      return mlp_wide_workspace_bytes(batch, M, N, mlp_wide_plan(batch, M, L, slots, true));
+    case kMlpPair:
+      if (!mlp_pair_supported(N, K, L, w_layout) || mlp_pair_cluster_slots(bf16, &slots) != DITTO_OK) return 0;
+      return mlp_pair_workspace_bytes(batch, M, N, mlp_pair_plan(batch, M, L, slots, true));
+    default:
+      if (!quad_supported(N, K, L) || mlp_quad_cluster_slots(bf16, &slots) != DITTO_OK) return 0;
+      return plan_workspace_bytes(quad_plan(batch, M, L, slots, true), batch, (M + kRows - 1) / kRows, kRows, N, kCluster);
   }
-  if (!pair_ok || mlp_pair_cluster_slots(bf16, &slots) != DITTO_OK) return 0;
-  return mlp_pair_workspace_bytes(batch, M, N, mlp_pair_plan(batch, M, L, slots, true));
 }
 
 int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
                      bool bf16, int w_layout, int act1, int act2, const void* b1, const void* b2, int variant,
                      void* workspace, size_t ws_bytes, int* status, cudaStream_t stream, long long* trace) {
-  const bool pair_ok = mlp_pair_supported(N, K, L, w_layout);
-  if (variant == kMlpPair && !pair_ok) return DITTO_ERR_UNSUPPORTED;
   // With few row blocks -- or a last wave that would leave most of the device idle -- some row blocks are
   // shared by several clusters, if the caller provided the scratch memory that form needs.
-  int slots = 0;
-  // Default: the four-CTA kernel where it covers the shape (measured faster at the benchmark configuration:
-  // its clusters of four fill 132 of the 148 SMs, clusters of eight only 120), the pair kernel for the
-  // shapes only it covers (K that is not a multiple of 64).
-  if (variant == kMlpPair || (variant == kMlpAuto && pair_ok && !quad_supported(N, K, L))) {
-    int rc = mlp_pair_cluster_slots(bf16, &slots);
-    if (rc) return rc;
-    PairPlan plan = mlp_pair_plan(batch, M, L, slots, workspace != nullptr);
-    if (ws_bytes < mlp_pair_workspace_bytes(batch, M, N, plan)) plan = mlp_pair_plan(batch, M, L, slots, false);
-    return launch_mlp_pair(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, act1, act2, b1, b2, plan, workspace, status,
-                           stream, trace);
+  int slots = 0, rc = 0;
+  switch (resolve_variant(variant, N, K, L, w_layout)) {
+    case kMlpWide: {
+      if (!mlp_wide_supported(N, K, L)) return DITTO_ERR_UNSUPPORTED;
+      if ((rc = mlp_wide_cluster_slots(bf16, &slots)) != DITTO_OK) return rc;
+      RowBlockPlan plan = mlp_wide_plan(batch, M, L, slots, workspace != nullptr);
+      if (ws_bytes < mlp_wide_workspace_bytes(batch, M, N, plan)) plan = mlp_wide_plan(batch, M, L, slots, false);
+      return launch_mlp_wide(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, act1, act2, b1, b2, plan, workspace, status,
+                             stream, trace);
+    }
+    case kMlpPair: {
+      if (!mlp_pair_supported(N, K, L, w_layout)) return DITTO_ERR_UNSUPPORTED;
+      if ((rc = mlp_pair_cluster_slots(bf16, &slots)) != DITTO_OK) return rc;
+      PairPlan plan = mlp_pair_plan(batch, M, L, slots, workspace != nullptr);
+      if (ws_bytes < mlp_pair_workspace_bytes(batch, M, N, plan)) plan = mlp_pair_plan(batch, M, L, slots, false);
+      return launch_mlp_pair(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, act1, act2, b1, b2, plan, workspace, status,
+                             stream, trace);
+    }
+    default: {
+      if (!quad_supported(N, K, L)) return DITTO_ERR_UNSUPPORTED;
+      if ((rc = mlp_quad_cluster_slots(bf16, &slots)) != DITTO_OK) return rc;
+      RowBlockPlan plan = quad_plan(batch, M, L, slots, workspace != nullptr);
+      if (ws_bytes < plan_workspace_bytes(plan, batch, (M + kRows - 1) / kRows, kRows, N, kCluster))
+        plan = quad_plan(batch, M, L, slots, false);
+      return launch_mlp_quad(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, act1, act2, b1, b2, plan, workspace, status,
+                             stream, trace);
+    }
   }
-  if (!quad_supported(N, K, L)) return DITTO_ERR_UNSUPPORTED;
-  int rc = mlp_quad_cluster_slots(bf16, &slots);
-  if (rc) return rc;
-  RowBlockPlan plan = quad_plan(batch, M, L, slots, workspace != nullptr);
-  if (ws_bytes < plan_workspace_bytes(plan, batch, (M + kRows - 1) / kRows, kRows, N, kCluster)) plan = quad_plan(batch, M, L, slots, false);
-  return launch_mlp_quad(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, act1, act2, b1, b2, plan, workspace, status, stream,
-                         trace);
 }
 
 }  // namespace ditto_b200

@@ -322,4 +322,27 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// Two exponentials per special-function instruction: 2^x0, 2^x1 evaluated on the packed 16-bit pair and
+// returned packed (low half = first).  The softmax rounds its probabilities to the 16-bit input type
+// before the second GEMM anyway; what is lost is the precision of the argument (x is rounded to 16 bit
+// before the exponential instead of after).
+template <bool BF16>
+__device__ __forceinline__ uint32_t ex2_packed(float x0, float x1) {
+  uint32_t w;
+  if constexpr (BF16) {
+    asm("{\n\t.reg .b32 t;\n\tcvt.rn.bf16x2.f32 t, %2, %1;\n\tex2.approx.ftz.bf16x2 %0, t;\n\t}" : "=r"(w) : "f"(x0), "f"(x1));
+  } else {
+    asm("{\n\t.reg .b32 t;\n\tcvt.rn.f16x2.f32 t, %2, %1;\n\tex2.approx.f16x2 %0, t;\n\t}" : "=r"(w) : "f"(x0), "f"(x1));
+  }
+  return w;
+}
+__device__ __forceinline__ float2 unpack_f16x2(uint32_t w) {
+  float2 r;
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}" : "=f"(r.x), "=f"(r.y) : "r"(w));
+  return r;
+}
+__device__ __forceinline__ float2 unpack_bf16x2(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
 }  // namespace ditto_b200

@@ -143,7 +143,7 @@ def multi_head_attention(qkv, num_heads, out=None, scale=1.0, flags=0):
     return out
 
 
-_VARIANT_BITS = {"auto": 0, "pair": 0x200, "quad": 0x400}
+_VARIANT_BITS = {"auto": 0, "pair": 0x200, "quad": 0x400, "wide": 0x800}
 _workspaces = {}
 
 
@@ -163,7 +163,8 @@ def gemm_relu_gemm(x, w1, w2, out=None, activation="relu", weight_layout="IO", v
     x [batch, M, K] or [M, K]; w1 [batch, K, L] / [K, L]; w2 [batch, L, N] / [L, N] when
     weight_layout == "IO" ([in, out]); "OI" takes the transposed [out, in] weights of
     nn/functional/linear.py.  activation: "relu" or "identity".  variant: "auto" (by shape), "pair"
-    (eight-CTA clusters of CTA pairs, 2-SM MMAs) or "quad" (four-CTA clusters).  workspace: "auto" (this
+    (eight-CTA clusters of CTA pairs, 2-SM MMAs), "quad" (four-CTA clusters, 128-wide hidden chunks) or "wide"
+    (four-CTA clusters, 256-wide hidden chunks).  workspace: "auto" (this
     module keeps a scratch buffer of ditto_b200_workspace_bytes() per device), None (no scratch: every row
     block is computed by one cluster) or a uint8 CUDA tensor.
     """

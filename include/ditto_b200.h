@@ -39,7 +39,8 @@ extern "C" {
 
 /* or-ed into `epilogue` of ditto_b200_gemm_relu_gemm: force one of the two kernels (default: chosen by shape) */
 #define DITTO_EPILOGUE_PAIR_MMA 0x200 /* eight-CTA clusters of CTA pairs, 2-SM MMAs */
-#define DITTO_EPILOGUE_QUAD_MMA 0x400 /* four-CTA clusters, single-SM MMAs */
+#define DITTO_EPILOGUE_QUAD_MMA 0x400 /* four-CTA clusters, single-SM MMAs, 128-wide hidden chunks */
+#define DITTO_EPILOGUE_WIDE_MMA 0x800 /* four-CTA clusters, single-SM MMAs, 256-wide hidden chunks */
 
 #define DITTO_OP_BMM_SOFTMAX_BMM 0
 #define DITTO_OP_GEMM_RELU_GEMM 1
@@ -78,8 +79,8 @@ int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M
  * (benchmark/chimera/cuda/bmm_bmm_cuda.py:69-150).
  *   x [batch, M, K]; w1 [batch, K, L]; w2 [batch, L, N]; y [batch, M, N]
  *   w_layout 0: weights as above ([in, out]); 1: [out, in] as in nn/functional/linear.py:4-41
- *   epilogue 0: identity between the GEMMs; 1: ReLU; | DITTO_EPILOGUE_PAIR_MMA / DITTO_EPILOGUE_QUAD_MMA
- *   forces one of the two kernels (same results up to fp32 summation order; default: by shape)
+ *   epilogue 0: identity between the GEMMs; 1: ReLU; | DITTO_EPILOGUE_PAIR_MMA / _QUAD_MMA / _WIDE_MMA
+ *   forces one of the kernels (same results up to fp32 summation order; default: by shape)
  *   workspace / ws_bytes: optional scratch memory (ditto_b200_workspace_bytes; contents irrelevant on entry,
  *   undefined on return).  With few row blocks several clusters share a row block, each takes a range of the
  *   hidden dimension and the fp32 partials of Y are added through the scratch memory in a fixed order (the
@@ -103,14 +104,15 @@ int ditto_b200_ffn(const void* x, const void* w1, const void* b1, const void* w2
                    void* stream);
 
 /* Scratch bytes with which the op runs fastest at this shape on the current device (0 when none; every call
- * also works without).  `op` may be or-ed with DITTO_EPILOGUE_PAIR_MMA / DITTO_EPILOGUE_QUAD_MMA to ask for the
+ * also works without).  `op` may be or-ed with DITTO_EPILOGUE_PAIR_MMA / DITTO_EPILOGUE_QUAD_MMA / DITTO_EPILOGUE_WIDE_MMA to ask for the
  * kernel that the same bits in `epilogue` select. */
 size_t ditto_b200_workspace_bytes(int op, int batch, int M, int N, int K, int L, int dtype);
 
 /* How many thread-block clusters of the MLP chain kernel the current device holds at once
  * (cudaOccupancyMaxActiveClusters): the number of row blocks -- or, for the pair kernel, (row block,
  * hidden range) items -- that run concurrently; a launch takes ceil(items / slots) waves.
- * variant: DITTO_EPILOGUE_PAIR_MMA (clusters of eight) or DITTO_EPILOGUE_QUAD_MMA (clusters of four).
+ * variant: DITTO_EPILOGUE_PAIR_MMA (clusters of eight), DITTO_EPILOGUE_QUAD_MMA or DITTO_EPILOGUE_WIDE_MMA
+ * (clusters of four).
  * Returns the count, or a negative DITTO_ERR_* code.  No counterpart in the reference (its schedules are
  * sized by the hardware table of python/ditto/hardware/__init__.py:43-54). */
 int ditto_b200_mlp_cluster_slots(int dtype, int variant);
@@ -132,6 +134,13 @@ int ditto_b200_selftest_umma_pair(const void* a, const void* b, float* c, int N,
  * reached the wait gives up, the kernel writes `code` to *status_word and ends normally, and the context
  * stays usable.  Takes about a second.  No counterpart in the reference. */
 int ditto_b200_selftest_wait_limit(int code, int* status_word, void* stream);
+
+/* Waits for `stream`, reads the status word the calls on it were given and returns DITTO_OK if it is zero,
+ * else DITTO_ERR_TIMEOUT (a device-side bounded wait expired in one of them: their outputs are not valid);
+ * the word is cleared again and its value -- which wait gave up -- is stored in *code_out (may be NULL).
+ * The reference reports a failed kernel as a tvm::Error out of the module call
+ * (src/runtime/graph_runtime.cc:212-226 synchronises the same way); no counterpart for the code itself. */
+int ditto_b200_check_status(int* status_word, void* stream, int* code_out);
 
 const char* ditto_b200_strerror(int code);
 /* Text of the last CUDA / driver error seen by the calling thread ("" if none). */

@@ -30,7 +30,10 @@ EXP_SHAPES = ((1, 16), (6, 16), (6, 64))
 
 
 def reference_root():
-    return os.environ.get("DITTO_REFERENCE_ROOT", "/root/reference")
+    """Where the reference's source tree lies: $DITTO_REFERENCE_ROOT, else a `reference` directory beside
+    this repository (the layout of the development container).  A machine without it keeps the prebuilt library."""
+    return os.environ.get("DITTO_REFERENCE_ROOT",
+                          os.path.normpath(os.path.join(HERE, os.pardir, os.pardir, "reference")))
 
 
 def host_flags():

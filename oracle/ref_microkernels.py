@@ -121,3 +121,25 @@ def bmm_softmax_bmm_cpu(Q, K, V, ki1=None, ki2=None):
         E = gemm(P, Vp, ki2)
         out.append(E[:, :N] / E[:, N:N + 1])
     return np.stack(out)
+
+
+def linear(x, weight, bias=None, ki=None):
+    """The reference's linear op (python/ditto/auto_compute/nn/functional/linear.py:4-41): x [M, in] times
+    weight [out, in] transposed, through the GEMM micro-kernel, then the bias add as its own step."""
+    y = gemm(x, np.ascontiguousarray(np.asarray(weight, dtype=np.float32).T), ki)
+    if bias is not None:
+        y = y + np.asarray(bias, dtype=np.float32)[None, :]
+    return y.astype(np.float32)
+
+
+def ffn(x, w1, b1, w2, b2, relu1=True, relu2=True):
+    """The reference's feed-forward block (python/ditto/auto_compute/nn/model/transformer.py:21-34):
+    activation(w_2(activation(w_1(x)))) with biased [out, in] linears; activation = ReLU as
+    if_then_else(v > 0, v, 0) (nn/functional/activation.py:9-26) or, for the variants without it, identity."""
+    h = linear(x, w1, b1)
+    if relu1:
+        h = np.where(h > 0, h, np.float32(0)).astype(np.float32)
+    y = linear(h, w2, b2)
+    if relu2:
+        y = np.where(y > 0, y, np.float32(0)).astype(np.float32)
+    return y

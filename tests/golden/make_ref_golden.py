@@ -20,6 +20,8 @@ OUT = os.path.join(HERE, "ref_microkernels.npz")
 
 # (batch, M, N, K, L): M need not be a multiple of the 6-row tile (the reference pads, bmm_bmm_cpu.py:294)
 CHAIN_SHAPES = ((2, 20, 32, 64, 48), (1, 96, 64, 64, 128), (3, 6, 16, 16, 16))
+# feed-forward block (rows, d_model, d_ff): linear + bias -> ReLU -> linear + bias -> ReLU, weights [out, in]
+FFN_SHAPES = ((20, 32, 64), (96, 64, 128))
 
 
 def exp_inputs():
@@ -57,6 +59,17 @@ def main():
         out[f"c{i}_bmm_softmax_bmm"] = R.bmm_softmax_bmm_cpu(a, b, c)
         # the same with the reduction split into 16-wide chunks (KI1 = KI2 = 16): identical by construction
         assert np.array_equal(out[f"c{i}_bmm_bmm"], R.bmm_bmm(a, b, c, 16, 16))
+    for i, (rows, d_model, d_ff) in enumerate(FFN_SHAPES):
+        rng = np.random.default_rng(600 + i)
+        x = rng.standard_normal((rows, d_model)).astype(np.float32)
+        w1 = (rng.standard_normal((d_ff, d_model)) * d_model ** -0.5).astype(np.float32)
+        b1 = (rng.standard_normal(d_ff) * 0.5).astype(np.float32)
+        w2 = (rng.standard_normal((d_model, d_ff)) * d_ff ** -0.5).astype(np.float32)
+        b2 = (rng.standard_normal(d_model) * 0.5).astype(np.float32)
+        out[f"f{i}_x"], out[f"f{i}_w1"], out[f"f{i}_b1"], out[f"f{i}_w2"], out[f"f{i}_b2"] = x, w1, b1, w2, b2
+        out[f"f{i}_relu_relu"] = R.ffn(x, w1, b1, w2, b2, True, True)
+        out[f"f{i}_relu_identity"] = R.ffn(x, w1, b1, w2, b2, True, False)
+        out[f"f{i}_identity_identity_nobias"] = R.ffn(x, w1, None, w2, None, False, False)
     np.savez_compressed(OUT, **out)
     print("wrote", OUT, os.path.getsize(OUT), "bytes")
 

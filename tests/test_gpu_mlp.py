@@ -58,18 +58,20 @@ QUAD_SHAPES = ((2, 256, 512, 128, 1024), (1, 512, 1024, 256, 1536), (1, 256, 512
 PAIR_SHAPES = ((2, 256, 512, 128, 1024), (1, 512, 1024, 256, 1536), (1, 256, 512, 64, 4096),
                (1, 128, 1024, 192, 512), (2, 208, 1024, 80, 768), (1, 16, 512, 64, 256),
                (3, 384, 512, 960, 2048))
-# Y widths only the [out, in] weight layout of the pair kernel covers (its W2 tiles are K-major)
+# Y widths the 256-wide-chunk kernel covers in both layouts, the pair kernel only with [out, in] weights (K-major W2 tiles)
 PAIR_SHAPES_OI = ((1, 256, 768, 128, 1024), (1, 272, 256, 64, 512))
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 @pytest.mark.parametrize("act", ["relu", "identity"])
 @pytest.mark.parametrize("layout", ["IO", "OI"])
-@pytest.mark.parametrize("variant", ["quad", "pair"])
+@pytest.mark.parametrize("variant", ["quad", "wide", "pair"])
 def test_parity_small(cuda, oracle, dtype, act, layout, variant):
-    """Both kernels, each forced: four-CTA clusters with single-SM MMAs, and eight-CTA clusters of CTA
-    pairs with 2-SM MMAs (no scratch memory here: one cluster per row block)."""
-    shapes = QUAD_SHAPES if variant == "quad" else PAIR_SHAPES + (PAIR_SHAPES_OI if layout == "OI" else ())
+    """Every kernel, each forced: four-CTA clusters with single-SM MMAs and 128-wide or 256-wide hidden
+    chunks, and eight-CTA clusters of CTA pairs with 2-SM MMAs (no scratch memory here: one cluster per row
+    block)."""
+    shapes = {"quad": QUAD_SHAPES, "wide": PAIR_SHAPES + PAIR_SHAPES_OI,
+              "pair": PAIR_SHAPES + (PAIR_SHAPES_OI if layout == "OI" else ())}[variant]
     for (batch, M, N, K, L) in shapes:
         x, w1, w2 = _inputs(21, batch, M, N, K, L, dtype)
         got = _run(cuda, x, w1, w2, dtype, act, layout, variant, workspace=None)
@@ -78,7 +80,7 @@ def test_parity_small(cuda, oracle, dtype, act, layout, variant):
 
 
 @pytest.mark.parametrize("layout", ["IO", "OI"])
-@pytest.mark.parametrize("variant", ["quad", "pair"])
+@pytest.mark.parametrize("variant", ["quad", "wide", "pair"])
 def test_shared_row_blocks(cuda, oracle, layout, variant):
     """Few row blocks (or a last wave that would leave most of the device idle): some row blocks are shared
     by several clusters, each takes a range of the hidden dimension, and the fp32 partials of Y are combined
@@ -89,7 +91,7 @@ def test_shared_row_blocks(cuda, oracle, layout, variant):
     split_cases = 0
     for (batch, M, N, K, L) in ((1, 16, 1024, 128, 4096), (1, 256, 1024, 256, 4096), (2, 208, 512, 64, 2048),
                                 (1, 2048, 1024, 256, 4096), (1, 4352, 512, 64, 1024)):
-        bits = _lib.EPILOGUE_PAIR_MMA if variant == "pair" else _lib.EPILOGUE_QUAD_MMA
+        bits = {"pair": _lib.EPILOGUE_PAIR_MMA, "quad": _lib.EPILOGUE_QUAD_MMA, "wide": _lib.EPILOGUE_WIDE_MMA}[variant]
         need = lib.ditto_b200_workspace_bytes(_lib.OP_GEMM_RELU_GEMM | bits, batch, M, N, K, L, _lib.DTYPE_BF16)
         if need == 0:
             continue        # the planner found nothing to gain at this shape on this device

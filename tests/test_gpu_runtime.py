@@ -96,6 +96,16 @@ def test_expired_wait_is_reported_not_fatal(cuda):
     torch.cuda.synchronize(cuda)
     assert int(status.item()) == 0x6A1
     assert lib.ditto_b200_selftest_wait_limit(0, status.data_ptr(), None) == _lib.ERR_INVALID_ARG
+    # the same report through the C ABI's helper: DITTO_ERR_TIMEOUT with the code, and the word is cleared
+    import ctypes
+    with torch.cuda.device(cuda):
+        stream = torch.cuda.current_stream().cuda_stream
+        status.zero_()                  # the word keeps the first code it was given until somebody clears it
+        assert lib.ditto_b200_selftest_wait_limit(0x6A2, status.data_ptr(), stream) == 0
+        code = ctypes.c_int(0)
+        assert lib.ditto_b200_check_status(status.data_ptr(), stream, ctypes.byref(code)) == _lib.ERR_TIMEOUT
+        assert code.value == 0x6A2 and int(status.item()) == 0
+        assert lib.ditto_b200_check_status(status.data_ptr(), stream, None) == _lib.OK
     q = (torch.rand(2, 256, 64, device=cuda) - 0.5).half()
     out = ops.bmm_softmax_bmm(q, q, q, scale=1.0, key_layout="LK")
     assert ops.device_status(cuda) == 0

@@ -201,6 +201,25 @@ def test_reference_microkernel_golden_chains(oracle):
     assert i == 3
 
 
+def test_reference_microkernel_golden_ffn(oracle):
+    """The feed-forward block -- linear + bias -> ReLU -> linear + bias -> ReLU with [out, in] weights
+    (nn/model/transformer.py:21-34, nn/functional/linear.py:4-41) -- evaluated through the reference's GEMM
+    micro-kernel: the C restatement `oracle_ffn` (fp32, no rounding of the hidden layer) agrees to 1e-6."""
+    g = np.load(REF_GOLDEN)
+    i = 0
+    while f"f{i}_x" in g:
+        x, w1, b1, w2, b2 = (g[f"f{i}_{k}"] for k in ("x", "w1", "b1", "w2", "b2"))
+        io1, io2 = np.ascontiguousarray(w1.T)[None], np.ascontiguousarray(w2.T)[None]
+        for key, a1, a2, bias in (("relu_relu", 1, 1, True), ("relu_identity", 1, 0, True),
+                                  ("identity_identity_nobias", 0, 0, False)):
+            got = oracle.ffn(x[None], io1, b1[None] if bias else None, io2, b2[None] if bias else None, a1, a2,
+                             oracle.FP32)[0]
+            want = g[f"f{i}_{key}"]
+            assert np.max(np.abs(got - want)) <= 1e-6 * np.max(np.abs(want)) + 1e-6, (i, key)
+        i += 1
+    assert i == 2
+
+
 def test_reference_microkernels_live(oracle):
     """Where the reference tree (or the library built from it) is present: fresh seeded inputs through the
     reference's micro-kernels against the restatement, so the pin is not limited to the committed cases."""
@@ -216,6 +235,13 @@ def test_reference_microkernels_live(oracle):
         assert np.array_equal(_bits(oracle.baseline_chain_fp32(a, b, c, 1)), _bits(R.bmm_relu_bmm(a, b, c)))
         if R.has_exp():
             assert np.array_equal(_bits(oracle.bmm_softmax_bmm_cpu_literal(a, b, c)), _bits(R.bmm_softmax_bmm_cpu(a, b, c)))
+    x = rng.standard_normal((14, 32)).astype(np.float32)
+    w1, w2 = rng.standard_normal((48, 32)).astype(np.float32) / 6, rng.standard_normal((32, 48)).astype(np.float32) / 7
+    b1, b2 = rng.standard_normal(48).astype(np.float32), rng.standard_normal(32).astype(np.float32)
+    got = oracle.ffn(x[None], np.ascontiguousarray(w1.T)[None], b1[None], np.ascontiguousarray(w2.T)[None], b2[None], 1, 1,
+                     oracle.FP32)[0]
+    want = R.ffn(x, w1, b1, w2, b2, True, True)
+    assert np.max(np.abs(got - want)) <= 1e-6 * np.max(np.abs(want)) + 1e-6
     if R.has_exp():
         x = rng.normal(0, 20, (24, 64)).astype(np.float32)
         assert np.array_equal(_bits(oracle.exp_ref_literal(x)), _bits(R.exp(x)))
