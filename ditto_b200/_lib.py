@@ -30,6 +30,7 @@ EPILOGUE_WIDE_MMA = 0x800
 EXPORTS = (
     "ditto_b200_bmm_softmax_bmm",
     "ditto_b200_gemm_relu_gemm",
+    "ditto_b200_gemm_relu_gemm_static_scratch",
     "ditto_b200_multi_head_attention",
     "ditto_b200_ffn",
     "ditto_b200_workspace_bytes",
@@ -78,6 +79,8 @@ def load():
     lib.ditto_b200_bmm_softmax_bmm.restype = i
     lib.ditto_b200_gemm_relu_gemm.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, i, vp, sz, vp, vp]
     lib.ditto_b200_gemm_relu_gemm.restype = i
+    lib.ditto_b200_gemm_relu_gemm_static_scratch.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, i, vp, vp]
+    lib.ditto_b200_gemm_relu_gemm_static_scratch.restype = i
     lib.ditto_b200_multi_head_attention.argtypes = [vp, vp, i, i, i, i, i, f, i, vp, vp]
     lib.ditto_b200_multi_head_attention.restype = i
     lib.ditto_b200_ffn.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, i, vp, vp]

@@ -215,6 +215,20 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
                                       static_cast<cudaStream_t>(stream), trace);
 }
 
+int ditto_b200_gemm_relu_gemm_static_scratch(const void* x, const void* w1, const void* w2, void* y, int batch, int M,
+                                             int N, int K, int L, int dtype, int w_layout, int epilogue,
+                                             int* status_word, void* stream) {
+  if (!x || !w1 || !w2 || !y) return DITTO_ERR_INVALID_ARG;
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0 || L <= 0) return DITTO_ERR_INVALID_ARG;
+  if (!aligned16(x) || !aligned16(w1) || !aligned16(w2) || !aligned16(y)) return DITTO_ERR_INVALID_ARG;
+  if (dtype != DITTO_DTYPE_FP16 && dtype != DITTO_DTYPE_BF16) return DITTO_ERR_UNSUPPORTED;
+  if (w_layout != 0 && w_layout != 1) return DITTO_ERR_INVALID_ARG;
+  if (epilogue != 0 && epilogue != 1) return DITTO_ERR_INVALID_ARG;
+  if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
+  return ditto_b200::launch_mlp_static_scratch(x, w1, w2, y, batch, M, N, K, L, dtype == DITTO_DTYPE_BF16, w_layout,
+                                               epilogue, status_word, static_cast<cudaStream_t>(stream));
+}
+
 int ditto_b200_ffn(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, void* y, int batch,
                    int M, int N, int K, int L, int dtype, int w_layout, int act1, int act2, int* status_word,
                    void* stream) {

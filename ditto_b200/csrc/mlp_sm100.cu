@@ -658,6 +658,47 @@ int mlp_quad_cluster_slots(bool bf16, int* slots) {
   return DITTO_OK;
 }
 
+// ------------------------------------------------------------------ the chain without caller-provided scratch
+// Scratch memory that belongs to the library image instead of the caller: a fixed array in device memory
+// that every GPU holds from the moment it loads this library until the process exits.
+constexpr size_t kStaticScratchBytes = 12u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int launch_mlp_static_scratch(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
+                              bool bf16, int w_layout, int act1, int* status, cudaStream_t stream) {
+  if (!quad_supported(N, K, L)) return DITTO_ERR_UNSUPPORTED;
+  // In host code `g_static_scratch` is only a handle for the symbol, not an address the GPU can use: the
+  // array's device address is looked up once per device, with that device current, and kept.
+  static std::atomic<unsigned char*> scratch_of_device[kMaxDevices];
+  int dev = 0;
+  cudaError_t e = current_device_checked(&dev);
+  if (e != cudaSuccess) return cuda_fail("static-scratch set-up", e);
+  unsigned char* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) return cuda_fail("static-scratch set-up (cudaGetSymbolAddress)", e);
+    scratch = static_cast<unsigned char*>(ptr);
+    scratch_of_device[dev].store(scratch, std::memory_order_release);
+  }
+  int slots = 0;
+  int rc = mlp_quad_cluster_slots(bf16, &slots);
+  if (rc) return rc;
+  const RowBlockPlan plan = quad_plan(batch, M, L, slots, true);
+  const size_t need = plan_workspace_bytes(plan, batch, (M + kRows - 1) / kRows, kRows, N, kCluster);
+  if (need > kStaticScratchBytes) {
+    char msg[160];
+    std::snprintf(msg, sizeof(msg), "this shape needs %zu bytes of scratch memory, the built-in array holds %zu; "
+                  "use ditto_b200_gemm_relu_gemm with a workspace", need, kStaticScratchBytes);
+    set_error("ditto_b200_gemm_relu_gemm_static_scratch", msg);
+    return DITTO_ERR_WORKSPACE;
+  }
+  // The counters at the end of the used part are cleared by the launch itself (cudaMemsetAsync on `stream`);
+  // the partial-result slabs are written before they are read and need no clearing.
+  return launch_mlp_quad(x, w1, w2, y, batch, M, N, K, L, bf16, w_layout, act1, 0, nullptr, nullptr, plan, scratch, status,
+                         stream, nullptr);
+}
+
 // Which kernel an "auto" call takes: the 256-wide-chunk kernel where it covers the shape (measured fastest at
 // the benchmark configuration), the 128-wide one for hidden sizes that are only multiples of 128, the pair
 // kernel for what neither covers.

@@ -29,6 +29,11 @@ int launch_mlp_chain(const void* x, const void* w1, const void* w2, void* y, int
 // Scratch bytes with which the chain runs fastest at this shape on the current device (0: none needed).
 size_t mlp_workspace_bytes(int batch, int M, int N, int K, int L, bool bf16, int w_layout, int variant);
 
+// The four-CTA kernel with the library's own scratch array in place of a caller-provided workspace
+// (see ditto_b200_gemm_relu_gemm_static_scratch).  Allocates nothing.
+int launch_mlp_static_scratch(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
+                              bool bf16, int w_layout, int act1, int* status, cudaStream_t stream);
+
 // Clusters of four CTAs of the four-CTA kernel the current device holds at once (queried once per device).
 int mlp_quad_cluster_slots(bool bf16, int* slots);
 

@@ -91,6 +91,30 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
                               int K, int L, int dtype, int w_layout, int epilogue, void* workspace,
                               size_t ws_bytes, int* status_word, void* stream);
 
+/* The MLP chain for callers that cannot allocate device memory.  No counterpart in the reference.
+ *
+ * ditto_b200_gemm_relu_gemm runs fastest on few row blocks when it is handed scratch memory, and somebody has
+ * to own that memory.  Some callers cannot: code that runs while a CUDA graph is being captured or inside a
+ * library's callback, where cudaMalloc is forbidden or would synchronise the device; plugins whose host hands
+ * them input and output buffers and nothing else; services with a fixed memory budget decided at start-up.
+ * For them the scratch memory is part of the library image: a 12 MiB array in device memory, which every GPU
+ * that loads the library holds until the process exits.  This entry point and everything under it call no
+ * cudaMalloc, cudaFree or other allocating routine.
+ *
+ *   Arguments as ditto_b200_gemm_relu_gemm without workspace / ws_bytes; epilogue 0 or 1 (no kernel bits: the
+ *   four-CTA kernel is used).  Shapes: L % 128 == 0, K % 64 == 0, N in {256, 512, 768, 1024}, M % 16 == 0.
+ *   Results are those of ditto_b200_gemm_relu_gemm | DITTO_EPILOGUE_QUAD_MMA with a workspace, bit for bit.
+ *   Limit: a shape whose plan needs more than the 12 MiB returns DITTO_ERR_WORKSPACE (text in
+ *   ditto_b200_last_cuda_error()) and launches nothing; use the entry point with a caller workspace then.
+ *   First call on a device: looks up the array's device address (cudaGetSymbolAddress, with that device
+ *   current) and the kernel's attributes, and keeps them.  Make that first call outside any stream capture.
+ *   Every call on a device uses the same array.  The part that must start at zero (a few counters) is cleared
+ *   on `stream` in front of the kernel; the rest is written before it is read.  Two calls that overlap on the
+ *   GPU (different streams, no dependency) race on it: order them, or give one of them its own workspace. */
+int ditto_b200_gemm_relu_gemm_static_scratch(const void* x, const void* w1, const void* w2, void* y, int batch, int M,
+                                             int N, int K, int L, int dtype, int w_layout, int epilogue,
+                                             int* status_word, void* stream);
+
 /* Position-wise feed-forward block  y = act2(act1(X W1 + b1) W2 + b2)  with the hidden layer on chip, the
  * fused form of PositionwiseFeedForward (python/ditto/auto_compute/nn/model/transformer.py:21-34:
  * linear -> ReLU -> linear -> ReLU, linear with bias as in nn/functional/linear.py:4-41; GELU as in
