@@ -132,42 +132,73 @@ def device_seed(w: Workload, index: int, tensor: int):
     return (1000 * w.cfg + index) * 8 + tensor
 
 
-def _device_draw(torch, seed, shape, w, device, std=1.0):
-    g = torch.Generator(device=device).manual_seed(seed)
+def _mix64(torch, k):
+    """murmur3's 64-bit finaliser on int64 tensors (multiplication wraps; shifts are made logical by masking)."""
+    k = k ^ ((k >> 33) & 0x7FFFFFFF)
+    k = k * -49064778989728563          # 0xff51afd7ed558ccd
+    k = k ^ ((k >> 33) & 0x7FFFFFFF)
+    k = k * -4265267296055464877        # 0xc4ceb9fe1a85ec53
+    return k ^ ((k >> 33) & 0x7FFFFFFF)
+
+
+def _device_units(torch, w, seeds, elems, device, std=1.0):
+    """[len(seeds), elems] values in the storage type: unit u depends only on seeds[u] (a counter-based
+    generator: value j of a unit = hash(seed, j) -> Box-Muller), so it is the same whichever units are drawn
+    beside it.  A few element-wise launches per call, whatever the number of units."""
     tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[w.dtype]
+    base = torch.tensor([_mix64_int(s) for s in seeds], dtype=torch.int64, device=device).reshape(-1, 1)
+    k = _mix64(torch, base + torch.arange(elems, dtype=torch.int64, device=device).reshape(1, -1))
+    u1 = (((k >> 40) & 0xFFFFFF).to(torch.float32) + 0.5) * (1.0 / (1 << 24))
+    u2 = (((k >> 16) & 0xFFFFFF).to(torch.float32) + 0.5) * (1.0 / (1 << 24))
+    del k
     if w.dist == "uniform":
-        return (torch.rand(*shape, device=device, generator=g) * 2 - 1).to(tdt)
-    return (torch.randn(*shape, device=device, generator=g) * std).to(tdt)
+        return (u1 * 2 - 1).to(tdt)
+    u1.log_().mul_(-2.0).sqrt_()
+    u2.mul_(6.283185307179586).cos_()
+    return u1.mul_(u2).mul_(std).to(tdt)
 
 
-def device_attention_inputs(w: Workload, lo: int, hi: int, device):
+def _mix64_int(x):
+    """The same finaliser on a Python int (wrapping to signed 64 bit), for the per-unit seeds."""
+    m = (1 << 64) - 1
+    x &= m
+    x ^= x >> 33
+    x = (x * 0xff51afd7ed558ccd) & m
+    x ^= x >> 33
+    x = (x * 0xc4ceb9fe1a85ec53) & m
+    x ^= x >> 33
+    return x - (1 << 64) if x >= (1 << 63) else x
+
+
+def device_attention_inputs(w: Workload, lo: int, hi: int, device, units_per_call=128):
     """Q [n, M, K], K [n, L, K], V [n, L, N] of slices [lo, hi) as device tensors in the storage type."""
     import torch
     tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[w.dtype]
     n = hi - lo
-    q = torch.empty(n, w.M, w.K, dtype=tdt, device=device)
-    k = torch.empty(n, w.L, w.K, dtype=tdt, device=device)
-    v = torch.empty(n, w.L, w.N, dtype=tdt, device=device)
-    for i in range(lo, hi):
-        q[i - lo] = _device_draw(torch, device_seed(w, i, 0), (w.M, w.K), w, device)
-        k[i - lo] = _device_draw(torch, device_seed(w, i, 1), (w.L, w.K), w, device)
-        v[i - lo] = _device_draw(torch, device_seed(w, i, 2), (w.L, w.N), w, device)
-    return q, k, v
+    out = []
+    for t, (rows, cols) in enumerate(((w.M, w.K), (w.L, w.K), (w.L, w.N))):
+        x = torch.empty(n, rows, cols, dtype=tdt, device=device)
+        for a in range(lo, hi, units_per_call):
+            b = min(a + units_per_call, hi)
+            seeds = [device_seed(w, i, t) for i in range(a, b)]
+            x[a - lo:b - lo] = _device_units(torch, w, seeds, rows * cols, device).reshape(b - a, rows, cols)
+        out.append(x)
+    return tuple(out)
 
 
 def device_mlp_inputs(w: Workload, lo: int, hi: int, device):
     """X rows of 128-row blocks [lo, hi) as a device tensor [(hi - lo) * 128, K]."""
     import torch
-    tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[w.dtype]
-    x = torch.empty((hi - lo) * 128, w.K, dtype=tdt, device=device)
-    for b in range(lo, hi):
-        x[(b - lo) * 128:(b - lo + 1) * 128] = _device_draw(torch, device_seed(w, b, 0), (128, w.K), w, device)
-    return x
+    seeds = [device_seed(w, b, 0) for b in range(lo, hi)]
+    if not seeds:
+        tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[w.dtype]
+        return torch.empty(0, w.K, dtype=tdt, device=device)
+    return _device_units(torch, w, seeds, 128 * w.K, device).reshape((hi - lo) * 128, w.K)
 
 
 def device_mlp_weights(w: Workload, device):
     """W1 [K, L] ~ N(0, 1/K), W2 [L, N] ~ N(0, 1/L): the same on every rank."""
     import torch
-    w1 = _device_draw(torch, device_seed(w, 0, 5), (w.K, w.L), w, device, w.K ** -0.5)
-    w2 = _device_draw(torch, device_seed(w, 0, 6), (w.L, w.N), w, device, w.L ** -0.5)
+    w1 = _device_units(torch, w, [device_seed(w, 0, 5)], w.K * w.L, device, w.K ** -0.5).reshape(w.K, w.L)
+    w2 = _device_units(torch, w, [device_seed(w, 0, 6)], w.L * w.N, device, w.L ** -0.5).reshape(w.L, w.N)
     return w1, w2
