@@ -170,7 +170,7 @@ def _mix64_int(x):
     return x - (1 << 64) if x >= (1 << 63) else x
 
 
-def device_attention_inputs(w: Workload, lo: int, hi: int, device, units_per_call=128):
+def device_attention_inputs(w: Workload, lo: int, hi: int, device, units_per_call=512):
     """Q [n, M, K], K [n, L, K], V [n, L, N] of slices [lo, hi) as device tensors in the storage type."""
     import torch
     tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[w.dtype]
