@@ -63,11 +63,13 @@ int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void
   // The reference asserts multiples of 16 (bmm_chain.py:34-38); so does this entry point.  Partial
   // 128-row tiles are handled by TMA zero fill, masked scores and predicated stores.
   if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
-  if (N != K || K > 128) return DITTO_ERR_UNSUPPORTED;
+  if (K > 128 || N > 128) return DITTO_ERR_UNSUPPORTED;
   if (static_cast<long long>(batch) * ((M + 127) / 128) > 0x7fffffffLL) return DITTO_ERR_UNSUPPORTED;
 
   const bool bf16 = dtype == DITTO_DTYPE_BF16;
-  const int d = K <= 64 ? 64 : 128;             // kernel variant; K itself may be any multiple of 16 below it
+  // kernel variant by the wider of the two widths; K (the reduction of Q K^T) and N (the width of V and of the
+  // output) may differ and be any multiples of 16 below it, as in the reference's definition (bmm_chain.py:28-38)
+  const int d = (K <= 64 && N <= 64) ? 64 : 128;
   int nt = (M > 128 && !(flags & DITTO_FLAG_ONE_TILE)) ? 2 : 1;
   // d <= 64: one tile per CTA with separate S / P columns, two CTAs per SM (see attention_sm100.cu)
   if (d == 64 && !(flags & (DITTO_FLAG_TWO_TILES | DITTO_FLAG_P_VIA_SMEM))) nt = 1;
@@ -83,15 +85,17 @@ int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void
   else
     rc = make_map_3d(&p.map_k, bf16, k, uK, uL, ub, uK, uL * uK, 64, 128);
   if (rc) return rc;
-  rc = make_map_3d(&p.map_v, bf16, v, uK, uL, ub, uK, uL * uK, 64, 128);
+  const uint64_t uN = N;
+  rc = make_map_3d(&p.map_v, bf16, v, uN, uL, ub, uN, uL * uN, 64, 128);
   if (rc) return rc;
   p.out = out;
   p.M = M;
   p.L = L;
   p.k_transposed = (k_layout == 0);
   p.d = K;
+  p.dv = N;
   p.heads = 1;
-  p.out_ld = K;
+  p.out_ld = N;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word;
 #ifdef DITTO_TRACE
@@ -134,6 +138,7 @@ int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M
   p.L = M;
   p.k_transposed = 0;
   p.d = head_dim;
+  p.dv = head_dim;
   p.heads = heads;
   p.q_col0 = 0;
   p.k_col0 = hidden;
@@ -164,14 +169,14 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
   if (act != 0 && act != 1) return DITTO_ERR_INVALID_ARG;
   if (variant_bits & (variant_bits - 1)) return DITTO_ERR_INVALID_ARG;   // at most one kernel can be named
   if (M % 16 || N % 16 || K % 16 || L % 16) return DITTO_ERR_INVALID_ARG;
-  if (N == K && K <= 128) {
+  if (N <= 128 && K <= 128) {
     // Small-N chains (the reference's shape family: N = K = 64, L = 512 ...): the result tile
     // [128, N] fits TMEM next to the intermediate, so the chain runs on the attention kernel with
     // the activation in place of the softmax: A = x, B = w1, C = w2.
     if (static_cast<long long>(batch) * ((M + 127) / 128) > 0x7fffffffLL) return DITTO_ERR_UNSUPPORTED;
     if (w_layout != 0) return DITTO_ERR_UNSUPPORTED;   // w2 as [N, L] is not an operand form of that kernel
     const bool bf16 = dtype == DITTO_DTYPE_BF16;
-    const int dk = K <= 64 ? 64 : 128;
+    const int dk = (K <= 64 && N <= 64) ? 64 : 128;
     ditto_b200::AttnParams p;
     std::memset(&p, 0, sizeof(p));
     const uint64_t uK = K, uM = M, uL = L, ub = batch;
@@ -179,13 +184,15 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
     if (rc) return rc;
     rc = make_map_3d(&p.map_k, bf16, w1, uL, uK, ub, uL, uK * uL, 64, dk);
     if (rc) return rc;
-    rc = make_map_3d(&p.map_v, bf16, w2, uK, uL, ub, uK, uL * uK, 64, 128);
+    const uint64_t uN = N;
+    rc = make_map_3d(&p.map_v, bf16, w2, uN, uL, ub, uN, uL * uN, 64, 128);
     if (rc) return rc;
     p.out = y;
     p.M = M;
     p.L = L;
     p.k_transposed = 1;
     p.d = K;
+    p.dv = N;
     p.heads = 1;
     p.out_ld = N;
     p.scale_log2 = 1.0f;
@@ -250,7 +257,7 @@ size_t ditto_b200_workspace_bytes(int op, int batch, int M, int N, int K, int L,
   // it runs faster when several clusters share a row block and combine fp32 partials of Y through scratch
   // memory (the hidden activations still never leave the chip); the call works without it.
   if ((op & 0xff) != DITTO_OP_GEMM_RELU_GEMM || batch <= 0 || M <= 0 || N <= 0 || K <= 0 || L <= 0) return 0;
-  if (N == K && K <= 128) return 0;
+  if (N <= 128 && K <= 128) return 0;
   // `op` may carry DITTO_EPILOGUE_PAIR_MMA / DITTO_EPILOGUE_QUAD_MMA like the call's `epilogue` argument
   const int variant = (op & DITTO_EPILOGUE_PAIR_MMA)   ? ditto_b200::kMlpPair
                       : (op & DITTO_EPILOGUE_QUAD_MMA) ? ditto_b200::kMlpQuad

@@ -398,7 +398,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_persistent_kernel(const
 #pragma unroll
         for (int u = 0; u < 4; ++u)
           w[u] = pack2<BF16>(__uint_as_float(o[8 * i + 2 * u]) * inv, __uint_as_float(o[8 * i + 2 * u + 1]) * inv);
-        if (grow < p.M && i * 8 < p.d) *reinterpret_cast<uint4*>(orow + i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        if (grow < p.M && i * 8 < p.dv) *reinterpret_cast<uint4*>(orow + i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
       }
       DITTO_STAMP(it * 16 + 14);
     }

@@ -533,7 +533,7 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
           w[i] = pack2<BF16>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          if (grow < p.M && cc + i * 8 < p.d)          // d is a multiple of 16: whole 16-byte pieces
+          if (grow < p.M && cc + i * 8 < p.dv)         // widths are multiples of 16: whole 16-byte pieces
             *reinterpret_cast<uint4*>(orow + cc * 2 + i * 16) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
       }
     }

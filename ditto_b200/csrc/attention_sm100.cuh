@@ -10,11 +10,12 @@ namespace ditto_b200 {
 struct AttnParams {
   CUtensorMap map_q;  // [batch, M, d] (or the packed [batch, M, 3*hidden]), box 64 x 128 x 1, 128B swizzle
   CUtensorMap map_k;  // [batch, L, d] (box 64 x 128 x 1) or, transposed, [batch, d, L] (box 64 x D x 1)
-  CUtensorMap map_v;  // [batch, L, d], box 64 x 128 x 1
-  void* out;          // [batch, M, d] fp16 / bf16
+  CUtensorMap map_v;  // [batch, L, dv], box 64 x 128 x 1
+  void* out;          // [batch, M, dv] fp16 / bf16
   int M;              // query rows per sequence (any multiple of 16)
   int L;              // key/value rows per sequence (any multiple of 16)
-  int d;              // head dimension in use (multiple of 16, <= the kernel's D)
+  int d;              // width of Q and K in use: the reduction length of S = Q K^T (multiple of 16, <= the kernel's D)
+  int dv;             // width of V and of the output (multiple of 16, <= the kernel's D); columns beyond it are zero-filled / not stored
   int k_transposed;   // 1: K stored [batch, D, L] (the reference's layout)
   int heads;          // 1, or heads folded into the slice index of a packed [sequences, rows, cols] input
   int q_col0, k_col0, v_col0;  // first column of Q / K / V inside the packed row (0 when not packed)

@@ -58,7 +58,7 @@ extern "C" {
  *   k_layout 1: key is [batch, L, K]
  *   scale 1.0 reproduces the reference's exp(QK^T)/sum semantics; the softmax is evaluated in the
  *   max-subtracted form, which is the same function without the overflow.
- * Supported: N == K <= 128; M, N, K, L multiples of 16 like the reference asserts (partial 128-row tiles are
+ * Supported: K <= 128 and N <= 128 (they may differ, as in the reference's definition); M, N, K, L multiples of 16 like the reference asserts (partial 128-row tiles are
  * zero-filled by TMA, masked and not stored); fp16 or bf16 in/out, fp32 accumulate. */
 int ditto_b200_bmm_softmax_bmm(const void* q, const void* k, const void* v, void* out, int batch, int M, int N,
                                int K, int L, int dtype, int k_layout, float scale, int flags, void* workspace,
@@ -85,7 +85,7 @@ int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M
  *   undefined on return).  With few row blocks several clusters share a row block, each takes a range of the
  *   hidden dimension and the fp32 partials of Y are added through the scratch memory in a fixed order (the
  *   hidden activations still never leave the chip).  NULL or too small: one cluster per row block.
- * Shapes: N == K <= 128 (any multiples of 16, [in, out] weights): the reference's own shape family;
+ * Shapes: N <= 128 and K <= 128 (any multiples of 16, [in, out] weights): the reference's own shape family;
  * otherwise L % 128 == 0, K % 64 == 0 (K % 16 == 0 where L % 256 == 0), N in {256, 512, 768, 1024}; M any multiple of 16. */
 int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N,
                               int K, int L, int dtype, int w_layout, int epilogue, void* workspace,

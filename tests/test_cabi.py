@@ -50,7 +50,7 @@ def test_argument_errors_are_synchronous():
     assert call(p, p, p, p, 1, 128, 64, 64, 128, 0, 1, -1.0, 0, None, 0, None, None) == _lib.ERR_INVALID_ARG
     assert call(p, p, p, p, 1, 128, 64, 64, 128, 7, 1, 1.0, 0, None, 0, None, None) == _lib.ERR_UNSUPPORTED  # dtype
     assert call(p, p, p, p, 1, 128, 144, 144, 128, 0, 1, 1.0, 0, None, 0, None, None) == _lib.ERR_UNSUPPORTED  # d > 128
-    assert call(p, p, p, p, 1, 128, 64, 80, 128, 0, 1, 1.0, 0, None, 0, None, None) == _lib.ERR_UNSUPPORTED  # N != K
+    assert call(p, p, p, p, 1, 128, 144, 64, 128, 0, 1, 1.0, 0, None, 0, None, None) == _lib.ERR_UNSUPPORTED  # N > 128
     mlp = lib.ditto_b200_gemm_relu_gemm
     assert mlp(None, p, p, p, 1, 128, 64, 64, 128, 1, 0, 1, None, 0, None, None) == _lib.ERR_INVALID_ARG
     assert mlp(p, p, p, p, 1, 128, 64, 64, 128, 1, 0, 5, None, 0, None, None) == _lib.ERR_INVALID_ARG

@@ -304,3 +304,20 @@ def test_umma_pair_building_block(cuda, b_mn, dtype):
         assert rc == 0 and int(status.item()) == 0
         want = a.astype(np.float64) @ (b if b_mn else b.T).astype(np.float64)
         np.testing.assert_allclose(c.cpu().numpy(), want, rtol=1e-5, atol=2e-4)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_value_width_differs_from_key_width(cuda, oracle, dtype):
+    """N != K: the reference's definition takes the width of V / the output (N) and the reduction length of
+    Q K^T (K) independently (bmm_chain.py:28-38).  Both layouts of K, ragged rows included."""
+    for (batch, M, N, K, L) in ((2, 256, 128, 64, 256), (3, 208, 64, 128, 272), (1, 128, 48, 80, 144),
+                                (2, 384, 32, 64, 1040), (1, 512, 112, 16, 512)):
+        rng = np.random.default_rng(97)
+        q = W._round(rng.standard_normal((batch, M, K)).astype(np.float32), dtype)
+        k = W._round(rng.standard_normal((batch, L, K)).astype(np.float32), dtype)
+        v = W._round(rng.standard_normal((batch, L, N)).astype(np.float32), dtype)
+        want = _oracle(oracle, q, k, v, dtype, K ** -0.5)
+        for layout in ("LK", "KL"):
+            got = _run(cuda, q, k, v, dtype, K ** -0.5, layout)
+            assert got.shape == (batch, M, N)
+            assert_close(got, want, dtype, f"{dtype} N != K {(batch, M, N, K, L)} {layout}")

@@ -199,6 +199,20 @@ def test_small_n_chains(cuda, oracle, dtype, act, d):
         assert_close(got, want, dtype, f"{dtype} {act} d={d} {(batch, M, L)}", scale=float(np.abs(want).max()))
 
 
+@pytest.mark.parametrize("act", ["relu", "identity"])
+def test_small_n_chains_with_different_widths(cuda, oracle, act):
+    """N != K, both <= 128: (A B) C with A [M, K], B [K, L], C [L, N] on the attention kernel's chain mode."""
+    dtype = "float16"
+    for (batch, M, N, K, L) in ((2, 256, 128, 64, 256), (3, 208, 64, 128, 272), (1, 128, 48, 80, 144), (2, 384, 32, 64, 1040)):
+        rng = np.random.default_rng(33)
+        a = W._round(rng.uniform(-1, 1, (batch, M, K)).astype(np.float32), dtype)
+        b = W._round(rng.uniform(-1, 1, (batch, K, L)).astype(np.float32), dtype)
+        c = W._round(rng.uniform(-1, 1, (batch, L, N)).astype(np.float32), dtype)
+        got = _run(cuda, a, b, c, dtype, act, "IO")
+        want = oracle.gemm_act_gemm(a, b, c, 1 if act == "relu" else 0, ODT[dtype], wide=False)
+        assert_close(got, want, dtype, f"{act} N != K {(batch, M, N, K, L)}", scale=float(np.abs(want).max()))
+
+
 def test_small_n_golden_and_cfg1_shape(cuda, oracle):
     case = "chain_fp16_identity"
     w = make_golden.workload(case)
