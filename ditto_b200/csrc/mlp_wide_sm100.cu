@@ -24,10 +24,11 @@
 // shared::cta -> shared::cluster bulk copies.  Hidden activations exist only in tensor memory and
 // (distributed) shared memory.  No TMA load in this file uses cluster multicast.
 //
-// Roles (14 warps): 0-7 epilogue (warp w: TMEM lanes 32 (w % 4) ..., column half w / 4), 8 and 12 GEMM1
-// operand producers (alternate stages), 9 GEMM1 issuer, 10 GEMM2 operand producer, 13 GEMM2 issuer (both
-// issuers converged, one elected lane issues), 11 free relay (tells the CTA that writes a unit slot next that
-// this CTA's GEMM2 is done with it).
+// Roles (12 warps -- registers are handed out to warps in fours, a thirteenth would cost every thread 40):
+// 0-7 epilogue (warp w: TMEM lanes 32 (w % 4) ..., column half w / 4), 8 GEMM1 operand producer, 9 GEMM1
+// issuer, 10 GEMM2 operand producer, 11 GEMM2 issuer (both issuers converged, one elected lane issues).
+// A unit's slot is free when all four CTAs have multiplied the unit: each CTA's GEMM2 completion arrives, by a
+// multicast tcgen05.commit, directly on the barrier of the CTA that writes the slot next.
 // Operands: a GEMM1 stage holds one k-step (X 128 x 64 and the W1 tile 64 x 256, 48 KB); a GEMM2 stage one W2
 // tile (64 x N/4, 32 KB); each GEMM has its own ring.
 // One issuing warp per GEMM: an issuer pays a few hundred clocks per stage for the barrier wait, the four MMAs
@@ -38,11 +39,16 @@
 // inside a round quarter by quarter across the CTAs, which is the order they arrive in -- and live in slot
 // n % kUnits of every CTA.
 //
-// Work items.  An item is (row block, hidden range): some row blocks may be shared by several clusters,
-// each writes its fp32 partial of Y to its own slab of the caller's workspace, and the last cluster to
-// finish a row block (a counter per CTA rank) adds the slabs in a fixed order and writes Y.
+// Work items.  An item is (batch entry, row block, hidden range).  Normally the range is the whole hidden
+// dimension and the launch is persistent: one cluster per place the device has, each walking its items with
+// rings, slots and barrier phases running on, so that the next item's GEMM1 and first hidden unit are under
+// way while the finished item's Y leaves tensor memory.  Row blocks may instead be shared by several clusters
+// (few row blocks, many SMs): each writes its fp32 partial of Y to its own slab of the caller's workspace, and
+// the last cluster to finish a row block (a counter per CTA rank) adds the slabs in a fixed order and writes
+// Y; such a launch has one item per cluster.
 #include <cuda.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstring>
 
@@ -96,8 +102,10 @@ constexpr int kUnits = DITTO_WIDE_UNITS;
 constexpr int kG1Stages = DITTO_WIDE_G1STAGES;
 constexpr int kW2Stages = DITTO_WIDE_W2STAGES;
 constexpr int kEpiWarps = 8;
-constexpr int kWarpProdG1a = 8, kWarpMmaG1 = 9, kWarpProdW2 = 10, kWarpFree = 11, kWarpProdG1b = 12, kWarpMmaG2 = 13;
-constexpr int kThreads = 14 * 32;
+constexpr int kWarpProdG1 = 8, kWarpMmaG1 = 9, kWarpProdW2 = 10, kWarpMmaG2 = 11;
+// Twelve warps: registers are handed out to warps in fours, so a thirteenth would cost every thread 40 of them
+// (65536 / (16 x 32) = 128 against 65536 / (12 x 32) -> 168), and the epilogue warps hold a 128 x 256 tile.
+constexpr int kThreads = 12 * 32;
 constexpr int kOffSlots = 0;
 constexpr int kOffG1Ring = kOffSlots + kUnits * kUnitBytes;
 constexpr int kOffW2Ring = kOffG1Ring + kG1Stages * kG1StageBytes;
@@ -114,6 +122,8 @@ struct WideParams {
   int* counters;       // shared row blocks: one per (batch, shared row block, CTA rank), zero at launch
   int M, N, K, L;
   int row_blocks;      // ceil(M / 128)
+  int batch;
+  int persistent;      // 1: no shared row blocks, a cluster walks several items (see the kernel)
   int whole_blocks;    // the first row blocks are computed by one cluster each ...
   int parts;           // ... the others by `parts` clusters, each taking a range of the hidden chunks
   int w_oi;            // 1: weights stored [out, in] (K-major B operands)
@@ -131,9 +141,9 @@ struct WideBars {
   uint64_t h_tmem_full;        // GEMM1 of the chunk is in tensor memory
   uint64_t h_tmem_empty;       // the epilogue warps hold the chunk in registers (8 warp arrivals)
   uint64_t h_ready[kUnits];    // the slot's unit is present (own: local arrive; a peer's: pushed bytes)
-  uint64_t g2_done[kUnits];    // this CTA's GEMM2 has finished reading the slot
-  uint64_t slot_free[kUnits];  // all four CTAs have (4 arrivals); kept at the CTA that writes the slot next
+  uint64_t slot_free[kUnits];  // all four CTAs' GEMM2 have finished reading the slot (4 multicast-commit arrivals at the CTA that writes it next)
   uint64_t y_done;             // the item's last MMA has retired
+  uint64_t y_free;             // the epilogue warps have read the item's Y out of tensor memory (8 warp arrivals)
   uint64_t epi_sync;           // all 256 epilogue threads, once per unit they write
   uint64_t y_sync;             // all 256 epilogue threads (shared row blocks only)
   uint32_t tmem_base;
@@ -151,7 +161,10 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
 
 }  // namespace
 
-template <bool BF16>
+// PLAIN: ReLU after GEMM1, nothing after GEMM2, no bias -- the chain as the reference defines it.  The general
+// form picks activation and bias at run time (one warp-uniform dispatch per accumulator piece); its six code
+// paths per call site cost registers the plain chain does not have to pay for.
+template <bool BF16, bool PLAIN>
 __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     mlp_wide_kernel(const __grid_constant__ WideParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -164,21 +177,44 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t q = cluster_ctarank();   // owns Y columns [q NS, (q+1) NS) and chunks q, q + 4, ... of the item
-  const int item = blockIdx.x / kCluster;
-  // items of a batch entry: the whole row blocks first, then the parts of the shared ones
-  const bool shared = item >= p.whole_blocks;
-  const int nparts = shared ? p.parts : 1;
-  const int rb = shared ? p.whole_blocks + (item - p.whole_blocks) / p.parts : item;   // 128-row block
-  const int sp = shared ? (item - p.whole_blocks) % p.parts : 0;                      // which part of the hidden dimension
-  const int b = blockIdx.y;
-  const int row0 = rb * kRows;
   const int NS = p.N / kCluster;          // this CTA's Y columns
   const int all_chunks = p.L / kChunk;
-  const int c0 = static_cast<int>(static_cast<long long>(sp) * all_chunks / nparts);
-  const int chunks = static_cast<int>(static_cast<long long>(sp + 1) * all_chunks / nparts) - c0;
-  const int units = 4 * chunks;           // 64-column units of the item, numbered in consumption order
-  const int my_rounds = static_cast<int>(q) < chunks ? (chunks - static_cast<int>(q) + kCluster - 1) / kCluster : 0;
   const int ksteps1 = (p.K + 63) / 64;
+  // Work items.  Without shared row blocks the launch is persistent: a cluster per place the device has
+  // (cudaOccupancyMaxActiveClusters), cluster c taking the (batch entry, row block) items c, c + clusters, ...
+  // Rings, slots, barrier phases and the unit numbering run on across items, so the next item's GEMM1 fills the
+  // tensor pipe while the last hidden units of the current item are still on their way and Y is written out.
+  // With shared row blocks every cluster has one item: grid.x numbers the items of a batch entry (whole row
+  // blocks first, then the parts of the shared ones), grid.y the batch entries.
+  const int cluster_id = blockIdx.x / kCluster;
+  const int n_clusters = gridDim.x / kCluster;
+  const int total_items = p.row_blocks * static_cast<int>(p.batch);
+  const int my_items = p.persistent ? (total_items - cluster_id + n_clusters - 1) / n_clusters : 1;
+  // What all items of a cluster have in common: which part of the hidden dimension they cover.
+  const bool shared = !p.persistent && cluster_id >= p.whole_blocks;
+  const int nparts = shared ? p.parts : 1;
+  const int rb_one = shared ? p.whole_blocks + (cluster_id - p.whole_blocks) / p.parts : cluster_id;   // 128-row block (one-item launch)
+  const int sp = shared ? (cluster_id - p.whole_blocks) % p.parts : 0;                                 // which part of the hidden dimension
+  const int c0 = sp * all_chunks / nparts;               // (parts <= 8, chunks in the thousands at most: 32 bits are plenty)
+  const int chunks = (sp + 1) * all_chunks / nparts - c0;
+  const int units = 4 * chunks;            // 64-column units of an item, numbered in consumption order
+  // this CTA owns chunks q, q + 4, ... of an item
+  const int my_rounds = static_cast<int>(q) < chunks ? (chunks - static_cast<int>(q) + kCluster - 1) / kCluster : 0;
+  struct Item {
+    int b, row0;                           // batch entry, first row of the block
+  };
+  auto decode = [&](int k) -> Item {       // the k-th item of this cluster
+    Item t;
+    if (p.persistent) {
+      const int id = cluster_id + k * n_clusters;
+      t.b = id / p.row_blocks;
+      t.row0 = (id - t.b * p.row_blocks) * kRows;
+    } else {
+      t.b = blockIdx.y;
+      t.row0 = rb_one * kRows;
+    }
+    return t;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kG1Stages; ++s) {
@@ -193,10 +229,10 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     mbar_init(&bar->h_tmem_empty, kEpiWarps);
     for (int x = 0; x < kUnits; ++x) {
       mbar_init(&bar->h_ready[x], 1);
-      mbar_init(&bar->g2_done[x], 1);
       mbar_init(&bar->slot_free[x], kCluster);
     }
     mbar_init(&bar->y_done, 1);
+    mbar_init(&bar->y_free, kEpiWarps);
     mbar_init(&bar->epi_sync, kEpiWarps * 32);
     mbar_init(&bar->y_sync, kEpiWarps * 32);
     bar->abort_word = 0;
@@ -219,38 +255,40 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   grid_dependency_wait();
   grid_launch_dependents();
 
-  if (warp == kWarpProdG1a || warp == kWarpProdG1b) {
-    // ------------------------------------------------------------ GEMM1 operand producers (one thread each)
-    // A stage holds one k-step of GEMM1: this block's 128 x 64 piece of X and the 64 x 256 tile of W1.  One
-    // thread gets a TMA box out every few hundred clocks, two boxes per 512 clocks of MMA work is more than
-    // one thread sustains: the two producers take alternate stages.
+  if (warp == kWarpProdG1) {
+    // ------------------------------------------------------------ GEMM1 operand producer (one thread)
+    // A stage holds one k-step of GEMM1: this block's 128 x 64 piece of X and the 64 x 256 tile of W1, a TMA
+    // box each (the atom view of [in, out] weights makes the W1 tile one box).  Operand delivery from L2 sets
+    // the pace (a stage per 1.3 k clocks); one thread gets two boxes out in about 600.
     if (lane == 0) {
-      const int pw = warp == kWarpProdG1a ? 0 : 1;
       tma_prefetch_desc(&p.map_x);
       tma_prefetch_desc(&p.map_w1);
-      int ps = 0, cnt = 0;
+      int ps = 0;
       uint32_t pph = 0;
       bool ok = true;
-      for (int i = 0; i < my_rounds && ok; ++i) {
-        const int hcol = (c0 + i * kCluster + static_cast<int>(q)) * kChunk;   // this CTA's chunk of round i
-        for (int ks = 0; ks < ksteps1 && ok; ++ks, ++cnt) {
-          if ((cnt & 1) == pw) {
-            ok = mbar_wait(&bar->g1empty[ps], pph ^ 1, abort_word, 0x100 + i);
-            if (!ok) break;
-            uint8_t* dst = smem + kOffG1Ring + ps * kG1StageBytes;
-            mbar_arrive_expect_tx(&bar->g1full[ps], kG1StageBytes);
-            tma_load_3d(dst, &p.map_x, &bar->g1full[ps], ks * 64, row0, b);
-            dst += kXTileBytes;
-            if (p.w_oi) {
-              tma_load_3d(dst, &p.map_w1, &bar->g1full[ps], ks * 64, hcol, b);
-            } else if (p.w_atoms) {
-              tma_load_4d(dst, &p.map_w1, &bar->g1full[ps], 0, ks * 64, hcol / 64, b);
-            } else {
-              for (int a = 0; a < kChunk / 64; ++a)
-                tma_load_3d(dst + a * 8192, &p.map_w1, &bar->g1full[ps], hcol + a * 64, ks * 64, b);
+      for (int k = 0; k < my_items && ok; ++k) {
+        const Item t = decode(k);
+        for (int i = 0; i < my_rounds && ok; ++i) {
+          const int hcol = (c0 + i * kCluster + static_cast<int>(q)) * kChunk;   // this CTA's chunk of round i
+          for (int ks = 0; ks < ksteps1 && ok; ++ks) {
+            {
+              ok = mbar_wait(&bar->g1empty[ps], pph ^ 1, abort_word, 0x100 + i);
+              if (!ok) break;
+              uint8_t* dst = smem + kOffG1Ring + ps * kG1StageBytes;
+              mbar_arrive_expect_tx(&bar->g1full[ps], kG1StageBytes);
+              tma_load_3d(dst, &p.map_x, &bar->g1full[ps], ks * 64, t.row0, t.b);
+              dst += kXTileBytes;
+              if (p.w_oi) {
+                tma_load_3d(dst, &p.map_w1, &bar->g1full[ps], ks * 64, hcol, t.b);
+              } else if (p.w_atoms) {
+                tma_load_4d(dst, &p.map_w1, &bar->g1full[ps], 0, ks * 64, hcol / 64, t.b);
+              } else {
+                for (int a = 0; a < kChunk / 64; ++a)
+                  tma_load_3d(dst + a * 8192, &p.map_w1, &bar->g1full[ps], hcol + a * 64, ks * 64, t.b);
+              }
             }
+            if (++ps == kG1Stages) { ps = 0; pph ^= 1; }
           }
-          if (++ps == kG1Stages) { ps = 0; pph ^= 1; }
         }
       }
     }
@@ -262,23 +300,28 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       int ps = 0;
       uint32_t pph = 0;
       const int ncol = static_cast<int>(q) * NS;
-      for (int n = 0; n < units; ++n) {
-        const int i = n / (4 * kCluster);
-        const int cr = min(kCluster, chunks - kCluster * i);
-        const int e = n - 4 * kCluster * i;
-        const int hrow = (c0 + i * kCluster + e % cr) * kChunk + (e / cr) * kUnitCols;
-        if (!mbar_wait(&bar->w2empty[ps], pph ^ 1, abort_word, 0x200 + i)) break;
-        uint8_t* dst = smem + kOffW2Ring + ps * kW2StageBytes;
-        mbar_arrive_expect_tx(&bar->w2full[ps], static_cast<uint32_t>(64 * NS * 2));
-        if (p.w_oi) {
-          tma_load_3d(dst, &p.map_w2, &bar->w2full[ps], hrow, ncol, b);
-        } else if (p.w_atoms) {
-          tma_load_4d(dst, &p.map_w2, &bar->w2full[ps], 0, hrow, ncol / 64, b);
-        } else {
-          for (int a = 0; a < NS / 64; ++a)
-            tma_load_3d(dst + a * 8192, &p.map_w2, &bar->w2full[ps], ncol + a * 64, hrow, b);
+      bool ok = true;
+      for (int k = 0; k < my_items && ok; ++k) {
+        const Item t = decode(k);
+        for (int n = 0; n < units; ++n) {
+          const int i = n / (4 * kCluster);
+          const int cr = min(kCluster, chunks - kCluster * i);
+          const int e = n - 4 * kCluster * i;
+          const int hrow = (c0 + i * kCluster + e % cr) * kChunk + (e / cr) * kUnitCols;
+          ok = mbar_wait(&bar->w2empty[ps], pph ^ 1, abort_word, 0x200 + i);
+          if (!ok) break;
+          uint8_t* dst = smem + kOffW2Ring + ps * kW2StageBytes;
+          mbar_arrive_expect_tx(&bar->w2full[ps], static_cast<uint32_t>(64 * NS * 2));
+          if (p.w_oi) {
+            tma_load_3d(dst, &p.map_w2, &bar->w2full[ps], hrow, ncol, t.b);
+          } else if (p.w_atoms) {
+            tma_load_4d(dst, &p.map_w2, &bar->w2full[ps], 0, hrow, ncol / 64, t.b);
+          } else {
+            for (int a = 0; a < NS / 64; ++a)
+              tma_load_3d(dst + a * 8192, &p.map_w2, &bar->w2full[ps], ncol + a * 64, hrow, t.b);
+          }
+          if (++ps == kW2Stages) { ps = 0; pph ^= 1; }
         }
-        if (++ps == kW2Stages) { ps = 0; pph ^= 1; }
       }
     }
   } else if (warp == kWarpMmaG1) {
@@ -301,26 +344,32 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       tc_fence_after_sync();
       return r;
     };
-    for (int i = 0; i < my_rounds && ok; ++i) {
-      // the accumulator is single: the previous chunk must be in the epilogue warps' registers
-      if (i > 0) DITTO_TIMED(w_acc, ok = wait(&bar->h_tmem_empty, (i - 1) & 1, 0x300 + i));
-      if (lane == 0) DITTO_STAMP(16 * i + 0);
-      for (int ks = 0; ks < ksteps1 && ok; ++ks) {
-        DITTO_TIMED(w_g1, ok = wait(&bar->g1full[cs], cph, 0x310 + i));
-        if (!ok) break;
-        const uint32_t sx = ring + cs * kG1StageBytes, sw = sx + kXTileBytes;
-        const uint64_t da = umma_desc_sw128(sx, 16, 1024);
-        const uint64_t db = p.w_oi ? umma_desc_sw128(sw, 16, 1024) : umma_desc_sw128(sw, 8192, 1024);
+    int gc = 0;                           // chunks this CTA has multiplied so far, over all items
+    for (int k = 0; k < my_items && ok; ++k) {
+      const Item t = decode(k);
+      const int tr = k < 6 ? 64 * k : 4096;   // timeline slot base (stamps past the buffer are dropped)
+      (void)tr;
+      for (int i = 0; i < my_rounds && ok; ++i, ++gc) {
+        // the accumulator is single: the previous chunk must be in the epilogue warps' registers
+        if (gc > 0) DITTO_TIMED(w_acc, ok = wait(&bar->h_tmem_empty, (gc - 1) & 1, 0x300 + i));
+        if (lane == 0) DITTO_STAMP(tr + 16 * i + 0);
+        for (int ks = 0; ks < ksteps1 && ok; ++ks) {
+          DITTO_TIMED(w_g1, ok = wait(&bar->g1full[cs], cph, 0x310 + i));
+          if (!ok) break;
+          const uint32_t sx = ring + cs * kG1StageBytes, sw = sx + kXTileBytes;
+          const uint64_t da = umma_desc_sw128(sx, 16, 1024);
+          const uint64_t db = p.w_oi ? umma_desc_sw128(sw, 16, 1024) : umma_desc_sw128(sw, 8192, 1024);
 #pragma unroll
-        for (int s4 = 0; s4 < 4; ++s4) {
-          const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
-          umma_ss_elected(tmem_h, da + ((s4 * 32) >> 4), db + offb, idesc1, (ks | s4) ? 1u : 0u, issuer);
+          for (int s4 = 0; s4 < 4; ++s4) {
+            const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
+            umma_ss_elected(tmem_h, da + ((s4 * 32) >> 4), db + offb, idesc1, (ks | s4) ? 1u : 0u, issuer);
+          }
+          umma_commit_elected(&bar->g1empty[cs], issuer);
+          if (++cs == kG1Stages) { cs = 0; cph ^= 1; }
         }
-        umma_commit_elected(&bar->g1empty[cs], issuer);
-        if (++cs == kG1Stages) { cs = 0; cph ^= 1; }
+        if (ok) umma_commit_elected(&bar->h_tmem_full, issuer);
+        if (lane == 0) DITTO_STAMP(tr + 16 * i + 1);
       }
-      if (ok) umma_commit_elected(&bar->h_tmem_full, issuer);
-      if (lane == 0) DITTO_STAMP(16 * i + 1);
     }
 #ifdef DITTO_TRACE
     if (lane == 0 && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
@@ -344,52 +393,56 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       tc_fence_after_sync();
       return r;
     };
-    for (int n = 0; n < units && ok; ++n) {
-      const int sl = n % kUnits;
-      const int i = n / (4 * kCluster);
-      const int cr = min(kCluster, chunks - kCluster * i);
-      const int src = (n - 4 * kCluster * i) % cr;
-      // a peer pushes this unit: arm the slot's barrier for its bytes (the own units arrive locally)
-      if (src != static_cast<int>(q) && lane == 0) mbar_arrive_expect_tx(&bar->h_ready[sl], kUnitBytes);
-      __syncwarp();
-      if (lane == 0 && (n & 15) == 0) DITTO_STAMP(16 * i + 2);
-      DITTO_TIMED(w_unit, ok = wait(&bar->h_ready[sl], (n / kUnits) & 1, 0x400 + i));
-      if (!ok) break;
-      if (lane == 0 && (n & 15) == 0) DITTO_STAMP(16 * i + 3);
-      DITTO_TIMED(w_g2, ok = wait(&bar->w2full[cs], cph, 0x410 + i));
-      if (!ok) break;
-      const uint32_t sw = ring + cs * kW2StageBytes;
-      const uint64_t da = umma_desc_sw128(slots + sl * kUnitBytes, 16, 1024);
-      const uint64_t db = p.w_oi ? umma_desc_sw128(sw, 16, 1024) : umma_desc_sw128(sw, 8192, 1024);
+    int gn = 0;                           // units consumed so far, over all items: slot gn % kUnits
+    const int all_units = units * my_items;
+    for (int k = 0; k < my_items && ok; ++k) {
+      const Item t = decode(k);
+      const int tr = k < 6 ? 64 * k : 4096;
+      (void)tr;
+      // the Y accumulator is single: the epilogue warps must have read the previous item's out
+      if (k > 0) DITTO_TIMED(w_unit, ok = wait(&bar->y_free, (k - 1) & 1, 0x420));
+      for (int n = 0; n < units && ok; ++n, ++gn) {
+        const int sl = gn % kUnits;
+        const int i = n / (4 * kCluster);
+        const int cr = min(kCluster, chunks - kCluster * i);
+        const int src = (n - 4 * kCluster * i) % cr;
+        // a peer pushes this unit: arm the slot's barrier for its bytes (the own units arrive locally)
+        if (src != static_cast<int>(q) && lane == 0) mbar_arrive_expect_tx(&bar->h_ready[sl], kUnitBytes);
+        __syncwarp();
+        if (lane == 0 && (n & 15) == 0) DITTO_STAMP(tr + 16 * i + 2);
+        DITTO_TIMED(w_unit, ok = wait(&bar->h_ready[sl], (gn / kUnits) & 1, 0x400 + i));
+        if (!ok) break;
+        if (lane == 0 && (n & 15) == 0) DITTO_STAMP(tr + 16 * i + 3);
+        DITTO_TIMED(w_g2, ok = wait(&bar->w2full[cs], cph, 0x410 + i));
+        if (!ok) break;
+        const uint32_t sw = ring + cs * kW2StageBytes;
+        const uint64_t da = umma_desc_sw128(slots + sl * kUnitBytes, 16, 1024);
+        const uint64_t db = p.w_oi ? umma_desc_sw128(sw, 16, 1024) : umma_desc_sw128(sw, 8192, 1024);
 #pragma unroll
-      for (int s4 = 0; s4 < 4; ++s4) {
-        const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
-        umma_ss_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (n | s4) ? 1u : 0u, issuer);
+        for (int s4 = 0; s4 < 4; ++s4) {
+          const uint32_t offb = p.w_oi ? (s4 * 32) >> 4 : (s4 * 2048) >> 4;
+          umma_ss_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (n | s4) ? 1u : 0u, issuer);
+        }
+        umma_commit_elected(&bar->w2empty[cs], issuer);
+        if (gn + kUnits < all_units) {
+          // The slot is free once all four CTAs have multiplied the unit: each one's MMA completion arrives
+          // directly on the barrier of the CTA that writes the slot next -- the owner of unit gn + kUnits, of
+          // this item or the next (all items of a cluster have the same number of units).
+          const int m = (n + kUnits) % units;
+          const int mi = m / (4 * kCluster);
+          const int mcr = min(kCluster, chunks - kCluster * mi);
+          umma_commit_mcast_elected(&bar->slot_free[sl], 1u << ((m - 4 * kCluster * mi) % mcr), issuer);
+        }
+        if (++cs == kW2Stages) { cs = 0; cph ^= 1; }
+        if (lane == 0 && (n & 15) == 15) DITTO_STAMP(tr + 16 * i + 4);
       }
-      umma_commit_elected(&bar->w2empty[cs], issuer);
-      umma_commit_elected(&bar->g2_done[sl], issuer);
-      if (++cs == kW2Stages) { cs = 0; cph ^= 1; }
-      if (lane == 0 && (n & 15) == 15) DITTO_STAMP(16 * i + 4);
+      if (ok) umma_commit_elected(&bar->y_done, issuer);
     }
-    if (ok) umma_commit_elected(&bar->y_done, issuer);
 #ifdef DITTO_TRACE
     if (lane == 0 && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
       p.trace[402] = w_unit; p.trace[403] = w_g2; p.trace[405] = clock64();
     }
 #endif
-  } else if (warp == kWarpFree) {
-    // ------------------------------------------------------------ free relay (one thread)
-    if (lane == 0) {
-      for (int n = 0; n + kUnits < units; ++n) {
-        const int sl = n % kUnits;
-        if (!mbar_wait(&bar->g2_done[sl], (n / kUnits) & 1, abort_word, 0x580 + n / (4 * kCluster))) break;
-        // tell the CTA that writes the slot next: the owner of unit n + kUnits
-        const int m = n + kUnits;
-        const int i = m / (4 * kCluster);
-        const int cr = min(kCluster, chunks - kCluster * i);
-        mbar_arrive_cluster(&bar->slot_free[sl], static_cast<uint32_t>((m - 4 * kCluster * i) % cr));
-      }
-    }
   } else if (warp < kEpiWarps) {
     // ------------------------------------------------------------ epilogue: eight warps
     // Warp w: rows 32 (w % 4) ... + 31 (its TMEM lanes), column half w / 4 of every 64-column quarter.  All
@@ -400,102 +453,55 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     const int row = (warp & 3) * 32 + lane;              // row of the block = TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     bool ok = true;
-    uint32_t free_waits[kUnits] = {};     // completed waits per slot: the parity of the next one
+    uint32_t free_par = 0;                // bit s: parity of the next wait for slot s to be free
     uint32_t sync_uses = 0;               // completed phases of epi_sync
-    for (int i = 0; i < my_rounds; ++i) {
-      const int cr = min(kCluster, chunks - kCluster * i);
-      const int hcol0 = (c0 + i * kCluster + static_cast<int>(q)) * kChunk;   // first hidden column of the chunk
-      ok = mbar_wait(&bar->h_tmem_full, i & 1, abort_word, 0x600 + i);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+    int gc = 0;                           // chunks drained so far, over all items
+    int ubase = 0;                        // units of the items before this one
+    const int colg = grp * (NS / 2);      // this warp group's share of the CTA's NS accumulator columns
+    const size_t ycol0 = static_cast<size_t>(q) * NS + colg;
+
+    // Y of item t leaves tensor memory.  With `release` the accumulator is handed back to the GEMM2 warp as soon
+    // as it is in registers (NS / 2 <= 128 columns per thread, rounded: 64 registers), before the stores.
+    auto drain_y = [&](const Item& t, int k, bool release) __attribute__((always_inline)) -> bool {
+      bool good = mbar_wait(&bar->y_done, k & 1, abort_word, 0x800);
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
       tc_fence_after_sync();
-      if (threadIdx.x == 0) DITTO_STAMP(16 * i + 6);
-      // the whole chunk leaves tensor memory first, so that the accumulator is released without waiting
-      // for a free slot (the next GEMM1 is ahead of this chunk's GEMM2 in the tensor-pipe order)
-      uint32_t pk[4][16];
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const int col = kk * kUnitCols + grp * 32;
-        const uint32_t* bias1 = p.b1 == nullptr ? nullptr
-                                                : reinterpret_cast<const uint32_t*>(p.b1) +
-                                                      (static_cast<size_t>(b) * p.L + hcol0 + col) / 2;
-        uint32_t h[32];
-        tmem_ld_x32_wait(tmem_h + lane_base + col, h);
-        act_pack<BF16>(h, bias1, p.act1, pk[kk]);
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar->h_tmem_empty);   // one arrival per warp
-      if (threadIdx.x == 0) DITTO_STAMP(16 * i + 7);
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const int n = 4 * kCluster * i + cr * kk + static_cast<int>(q);
-        const int sl = n % kUnits;
-        if (n >= kUnits) {
-          // every CTA has finished GEMM2 on the slot's previous unit: it may be overwritten
-          uint32_t par = 0;
-#pragma unroll
-          for (int t = 0; t < kUnits; ++t)
-            if (t == sl) par = free_waits[t]++ & 1;
-          ok = mbar_wait_cluster(&bar->slot_free[sl], par, abort_word, 0x700 + i);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-        }
-        uint8_t* slot = smem + kOffSlots + sl * kUnitBytes;
-#pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-          const int ch = grp * 4 + c4;      // 16-byte piece of the 128-byte row
-          const uint32_t* w = &pk[kk][4 * c4];
-          *reinterpret_cast<uint4*>(slot + row * 128 + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(&bar->epi_sync);
-        ok = mbar_wait(&bar->epi_sync, sync_uses++ & 1, abort_word, 0x780 + i);   // all 256 threads have written
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (threadIdx.x == 0) {
-          const uint32_t slot_addr = smem_u32(slot);
-          const uint32_t bar_addr = smem_u32(&bar->h_ready[sl]);
-          for (uint32_t d = 1; d < kCluster; ++d) {
-            const uint32_t peer = (q + d) % kCluster;     // every CTA of the cluster consumes the unit
-            bulk_copy_to_peer(map_to_cta(slot_addr, peer), slot, kUnitBytes, map_to_cta(bar_addr, peer));
-          }
-          mbar_arrive(&bar->h_ready[sl]);    // the local copy is in place
-          DITTO_STAMP(16 * i + 8 + kk);
-        }
-      }
-      if (!ok) break;
-    }
-    if (ok) {
-      ok = mbar_wait(&bar->y_done, 0, abort_word, 0x800);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
-      tc_fence_after_sync();
-      if (threadIdx.x == 0) DITTO_STAMP(500);
-      const int colg = grp * (NS / 2);      // this warp group's share of the CTA's NS accumulator columns
-      const size_t ycol0 = static_cast<size_t>(q) * NS + colg;
+      if (threadIdx.x == 0) DITTO_STAMP(k < 6 ? 500 + 2 * k : 4096);
       if (!shared) {
-        uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(b) * p.M + row0 + row) * p.N + ycol0) * 2;
+        uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(t.b) * p.M + t.row0 + row) * p.N + ycol0) * 2;
         const uint32_t* bias2 = p.b2 == nullptr ? nullptr
-                                                : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(b) * p.N + ycol0) / 2;
-        for (int cc = 0; cc < NS / 2; cc += 32) {
-          uint32_t o[32];
-          tmem_ld_x32_wait(tmem_y + lane_base + colg + cc, o);
-          uint32_t w[16];
-          act_pack<BF16>(o, bias2 == nullptr ? nullptr : bias2 + cc / 2, p.act2, w);
-          if (row0 + row < p.M) {             // rows >= M of a partial last block were computed on zero-filled X
+                                                : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(t.b) * p.N + ycol0) / 2;
+        uint32_t w[8][8];                       // 16 columns a piece: short live ranges next to the 64 result registers
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              *reinterpret_cast<uint4*>(yrow + cc * 2 + j * 16) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        for (int c = 0; c < 8; ++c) {
+          if (c * 16 < NS / 2) {
+            uint32_t o[16];
+            tmem_ld_x16_wait(tmem_y + lane_base + colg + c * 16, o);
+            if constexpr (PLAIN) act_pack_fixed<BF16, 0, false>(o, nullptr, w[c]);
+            else act_pack<BF16>(o, bias2 == nullptr ? nullptr : bias2 + c * 8, p.act2, w[c]);
+          }
+        }
+        if (release) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar->y_free);
+        }
+        if (t.row0 + row < p.M) {               // rows >= M of a partial last block were computed on zero-filled X
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            if (c * 16 < NS / 2) {
+              *reinterpret_cast<uint4*>(yrow + c * 32) = make_uint4(w[c][0], w[c][1], w[c][2], w[c][3]);
+              *reinterpret_cast<uint4*>(yrow + c * 32 + 16) = make_uint4(w[c][4], w[c][5], w[c][6], w[c][7]);
+            }
           }
         }
       } else {
         // this cluster's fp32 partial goes to its slab; bias and activation are applied when the slabs are added
         const size_t mpad = static_cast<size_t>(p.row_blocks - p.whole_blocks) * kRows;   // rows of the shared blocks
         const size_t slab = static_cast<size_t>(gridDim.y) * mpad * p.N;
-        const int srow0 = row0 - p.whole_blocks * kRows;
-        float* prow = p.slabs + static_cast<size_t>(sp) * slab + (static_cast<size_t>(b) * mpad + srow0 + row) * p.N + ycol0;
+        const int srow0 = t.row0 - p.whole_blocks * kRows;
+        float* prow = p.slabs + static_cast<size_t>(sp) * slab + (static_cast<size_t>(t.b) * mpad + srow0 + row) * p.N + ycol0;
         for (int cc = 0; cc < NS / 2; cc += 32) {
           uint32_t o[32];
           tmem_ld_x32_wait(tmem_y + lane_base + colg + cc, o);
@@ -505,18 +511,134 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         }
         __threadfence();
         mbar_arrive(&bar->y_sync);
-        ok = mbar_wait(&bar->y_sync, 0, abort_word, 0x810);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok && threadIdx.x == 0) {
-          int* ctr = p.counters + (static_cast<size_t>(b) * (p.row_blocks - p.whole_blocks) + (rb - p.whole_blocks)) * kCluster + q;
+        good = mbar_wait(&bar->y_sync, 0, abort_word, 0x810);
+        good = __all_sync(0xffffffffu, good);
+        if (good && threadIdx.x == 0) {
+          int* ctr = p.counters + (static_cast<size_t>(t.b) * (p.row_blocks - p.whole_blocks) + (rb_one - p.whole_blocks)) * kCluster + q;
           const int seen = atomicAdd(ctr, 1);
           __threadfence();
           bar->last_flag = (seen == p.parts - 1) ? 1u : 0u;
         }
-        // (the combining pass runs below, on all threads of the CTA, once the other warps are done too)
+        // (the combining pass runs after the roles, on all threads of the CTA)
       }
-      if (threadIdx.x == 0) DITTO_STAMP(501);
+      if (threadIdx.x == 0) DITTO_STAMP(k < 6 ? 501 + 2 * k : 4096);
+      return good;
+    };
+
+    // Order at an item boundary: the first unit of the next item's first chunk is pushed BEFORE the finished
+    // item's Y is read out.  That unit only needs a slot the finished item's last GEMM2 steps release, and with
+    // it (and Y handed back right after) the GEMM2 warp goes on almost without a gap; the Y stores and the rest
+    // of the chunk's hand-over run behind it.
+    int pending = -1;                     // item whose Y is still in tensor memory
+    for (int k = 0; k < my_items && ok; ++k) {
+      const Item t = decode(k);
+      const int tr = k < 6 ? 64 * k : 4096;
+      (void)tr;
+      for (int i = 0; i < my_rounds; ++i, ++gc) {
+        const int cr = min(kCluster, chunks - kCluster * i);
+        const int hcol0 = (c0 + i * kCluster + static_cast<int>(q)) * kChunk;   // first hidden column of the chunk
+        const uint32_t* bias1 = p.b1 == nullptr ? nullptr
+                                                : reinterpret_cast<const uint32_t*>(p.b1) +
+                                                      (static_cast<size_t>(t.b) * p.L + hcol0 + grp * 32) / 2;
+        // quarter kk of the chunk: tensor memory -> bias, activation, rounding -> registers
+        auto load_quarter = [&](int kk, uint32_t (&v)[16]) __attribute__((always_inline)) {
+          uint32_t h[32];
+          tmem_ld_x32_wait(tmem_h + lane_base + kk * kUnitCols + grp * 32, h);
+          if constexpr (PLAIN) act_pack_fixed<BF16, 1, false>(h, nullptr, v);
+          else act_pack<BF16>(h, bias1 == nullptr ? nullptr : bias1 + kk * (kUnitCols / 2), p.act1, v);
+        };
+        auto release_h = [&]() __attribute__((always_inline)) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar->h_tmem_empty);   // one arrival per warp
+          if (threadIdx.x == 0) DITTO_STAMP(tr + 16 * i + 7);
+        };
+        // quarter kk becomes a unit: into its slot once that is free, then to the three peers
+        auto emit = [&](int kk, const uint32_t (&v)[16]) __attribute__((always_inline)) -> bool {
+          const int gn = ubase + 4 * kCluster * i + cr * kk + static_cast<int>(q);
+          const int sl = gn % kUnits;
+          bool good = true;
+          if (gn >= kUnits) {
+            // every CTA has finished GEMM2 on the slot's previous unit: it may be overwritten
+            const uint32_t par = (free_par >> sl) & 1u;
+            free_par ^= 1u << sl;
+            good = mbar_wait_cluster(&bar->slot_free[sl], par, abort_word, 0x700 + i);
+            good = __all_sync(0xffffffffu, good);
+            if (!good) return false;
+          }
+          uint8_t* slot = smem + kOffSlots + sl * kUnitBytes;
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const int ch = grp * 4 + c4;      // 16-byte piece of the 128-byte row
+            *reinterpret_cast<uint4*>(slot + row * 128 + ((ch ^ (row & 7)) << 4)) =
+                make_uint4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+          }
+          fence_proxy_async_smem();
+          mbar_arrive(&bar->epi_sync);
+          good = mbar_wait(&bar->epi_sync, sync_uses++ & 1, abort_word, 0x780 + i);   // all 256 threads have written
+          good = __all_sync(0xffffffffu, good);
+          if (!good) return false;
+          if (threadIdx.x == 0) {
+            const uint32_t slot_addr = smem_u32(slot);
+            const uint32_t bar_addr = smem_u32(&bar->h_ready[sl]);
+            for (uint32_t d = 1; d < kCluster; ++d) {
+              const uint32_t peer = (q + d) % kCluster;     // every CTA of the cluster consumes the unit
+              bulk_copy_to_peer(map_to_cta(slot_addr, peer), slot, kUnitBytes, map_to_cta(bar_addr, peer));
+            }
+            mbar_arrive(&bar->h_ready[sl]);    // the local copy is in place
+            DITTO_STAMP(tr + 16 * i + 8 + kk);
+          }
+          return true;
+        };
+
+        ok = mbar_wait(&bar->h_tmem_full, gc & 1, abort_word, 0x600 + i);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (threadIdx.x == 0) DITTO_STAMP(tr + 16 * i + 6);
+        if (pending < 0) {
+          // the whole chunk leaves tensor memory first, so that the accumulator is released without waiting
+          // for a free slot (the next GEMM1 is ahead of this chunk's GEMM2 in the tensor-pipe order)
+          uint32_t pk[4][16];
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) load_quarter(kk, pk[kk]);
+          release_h();
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            ok = emit(kk, pk[kk]);
+            if (!ok) break;
+          }
+        } else {
+          // item boundary: first quarter, the finished item's Y, then the other three quarters
+          {
+            uint32_t p0[16];
+            load_quarter(0, p0);
+            ok = emit(0, p0);
+          }
+          if (ok) ok = drain_y(decode(pending), pending, true);
+          if (!ok) break;
+          pending = -1;
+          uint32_t pk[3][16];
+#pragma unroll
+          for (int kk = 1; kk < 4; ++kk) load_quarter(kk, pk[kk - 1]);
+          release_h();
+#pragma unroll
+          for (int kk = 1; kk < 4; ++kk) {
+            ok = emit(kk, pk[kk - 1]);
+            if (!ok) break;
+          }
+        }
+        if (!ok) break;
+      }
+      if (!ok) break;
+      ubase += units;
+      if (pending >= 0) {                 // a CTA without a chunk in this item (fewer chunks than CTAs)
+        ok = drain_y(decode(pending), pending, true);
+        if (!ok) break;
+      }
+      pending = k;
     }
+    if (ok && pending >= 0) drain_y(decode(pending), pending, false);
   }
 
   // After a wait has given up, copies this CTA issued (TMA loads into its rings, pushes into its peers'
@@ -527,6 +649,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   }
   tc_fence_before_sync();
   __syncthreads();
+  const Item t0 = decode(0);              // with shared row blocks a cluster has this one item
   if (shared && bar->last_flag != 0u && bar->abort_word == 0u) {
     // Every part of this CTA's (rows, columns) region of a shared row block is in its slab, and this
     // cluster was the last to get there: add the slabs in slab order, apply bias and activation, write Y.
@@ -536,10 +659,10 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     const size_t slab = static_cast<size_t>(gridDim.y) * mpad * p.N;
     const size_t col0 = static_cast<size_t>(q) * NS;
     const uint32_t* bias2 = p.b2 == nullptr ? nullptr
-                                            : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(b) * p.N + col0) / 2;
-    combine_slabs<BF16>(p.slabs + (static_cast<size_t>(b) * mpad + (row0 - p.whole_blocks * kRows)) * p.N + col0, slab, p.parts,
-                        min(kRows, p.M - row0), NS, static_cast<size_t>(p.N), bias2, p.act2,
-                        reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(b) * p.M + row0) * p.N + col0) * 2,
+                                            : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(t0.b) * p.N + col0) / 2;
+    combine_slabs<BF16>(p.slabs + (static_cast<size_t>(t0.b) * mpad + (t0.row0 - p.whole_blocks * kRows)) * p.N + col0, slab, p.parts,
+                        min(kRows, p.M - t0.row0), NS, static_cast<size_t>(p.N), bias2, p.act2,
+                        reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(t0.b) * p.M + t0.row0) * p.N + col0) * 2,
                         static_cast<size_t>(p.N) * 2, static_cast<int>(threadIdx.x), kThreads);
   }
   cluster_sync_all();                     // no CTA leaves while a peer may still write to it
@@ -566,8 +689,10 @@ cudaError_t wide_configure(int* slots_out) {
   cudaError_t e = current_device_checked(&dev);
   if (e != cudaSuccess) return e;
   if (!device_configured(configured, dev)) {
-    auto kern = mlp_wide_kernel<BF16>;
+    auto kern = mlp_wide_kernel<BF16, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(mlp_wide_kernel<BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
     // how many clusters of four the device holds at once: the unit row-block sharing is sized against
     cudaLaunchConfig_t cfg = {};
@@ -660,6 +785,8 @@ int launch_mlp_wide(const void* x, const void* w1, const void* w2, void* y, int 
   p.K = K;
   p.L = L;
   p.row_blocks = rbs;
+  p.batch = batch;
+  p.persistent = split ? 0 : 1;
   p.whole_blocks = split ? plan.whole_blocks : rbs;
   p.parts = split ? plan.parts : 1;
   p.w_oi = w_layout == 1;
@@ -678,7 +805,13 @@ int launch_mlp_wide(const void* x, const void* w1, const void* w2, void* y, int 
     if (e != cudaSuccess) return cuda_fail("mlp wide counters", e);
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(kCluster * (p.whole_blocks + (rbs - p.whole_blocks) * p.parts)), static_cast<unsigned>(batch), 1);
+  if (p.persistent) {
+    // one cluster per place the device has (fewer when there are fewer items); each walks its items
+    const long long items = static_cast<long long>(rbs) * batch;
+    cfg.gridDim = dim3(static_cast<unsigned>(kCluster * std::min<long long>(items, slots)), 1, 1);
+  } else {
+    cfg.gridDim = dim3(static_cast<unsigned>(kCluster * (p.whole_blocks + (rbs - p.whole_blocks) * p.parts)), static_cast<unsigned>(batch), 1);
+  }
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
@@ -687,7 +820,9 @@ int launch_mlp_wide(const void* x, const void* w1, const void* w2, void* y, int 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = split ? 0 : 1;           // a launch with shared row blocks follows its own counter reset: plain stream order
-  cudaError_t e = bf16 ? cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true>, p) : cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false>, p);
+  const bool plain = act1 == 1 && act2 == 0 && b1 == nullptr && b2 == nullptr;
+  cudaError_t e = plain ? (bf16 ? cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, true>, p) : cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, true>, p))
+                        : (bf16 ? cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, false>, p) : cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, false>, p));
   return e == cudaSuccess ? DITTO_OK : cuda_fail("mlp wide kernel launch", e);
 }
 

@@ -213,6 +213,18 @@ __device__ __forceinline__ void umma_commit_elected(uint64_t* bar, uint32_t issu
       : "memory");
 }
 
+// The same, arriving (once) on the barrier at this offset in every CTA of the cluster named by `cta_mask`
+// (bit r = cluster rank r): a consumer's MMA completion releases a buffer in the producer's CTA directly.
+__device__ __forceinline__ void umma_commit_mcast_elected(uint64_t* bar, uint32_t cta_mask, uint32_t issuer) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t.reg .b16 lo, hi;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "mov.b32 {lo, hi}, %1;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], lo;\n\t}"
+      ::"r"(smem_u32(bar)), "r"(cta_mask), "r"(issuer)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- CTA pairs (cta_group::2)
 // Two CTAs with consecutive cluster ranks (even = leader) execute one MMA of M = 256: each holds
 // its 128 rows of A and half of B's N extent in its own shared memory (same offsets in both) and
