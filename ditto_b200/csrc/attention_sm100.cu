@@ -61,7 +61,13 @@ namespace {
 
 constexpr int kBM = 128;   // query rows per tile
 constexpr int kBN = 128;   // K/V rows per block
-constexpr int threads_for(int nt) { return 32 * (4 * nt + 2); }
+// 1: the two-tile kernel runs with twelve warps (two of them idle) so that its third warp group can hand
+// registers to the two softmax warp groups (setmaxnreg: 136 / 184 instead of 168 each; ptxas refuses a larger step with "register allocation failed" under this launch bound).  Measured: no gain
+// (the softmax warps spill 20 bytes at 168 registers and are not bound by per-thread work), so it is off.
+#ifndef DITTO_ATTN_SETMAXNREG
+#define DITTO_ATTN_SETMAXNREG 0
+#endif
+constexpr int threads_for(int nt) { return (DITTO_ATTN_SETMAXNREG && nt == 2) ? 384 : 32 * (4 * nt + 2); }
 constexpr int kModeSoftmax = 0, kModeRelu = 1, kModeIdentity = 2;
 constexpr int kSplit = 96;  // K/V rows in the first part of P (the rest follows separately)
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; P stays <= 2^8 with a stale max
@@ -177,6 +183,12 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
   grid_dependency_wait();
   grid_launch_dependents();
   if (warp == 0) DITTO_STAMP(512, 0, 8);
+#if DITTO_ATTN_SETMAXNREG
+  if constexpr (NT == 2) {
+    if (warp < 8) asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+    else asm volatile("setmaxnreg.dec.sync.aligned.u32 136;");
+  }
+#endif
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer (one thread)
