@@ -111,6 +111,40 @@ def test_shared_row_blocks(cuda, oracle, layout, variant):
     assert split_cases >= 2, "the planner shared row blocks in fewer cases than expected"
 
 
+@pytest.mark.parametrize("layout", ["IO", "OI"])
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_work_loop_many_items(cuda, oracle, dtype, layout):
+    """More (batch entry, row block) items than the device holds clusters at once (33 of four CTAs on a B200):
+    a cluster walks several items with its rings, slots and barrier phases running on.  Shapes: two hidden
+    chunks (two of the four CTAs own none and only write Y), a single chunk, six chunks (partial second
+    round) with partial last row blocks in three batch entries and a K that is not a multiple of 64, and
+    whole rounds.  Also the general (bias / GELU) form of the loop."""
+    lib = _lib.load()
+    slots = lib.ditto_b200_mlp_cluster_slots(_lib.DTYPE_BF16, _lib.EPILOGUE_WIDE_MMA)
+    assert slots > 0
+    for (batch, M, N, K, L) in ((1, 128 * 70, 256, 64, 512), (1, 128 * 40, 768, 128, 256),
+                                (3, 128 * 23 + 16, 512, 80, 1536), (2, 4480, 1024, 64, 1024)):
+        assert batch * ((M + 127) // 128) > slots, "the shape no longer needs the work loop on this device"
+        x, w1, w2 = _inputs(29, batch, M, N, K, L, dtype)
+        got = _run(cuda, x, w1, w2, dtype, "relu", layout, "wide", workspace=None)
+        want = oracle.gemm_act_gemm(x, w1, w2, 1, ODT[dtype], wide=False)
+        assert_close(got, want, dtype, f"work loop {dtype} {layout} {(batch, M, N, K, L)}")
+        again = _run(cuda, x, w1, w2, dtype, "relu", layout, "wide", workspace=None)
+        assert np.array_equal(got, again), "runs of the work loop differ"
+    M, N, K, L = 128 * 40, 256, 64, 768
+    x, w1, w2 = _inputs(31, 1, M, N, K, L, dtype)
+    rng = np.random.default_rng(32)
+    b1 = W._round(rng.standard_normal((1, L)).astype(np.float32) * 0.5, dtype)
+    b2 = W._round(rng.standard_normal((1, N)).astype(np.float32) * 0.5, dtype)
+    d1, d2 = ((_dev(w1.transpose(0, 2, 1), dtype, cuda), _dev(w2.transpose(0, 2, 1), dtype, cuda)) if layout == "OI"
+              else (_dev(w1, dtype, cuda), _dev(w2, dtype, cuda)))
+    out = torch.full((1, M, N), float("nan"), dtype=TDT[dtype], device=cuda)
+    ops.ffn(_dev(x, dtype, cuda), d1, _dev(b1, dtype, cuda), d2, _dev(b2, dtype, cuda), out=out, act1="gelu", act2="relu",
+            weight_layout=layout)
+    assert ops.device_status(cuda) == 0
+    assert_close(out.float().cpu().numpy(), oracle.ffn(x, w1, b1, w2, b2, 2, 1, ODT[dtype]), dtype, f"work loop ffn {dtype} {layout}")
+
+
 def test_golden_vector(cuda):
     case = "mlp_bf16_relu"
     w = make_golden.workload(case)
