@@ -122,6 +122,8 @@ struct WideParams {
   int* counters;       // shared row blocks: one per (batch, shared row block, CTA rank), zero at launch
   int M, N, K, L;
   int row_blocks;      // ceil(M / 128)
+  int n0;              // first Y column of this launch's column group (a launch covers N <= 1024 columns of ldn)
+  int ldn;             // columns of Y, W2 and b2 in memory
   int batch;
   int persistent;      // 1: no shared row blocks, a cluster walks several items (see the kernel)
   int whole_blocks;    // the first row blocks are computed by one cluster each ...
@@ -299,7 +301,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       tma_prefetch_desc(&p.map_w2);
       int ps = 0;
       uint32_t pph = 0;
-      const int ncol = static_cast<int>(q) * NS;
+      const int ncol = p.n0 + static_cast<int>(q) * NS;   // W2 / Y column in memory
       bool ok = true;
       for (int k = 0; k < my_items && ok; ++k) {
         const Item t = decode(k);
@@ -469,9 +471,9 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       tc_fence_after_sync();
       if (threadIdx.x == 0) DITTO_STAMP(k < 6 ? 500 + 2 * k : 4096);
       if (!shared) {
-        uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(t.b) * p.M + t.row0 + row) * p.N + ycol0) * 2;
+        uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(t.b) * p.M + t.row0 + row) * p.ldn + p.n0 + ycol0) * 2;
         const uint32_t* bias2 = p.b2 == nullptr ? nullptr
-                                                : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(t.b) * p.N + ycol0) / 2;
+                                                : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(t.b) * p.ldn + p.n0 + ycol0) / 2;
         uint32_t w[8][8];                       // 16 columns a piece: short live ranges next to the 64 result registers
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
@@ -659,11 +661,11 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     const size_t slab = static_cast<size_t>(gridDim.y) * mpad * p.N;
     const size_t col0 = static_cast<size_t>(q) * NS;
     const uint32_t* bias2 = p.b2 == nullptr ? nullptr
-                                            : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(t0.b) * p.N + col0) / 2;
+                                            : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(t0.b) * p.ldn + p.n0 + col0) / 2;
     combine_slabs<BF16>(p.slabs + (static_cast<size_t>(t0.b) * mpad + (t0.row0 - p.whole_blocks * kRows)) * p.N + col0, slab, p.parts,
                         min(kRows, p.M - t0.row0), NS, static_cast<size_t>(p.N), bias2, p.act2,
-                        reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(t0.b) * p.M + t0.row0) * p.N + col0) * 2,
-                        static_cast<size_t>(p.N) * 2, static_cast<int>(threadIdx.x), kThreads);
+                        reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(t0.b) * p.M + t0.row0) * p.ldn + p.n0 + col0) * 2,
+                        static_cast<size_t>(p.ldn) * 2, static_cast<int>(threadIdx.x), kThreads);
   }
   cluster_sync_all();                     // no CTA leaves while a peer may still write to it
   if (warp == 0) {
@@ -674,9 +676,23 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
 
 // ------------------------------------------------------------------ host side
 bool mlp_wide_supported(int N, int K, int L) {
-  // 256-wide hidden chunks; N/4 Y columns per CTA in whole 64-column groups, at most 256; K in 16-wide steps
-  // (a last partial 64-wide k-step is zero-filled by TMA)
-  return L % kChunk == 0 && K % 16 == 0 && N % (kCluster * 64) == 0 && N <= kCluster * 256;
+  // 256-wide hidden chunks; K in 16-wide steps (a last partial 64-wide k-step is zero-filled by TMA); a launch
+  // covers up to 1024 Y columns -- N/4 per CTA in whole 64-column groups, at most 256 -- and wider results are
+  // computed as several launches over column groups (see mlp_wide_column_groups)
+  return L % kChunk == 0 && K % 16 == 0 && N % (kCluster * 64) == 0;
+}
+
+static int mlp_wide_column_groups(int N, int* first, int* width) {
+  // N = 256 u columns in g = ceil(u / 4) groups of near-equal width (multiples of 256, at most 1024)
+  const int u = N / 256, g = (u + 3) / 4;
+  int c = 0;
+  for (int i = 0; i < g; ++i) {
+    const int w = (u / g + (i < u % g ? 1 : 0)) * 256;
+    first[i] = c;
+    width[i] = w;
+    c += w;
+  }
+  return g;
 }
 
 namespace {
@@ -724,13 +740,18 @@ RowBlockPlan mlp_wide_plan(int batch, int M, int L, int cluster_slots, bool allo
 }
 
 size_t mlp_wide_workspace_bytes(int batch, int M, int N, const RowBlockPlan& plan) {
-  return plan_workspace_bytes(plan, batch, (M + kRows - 1) / kRows, kRows, N, kCluster);
+  int first[16], width[16];
+  const int widest = (N % 256 == 0 && N <= 16 * kCluster * 256 && mlp_wide_column_groups(N, first, width) > 0) ? width[0] : N;
+  return plan_workspace_bytes(plan, batch, (M + kRows - 1) / kRows, kRows, widest, kCluster);
 }
 
-int launch_mlp_wide(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
-                    bool bf16, int w_layout, int act1, int act2, const void* b1, const void* b2, const RowBlockPlan& plan,
-                    void* workspace, int* status, cudaStream_t stream, long long* trace) {
-  if (!mlp_wide_supported(N, K, L) || batch > 65535) return DITTO_ERR_UNSUPPORTED;
+namespace {
+
+// One launch: the Y columns [n0, n0 + N) of a result that has ldn columns in memory (N <= 1024).
+int launch_wide_group(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
+                      int n0, int ldn, bool bf16, int w_layout, int act1, int act2, const void* b1, const void* b2,
+                      const RowBlockPlan& plan, void* workspace, int* status, cudaStream_t stream, long long* trace) {
+  if (!mlp_wide_supported(N, K, L) || N > kCluster * 256 || batch > 65535) return DITTO_ERR_UNSUPPORTED;
   int slots = 0;
   int rc = mlp_wide_cluster_slots(bf16, &slots);
   if (rc) return rc;
@@ -742,7 +763,7 @@ int launch_mlp_wide(const void* x, const void* w1, const void* w2, void* y, int 
   const bool split = shared_blocks > 0 && plan.parts > 1;
   WideParams p;
   std::memset(&p, 0, sizeof(p));
-  const uint64_t uM = M, uN = N, uK = K, uL = L, ub = batch;
+  const uint64_t uM = M, uN = ldn, uK = K, uL = L, ub = batch;   // uN: W2's extent along N in memory
   {
     const uint64_t dims[3] = {uK, uM, ub}, strides[2] = {uK * 2, uM * uK * 2};
     const uint32_t box[3] = {64, kRows, 1};
@@ -782,6 +803,8 @@ int launch_mlp_wide(const void* x, const void* w1, const void* w2, void* y, int 
   p.y = y;
   p.M = M;
   p.N = N;
+  p.n0 = n0;
+  p.ldn = ldn;
   p.K = K;
   p.L = L;
   p.row_blocks = rbs;
@@ -824,6 +847,26 @@ int launch_mlp_wide(const void* x, const void* w1, const void* w2, void* y, int 
   cudaError_t e = plain ? (bf16 ? cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, true>, p) : cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, true>, p))
                         : (bf16 ? cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, false>, p) : cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, false>, p));
   return e == cudaSuccess ? DITTO_OK : cuda_fail("mlp wide kernel launch", e);
+}
+
+}  // namespace
+
+int launch_mlp_wide(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N, int K, int L,
+                    bool bf16, int w_layout, int act1, int act2, const void* b1, const void* b2, const RowBlockPlan& plan,
+                    void* workspace, int* status, cudaStream_t stream, long long* trace) {
+  if (!mlp_wide_supported(N, K, L) || N > 16 * kCluster * 256) return DITTO_ERR_UNSUPPORTED;
+  // Results wider than 1024 columns do not fit the cluster's tensor memory next to a hidden chunk: they are
+  // computed group of columns by group, one launch each, in stream order (the scratch memory of a plan with
+  // shared row blocks is sized for the widest group and reused).  Every group recomputes GEMM1 -- the hidden
+  // layer still never leaves the chip; the price is (groups - 1) x the FLOPs of GEMM1.
+  int first[16], width[16];
+  const int groups = mlp_wide_column_groups(N, first, width);
+  for (int g = 0; g < groups; ++g) {
+    const int rc = launch_wide_group(x, w1, w2, y, batch, M, width[g], K, L, first[g], N, bf16, w_layout, act1, act2, b1, b2,
+                                     plan, workspace, status, stream, g == 0 ? trace : nullptr);
+    if (rc != DITTO_OK) return rc;
+  }
+  return DITTO_OK;
 }
 
 }  // namespace ditto_b200

@@ -145,6 +145,33 @@ def test_work_loop_many_items(cuda, oracle, dtype, layout):
     assert_close(out.float().cpu().numpy(), oracle.ffn(x, w1, b1, w2, b2, 2, 1, ODT[dtype]), dtype, f"work loop ffn {dtype} {layout}")
 
 
+@pytest.mark.parametrize("layout", ["IO", "OI"])
+def test_results_wider_than_1024_columns(cuda, oracle, layout):
+    """N above 1024 (any multiple of 256): the result is computed in column groups of at most 1024, one
+    launch each -- 2048 = 1024 + 1024, 1280 = 768 + 512, 3072 = 3 x 1024 -- with and without scratch memory for
+    shared row blocks, and with biases (the second one is offset per group) in the feed-forward form."""
+    dtype = "bfloat16"
+    for (batch, M, N, K, L) in ((1, 256, 2048, 64, 512), (2, 208, 1280, 80, 768), (1, 128, 3072, 128, 256),
+                                (1, 128 * 36, 1536, 64, 512)):
+        x, w1, w2 = _inputs(37, batch, M, N, K, L, dtype)
+        want = oracle.gemm_act_gemm(x, w1, w2, 1, ODT[dtype], wide=False)
+        for ws in (None, "auto"):
+            got = _run(cuda, x, w1, w2, dtype, "relu", layout, "auto", workspace=ws)
+            assert_close(got, want, dtype, f"wide N {layout} ws={ws} {(batch, M, N, K, L)}")
+    M, N, K, L = 384, 2048, 64, 512
+    x, w1, w2 = _inputs(38, 1, M, N, K, L, dtype)
+    rng = np.random.default_rng(39)
+    b1 = W._round(rng.standard_normal((1, L)).astype(np.float32) * 0.5, dtype)
+    b2 = W._round(rng.standard_normal((1, N)).astype(np.float32) * 0.5, dtype)
+    d1, d2 = ((_dev(w1.transpose(0, 2, 1), dtype, cuda), _dev(w2.transpose(0, 2, 1), dtype, cuda)) if layout == "OI"
+              else (_dev(w1, dtype, cuda), _dev(w2, dtype, cuda)))
+    out = torch.full((1, M, N), float("nan"), dtype=TDT[dtype], device=cuda)
+    ops.ffn(_dev(x, dtype, cuda), d1, _dev(b1, dtype, cuda), d2, _dev(b2, dtype, cuda), out=out, act1="relu", act2="relu",
+            weight_layout=layout)
+    assert ops.device_status(cuda) == 0
+    assert_close(out.float().cpu().numpy(), oracle.ffn(x, w1, b1, w2, b2, 1, 1, ODT[dtype]), dtype, f"wide N ffn {layout}")
+
+
 def test_golden_vector(cuda):
     case = "mlp_bf16_relu"
     w = make_golden.workload(case)
