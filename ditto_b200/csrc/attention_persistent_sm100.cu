@@ -100,7 +100,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_persistent_kernel(const
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar->q_full[i], 1);
-      mbar_init(&bar->q_empty[i], 1);
+      mbar_init(&bar->q_empty[i], 1 + 4);     // the item's last S MMA has read Q, and the four softmax warps are done
+                                              // with the buffer as the staging area of the item's write-out
     }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&bar->k_full[s], 1);
@@ -389,17 +390,34 @@ __global__ void __launch_bounds__(kThreads, 2) attention_persistent_kernel(const
       tc_fence_before_sync();
       mbar_arrive(&bar->o_free);                   // the next item's first P*V may overwrite O
       const float inv = MODE == kModeSoftmax ? 1.0f / l : 1.0f;
-      const int grow = m0 + row;
-      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
-                      ((static_cast<size_t>(seq) * p.M + grow) * p.out_ld + head_col) * 2;
+      // Written straight from the registers a store instruction would touch 32 rows, 16 bytes each; the
+      // requests back up the load/store path and delay the barrier operations behind them.  Every warp turns
+      // its 32 rows x 128 bytes around in 4 KB of shared memory of its own (16-byte pieces swizzled by row) and
+      // writes 4 rows x 128 contiguous bytes per instruction.
+      // The staging area is the item's own Q buffer: every MMA of the item has retired (o_done), and the
+      // producer refills the buffer -- for the item after next -- only when these warps have arrived on
+      // q_empty as well.
+      uint8_t* stage = smem + kOffQ + (it & 1) * kTileQ + warp * 4096;
 #pragma unroll
       for (int i = 0; i < kD / 8; ++i) {
         uint32_t w[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u)
           w[u] = pack2<BF16>(__uint_as_float(o[8 * i + 2 * u]) * inv, __uint_as_float(o[8 * i + 2 * u + 1]) * inv);
-        if (grow < p.M && i * 8 < p.dv) *reinterpret_cast<uint4*>(orow + i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(stage + lane * 128 + ((i ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
+      __syncwarp();
+      const size_t out_row0 = static_cast<size_t>(seq) * p.M + m0 + warp * 32;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = 4 * i + (lane >> 3), piece = lane & 7;
+        const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((piece ^ (rr & 7)) << 4));
+        if (m0 + warp * 32 + rr < p.M && piece * 8 < p.dv)
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.out) + ((out_row0 + rr) * p.out_ld + head_col + piece * 8) * 2) = v;
+      }
+      fence_proxy_async_smem();                    // these generic-proxy accesses precede the TMA write of the next Q
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->q_empty[it & 1]);
       DITTO_STAMP(it * 16 + 14);
     }
   }

@@ -31,7 +31,9 @@
 // that reads it, and the tensor pipe executes one thread's MMAs in order.
 #include "attention_sm100.cuh"
 
+#include <algorithm>
 #include <atomic>
+#include <type_traits>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -80,6 +82,10 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units; P stays <= 2^8 with a 
 template <int D, int NT, bool PSMEM>
 constexpr bool kSeparateP = (NT == 1 && D == 64 && !PSMEM);
 
+// Instances whose CTAs walk several work items (the others are launched with one CTA per item).
+template <int D, int NT, bool PSMEM>
+constexpr bool kLoopItems = (D == 128 && !kSeparateP<D, NT, PSMEM>);
+
 template <int D, int NT, bool PSMEM>
 struct Smem {
   static constexpr int kTileQ = kBM * D * 2;
@@ -91,13 +97,15 @@ struct Smem {
   static constexpr int kOffV = kOffK + kStages * kTileKV;
   static constexpr int kOffP = kOffV + kStages * kTileKV;
   static constexpr int kOffBar = kOffP + (PSMEM ? NT * kTileP : 0);
-  static constexpr int kBytes = kOffBar + 512 + 1024;  // barriers + slack for 1024-byte alignment
+  static constexpr int kOffStage = kOffBar + 512;       // 4 KB per softmax warp: O rows on their way to global memory
+  static constexpr int kBytes = kOffStage + NT * 4 * 4096 + 1024;  // ... + slack for 1024-byte alignment
 };
 
 struct Barriers {
-  uint64_t q_full;
+  uint64_t q_full[2], q_empty[2];   // per query tile: Q has landed / the item's last S MMA has read it
   uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
   uint64_t s_full[2], p_part[2][2], o_done[2];
+  uint64_t o_free[2];    // the softmax warps have read the finished item's O out of tensor memory (4 warp arrivals)
   uint64_t s_taken[2];   // separate-P variant: the softmax warps hold S in registers
   uint32_t tmem_base;
   uint32_t abort_word;
@@ -140,20 +148,37 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
   constexpr int kMmaWarp = 4 * NT + 1;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // 1-D grid, tile index fastest: the tiles of a slice are scheduled together (their K/V share L2),
-  // and the number of slices is not limited by the 65535 of the other grid dimensions
+  // Work items: (slice, tile of NT x 128 query rows), tile index fastest, so that the tiles of a slice are
+  // worked on together (their K/V share L2) and the number of slices is not limited by the 65535 of the other
+  // grid dimensions.  The grid is one CTA per place the device has and CTA b takes the items b, b + grid, ...:
+  // the K/V ring, the barrier phases and the tensor-memory columns run on across items, the next item's Q and
+  // first K/V blocks are loaded and its first scores computed under the current item's last blocks, and O is
+  // written out while the other tile is still being multiplied.  A CTA's fixed cost -- launch, set-up, first
+  // loads, pipeline fill, write-out, measured 9 us per item against 1.7 us per K/V block -- is paid once per
+  // CTA instead of once per item.  (The separate-P variant has one item per CTA.)
   const int tiles = (p.M + NT * kBM - 1) / (NT * kBM);
-  const int slice = blockIdx.x / tiles;
-  // Packed multi-head input: slice = (sequence, head); rows come from the sequence, columns from
-  // the head.  Plain batched input has heads == 1 and zero column offsets.
-  const int seq = slice / p.heads;
-  const int head_col = (slice % p.heads) * p.d;
-  const int m0 = (blockIdx.x % tiles) * (NT * kBM);
+  // The loop is a compile-time property of the instance (head dimension 128; see the launcher): with one item
+  // per CTA known at compile time the other instances keep the code -- and the registers -- of a single pass.
+  constexpr bool kLoop = kLoopItems<D, NT, PSMEM>;
+  const int my_items = kLoop ? (p.items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x) : 1;
+  struct Item {
+    int slice, seq, head_col, m0;
+  };
+  auto decode = [&](int k) -> Item {
+    Item it;
+    const int id = static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+    it.slice = id / tiles;
+    // Packed multi-head input: slice = (sequence, head); rows come from the sequence, columns from
+    // the head.  Plain batched input has heads == 1 and zero column offsets.
+    it.seq = it.slice / p.heads;
+    it.head_col = (it.slice % p.heads) * p.d;
+    it.m0 = (id % tiles) * (NT * kBM);
+    return it;
+  };
   const int nkv = (p.L + kBN - 1) / kBN;        // the last block may be partial: TMA zero-fills rows >= L
   const int ksteps_d = p.d / 16;                // head dimension actually used by S = Q K^T (<= D / 16)
 
   if (threadIdx.x == 0) {
-    mbar_init(&bar->q_full, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&bar->k_full[s], 1);
       mbar_init(&bar->k_empty[s], 1);
@@ -161,6 +186,9 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
       mbar_init(&bar->v_empty[s], 1);
     }
     for (int t = 0; t < NT; ++t) {
+      mbar_init(&bar->q_full[t], 1);
+      mbar_init(&bar->q_empty[t], 1);
+      mbar_init(&bar->o_free[t], 4);
       mbar_init(&bar->s_full[t], 1);
       mbar_init(&bar->p_part[t][0], kBM);
       mbar_init(&bar->p_part[t][1], kBM);
@@ -196,41 +224,58 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
       tma_prefetch_desc(&p.map_q);
       tma_prefetch_desc(&p.map_k);
       tma_prefetch_desc(&p.map_v);
-      mbar_arrive_expect_tx(&bar->q_full, NT * SM::kTileQ);
-      for (int t = 0; t < NT; ++t)
-        for (int a = 0; a < kAtoms; ++a)
-          tma_load_3d(smem + SM::kOffQ + t * SM::kTileQ + a * (kBM * 128), &p.map_q, &bar->q_full,
-                      p.q_col0 + head_col + a * 64, m0 + t * kBM, seq);
       bool ok = true;
       int armed_k[4] = {-1, -1, -1, -1}, armed_v[4] = {-1, -1, -1, -1};  // parity of the newest armed phase
-      for (int j = 0; j < nkv; ++j) {
-        const int s = j % kStages;
-        const uint32_t ph = (j / kStages) & 1;
-        ok = mbar_wait(&bar->k_empty[s], ph ^ 1, abort_word, 0x100 + j);
-        if (!ok) break;
-        {
-          uint8_t* dst = smem + SM::kOffK + s * SM::kTileKV;
-          mbar_arrive_expect_tx(&bar->k_full[s], SM::kTileKV);
-          armed_k[s] = static_cast<int>(ph);
-          if (p.k_transposed) {
-            // K given as [slice, D, L]: boxes of 64 kv-columns x D rows (MN-major operand)
-            for (int a = 0; a < kBN / 64; ++a)
-              tma_load_3d(dst + a * (D * 128), &p.map_k, &bar->k_full[s], j * kBN + a * 64, 0, slice);
-          } else {
+      int g = 0;                            // K/V blocks loaded so far, over all items: ring stage g % kStages
+      for (int k = 0; k < my_items && ok; ++k) {
+        const Item it = decode(k);
+        auto load_q = [&]() {
+          for (int t = 0; t < NT && ok; ++t) {
+            // the tile's Q buffer is single: the previous item's last S MMA must have read it
+            if (k > 0) ok = mbar_wait(&bar->q_empty[t], (k - 1) & 1, abort_word, 0x180 + t);
+            if (!ok) break;
+            mbar_arrive_expect_tx(&bar->q_full[t], SM::kTileQ);
             for (int a = 0; a < kAtoms; ++a)
-              tma_load_3d(dst + a * (kBN * 128), &p.map_k, &bar->k_full[s], p.k_col0 + head_col + a * 64,
-                          j * kBN, seq);
+              tma_load_3d(smem + SM::kOffQ + t * SM::kTileQ + a * (kBM * 128), &p.map_q, &bar->q_full[t],
+                          p.q_col0 + it.head_col + a * 64, it.m0 + t * kBM, it.seq);
           }
-        }
-        ok = mbar_wait(&bar->v_empty[s], ph ^ 1, abort_word, 0x200 + j);
-        if (!ok) break;
-        {
-          uint8_t* dst = smem + SM::kOffV + s * SM::kTileKV;
-          mbar_arrive_expect_tx(&bar->v_full[s], SM::kTileKV);
-          armed_v[s] = static_cast<int>(ph);
-          for (int a = 0; a < kAtoms; ++a)
-            tma_load_3d(dst + a * (kBN * 128), &p.map_v, &bar->v_full[s], p.v_col0 + head_col + a * 64,
-                        j * kBN, seq);
+        };
+        // A later item's first K block goes out before its Q: the ring stage is free an iteration before the Q
+        // buffers are, and the MMA warp looks two K blocks ahead.
+        if (k == 0) load_q();
+        for (int j = 0; j < nkv && ok; ++j, ++g) {
+          const int s = g % kStages;
+          const uint32_t ph = (g / kStages) & 1;
+          ok = mbar_wait(&bar->k_empty[s], ph ^ 1, abort_word, 0x100 + j);
+          if (!ok) break;
+          {
+            uint8_t* dst = smem + SM::kOffK + s * SM::kTileKV;
+            mbar_arrive_expect_tx(&bar->k_full[s], SM::kTileKV);
+            armed_k[s] = static_cast<int>(ph);
+            if (p.k_transposed) {
+              // K given as [slice, D, L]: boxes of 64 kv-columns x D rows (MN-major operand)
+              for (int a = 0; a < kBN / 64; ++a)
+                tma_load_3d(dst + a * (D * 128), &p.map_k, &bar->k_full[s], j * kBN + a * 64, 0, it.slice);
+            } else {
+              for (int a = 0; a < kAtoms; ++a)
+                tma_load_3d(dst + a * (kBN * 128), &p.map_k, &bar->k_full[s], p.k_col0 + it.head_col + a * 64,
+                            j * kBN, it.seq);
+            }
+          }
+          if (j == 0 && k > 0) {
+            load_q();
+            if (!ok) break;
+          }
+          ok = mbar_wait(&bar->v_empty[s], ph ^ 1, abort_word, 0x200 + j);
+          if (!ok) break;
+          {
+            uint8_t* dst = smem + SM::kOffV + s * SM::kTileKV;
+            mbar_arrive_expect_tx(&bar->v_full[s], SM::kTileKV);
+            armed_v[s] = static_cast<int>(ph);
+            for (int a = 0; a < kAtoms; ++a)
+              tma_load_3d(dst + a * (kBN * 128), &p.map_v, &bar->v_full[s], p.v_col0 + it.head_col + a * 64,
+                          j * kBN, it.seq);
+          }
         }
       }
       if (!ok) {
@@ -299,17 +344,25 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
     // With a single K/V stage the release cannot wait for the next iteration's first MMA
     // (that MMA needs the very load the release unblocks).
     constexpr bool kDeferRelease = kStages >= 2;
-    bool ok = wait(&bar->q_full, 0, 0x300) && wait(&bar->k_full[0], 0, 0x301);
+    // The CTA's K/V blocks form one sequence G = 0 .. my_items * nkv - 1 (block j = G % nkv of item G / nkv):
+    // ring stages, barrier phases and the look-ahead waits follow G, whatever item a block belongs to.
+    const int total_blocks = my_items * nkv;
+    bool ok = wait(&bar->k_full[0], 0, 0x301);
+    for (int t = 0; t < NT && ok; ++t) {
+      ok = wait(&bar->q_full[t], 0, 0x300 + t);
+      if (!ok) break;
+      issue_s(t, 0);
+      if (nkv == 1) umma_commit_elected(&bar->q_empty[t], issuer);   // the item's only S: its Q may be replaced
+    }
     if (ok) {
-      for (int t = 0; t < NT; ++t) issue_s(t, 0);
       umma_commit_elected(&bar->k_empty[0], issuer);
       // operands of the first iteration; later ones are checked one iteration ahead, off the
       // critical path (the loads land long before they are needed)
       ok = wait(&bar->v_full[0], 0, 0x400);
-      if (ok && nkv > 1) ok = wait(&bar->k_full[1 % kStages], (1 / kStages) & 1, 0x600);
+      if (ok && total_blocks > 1) ok = wait(&bar->k_full[1 % kStages], (1 / kStages) & 1, 0x600);
     }
     if constexpr (kSep) {
-      // S(j+1) is issued as soon as the softmax warps have taken S(j) out of TMEM, ahead of
+      // One item per CTA.  S(j+1) is issued as soon as the softmax warps have taken S(j) out of TMEM, ahead of
       // P*V(j): the tensor pipe computes the next scores while the exponentials run.
       for (int j = 0; j < nkv && ok; ++j) {
         const int sv = j % kStages;
@@ -337,41 +390,76 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
         }
       }
     }
-    for (int j = 0; j < (kSep ? 0 : nkv) && ok; ++j) {
-      const int sv = j % kStages;
-      const int sk = (j + 1) % kStages;
-      const bool more = (j + 1 < nkv);
-#pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        ok = wait(&bar->p_part[t][0], j & 1, 0x500 + j);
-        if (!ok) break;
-        DITTO_STAMP(512, j, 1 + 4 * t);
+    // The issuing warp has to stay converged, and every conditional region around an elected issue or a
+    // warp-wide wait costs it a reconvergence: the iteration body therefore exists in three compile-time
+    // forms -- a block inside an item, an item's second-to-last block (its S is the item's last: Q is
+    // released) and an item's last block (O is complete; the next S is the next item's first) -- and the
+    // loop over an item's inner blocks carries no item-boundary tests at all.
+    int G = 0;                                 // the CTA's K/V blocks so far
+    auto iteration = [&](auto kind_c, int j, int k) -> bool {
+      constexpr int kind = decltype(kind_c)::value;     // 0 inner block, 1 second-to-last, 2 last of its item
+      const int sv = G % kStages;
+      const int sk = (G + 1) % kStages;
+      auto tile_step = [&](auto tile) -> bool {
+        constexpr int t = decltype(tile)::value;
+        if (!wait(&bar->p_part[t][0], G & 1, 0x500 + j)) return false;
+        DITTO_STAMP(512, G, 1 + 4 * t);
         issue_pv(t, sv, 0, j > 0 ? 1u : 0u);
-        if (kDeferRelease && t == 0 && j > 0) {
+        if (kDeferRelease && t == 0 && G > 0) {
           // Release the stages the previous iteration finished with.  Deferred to here so that
           // the two commits do not sit between "P is ready" and the first MMA that consumes it.
-          umma_commit_elected(&bar->v_empty[(j - 1) % kStages], issuer);
+          umma_commit_elected(&bar->v_empty[(G - 1) % kStages], issuer);
           umma_commit_elected(&bar->k_empty[sv], issuer);
         }
-        ok = wait(&bar->p_part[t][1], j & 1, 0x580 + j);
-        if (!ok) break;
-        DITTO_STAMP(512, j, 2 + 4 * t);
+        if (!wait(&bar->p_part[t][1], G & 1, 0x580 + j)) return false;
+        DITTO_STAMP(512, G, 2 + 4 * t);
         issue_pv(t, sv, 1, 1u);
         // Same thread, in-order pipe: the next S overwrites the P it follows only after P*V has
         // read it, and its commit also covers that P*V (a commit tracks every earlier MMA).
-        if (more) issue_s(t, sk); else umma_commit_elected(&bar->o_done[t], issuer);
-        DITTO_STAMP(512, j, 3 + 4 * t);
+        if constexpr (kind == 0) {
+          issue_s(t, sk);
+        } else if constexpr (kind == 1) {
+          issue_s(t, sk);
+          umma_commit_elected(&bar->q_empty[t], issuer);   // that was the item's last S: its Q may be replaced
+        } else {
+          umma_commit_elected(&bar->o_done[t], issuer);
+          if (k + 1 < my_items) {
+            // the next item's first S: its Q must have landed
+            if (!wait(&bar->q_full[t], (k + 1) & 1, 0x300 + t)) return false;
+            issue_s(t, sk);
+            if (nkv == 1) umma_commit_elected(&bar->q_empty[t], issuer);
+          }
+        }
+        DITTO_STAMP(512, G, 3 + 4 * t);
+        return true;
+      };
+      if (!tile_step(std::integral_constant<int, 0>{})) return false;
+      if constexpr (NT == 2) {
+        if (!tile_step(std::integral_constant<int, 1>{})) return false;
       }
-      if (!ok) break;
+      const bool more = G + 1 < total_blocks;
       if (!kDeferRelease) {
         umma_commit_elected(&bar->v_empty[sv], issuer);
         if (more) umma_commit_elected(&bar->k_empty[sk], issuer);
       }
       if (more) {
-        ok = wait(&bar->v_full[sk], ((j + 1) / kStages) & 1, 0x400 + j);
-        if (ok && j + 2 < nkv) ok = wait(&bar->k_full[(j + 2) % kStages], ((j + 2) / kStages) & 1, 0x600 + j);
+        if (!wait(&bar->v_full[sk], ((G + 1) / kStages) & 1, 0x400 + j)) return false;
+        if (G + 2 < total_blocks && !wait(&bar->k_full[(G + 2) % kStages], ((G + 2) / kStages) & 1, 0x600 + j)) return false;
       }
-      DITTO_STAMP(512, j, 0);
+      DITTO_STAMP(512, G, 0);
+      ++G;
+      return true;
+    };
+    for (int k = 0; k < (kSep ? 0 : my_items) && ok; ++k) {
+      if (k > 0) {
+        // the first P*V of an item overwrites O: the finished item's O must be out of tensor memory
+        for (int t = 0; t < NT && ok; ++t) ok = wait(&bar->o_free[t], (k - 1) & 1, 0x680 + t);
+        if (!ok) break;
+      }
+      int j = 0;
+      for (; j < nkv - 2 && ok; ++j) ok = iteration(std::integral_constant<int, 0>{}, j, k);
+      if (ok && nkv >= 2) { ok = iteration(std::integral_constant<int, 1>{}, j, k); ++j; }
+      if (ok) ok = iteration(std::integral_constant<int, 2>{}, j, k);
     }
   } else if (warp < 4 * NT) {
     // ------------------------------------------------------------ softmax + epilogue
@@ -382,15 +470,18 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
     const uint32_t o_col = lane_base + kColO + t * D;
     const uint32_t p_col = kSep ? lane_base + kColP : s_col;   // P overwrites S unless it has its own columns
     const float c = p.scale_log2;
-    float m = -INFINITY, l = 0.f;
     bool ok = true;
 
-    for (int j = 0; j < nkv; ++j) {
-      ok = mbar_wait(&bar->s_full[t], j & 1, abort_word, 0x800 + j);
+    uint32_t par = 0;                       // parity of the K/V blocks of all items so far: the phase of s_full / p_part
+
+    for (int k = 0; k < my_items && ok; ++k) {
+    float m = -INFINITY, l = 0.f;
+    for (int j = 0; j < nkv; ++j, par ^= 1u) {
+      ok = mbar_wait(&bar->s_full[t], par, abort_word, 0x800 + j);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      if ((warp & 3) == 0) DITTO_STAMP(t * 256, j, 0); else DITTO_STAMP(t * 256, j, 8 + (warp & 3));
+      if ((warp & 3) == 0) DITTO_STAMP(t * 256, k * nkv + j, 0); else DITTO_STAMP(t * 256, k * nkv + j, 8 + (warp & 3));
 
       uint32_t sv[kBN];
       tmem_ld_x128_wait(s_col, sv);
@@ -398,7 +489,7 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
         tc_fence_before_sync();
         mbar_arrive(&bar->s_taken[t]);             // the S columns may be overwritten by S(j+1)
       }
-      if ((warp & 3) == 0) DITTO_STAMP(t * 256, j, 1);
+      if ((warp & 3) == 0) DITTO_STAMP(t * 256, k * nkv + j, 1);
 
       float m_new = m;
       if constexpr (MODE == kModeSoftmax) {
@@ -455,7 +546,7 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
         m = m_new;
       }
 
-      if ((warp & 3) == 0) DITTO_STAMP(t * 256, j, 2);
+      if ((warp & 3) == 0) DITTO_STAMP(t * 256, k * nkv + j, 2);
       const float mc = m * c;
       float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
@@ -487,7 +578,7 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
             pk[i] = pack2<BF16>(p0, p1);
           }
         }
-        if (part == 0 && (warp & 3) == 0) DITTO_STAMP(t * 256, j, 3);
+        if (part == 0 && (warp & 3) == 0) DITTO_STAMP(t * 256, k * nkv + j, 3);
         if constexpr (PSMEM) {
           // K-major, 128B-swizzled A operand: 64-column atoms of 128 rows x 128 bytes, 16-byte chunks.
           uint8_t* pt = smem + SM::kOffP + t * SM::kTileP;
@@ -519,35 +610,61 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
         }
         tc_fence_before_sync();
         mbar_arrive(&bar->p_part[t][part]);
-        if (part == 0 && (warp & 3) == 0) DITTO_STAMP(t * 256, j, 4);
+        if (part == 0 && (warp & 3) == 0) DITTO_STAMP(t * 256, k * nkv + j, 4);
       }
       l += sum0 + sum1;
-      if ((warp & 3) == 0) DITTO_STAMP(t * 256, j, 5); else DITTO_STAMP(t * 256, j, 5 + (warp & 3));
+      if ((warp & 3) == 0) DITTO_STAMP(t * 256, k * nkv + j, 5); else DITTO_STAMP(t * 256, k * nkv + j, 5 + (warp & 3));
     }
 
-    if (ok) {
-      ok = mbar_wait(&bar->o_done[t], 0, abort_word, 0xA00);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
-      tc_fence_after_sync();
+    if (!ok) break;
+    ok = mbar_wait(&bar->o_done[t], k & 1, abort_word, 0xA00);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    tc_fence_after_sync();
+    if ((warp & 3) == 0) DITTO_STAMP(t * 256, k * nkv + nkv - 1, 12);
+    {
+      const Item it = decode(k);
       const float inv = MODE == kModeSoftmax ? 1.0f / l : 1.0f;
-      const int grow = m0 + t * kBM + row;          // rows >= M (partial last tile) are computed on zero-filled Q, not stored
-      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
-                      ((static_cast<size_t>(seq) * p.M + grow) * p.out_ld + head_col) * 2;
+      // O leaves tensor memory whole (normalised and rounded: D / 2 registers), so that the accumulator is
+      // handed back before the stores and the next item's first P*V never waits for them
+      uint32_t w[D / 2];
+      {
+        uint32_t o[D];                                  // one load for the whole row (the scores' registers are free now)
+        if constexpr (D == 128) tmem_ld_x128_wait(o_col, o); else tmem_ld_x64_wait(o_col, o);   // warp-collective
 #pragma unroll
-      for (int cc = 0; cc < D; cc += 32) {
-        uint32_t o[32];
-        tmem_ld_x32_wait(o_col + cc, o);              // warp-collective: every lane takes part
-        uint32_t w[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
+        for (int i = 0; i < D / 2; ++i)
           w[i] = pack2<BF16>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          if (grow < p.M && cc + i * 8 < p.dv)         // widths are multiples of 16: whole 16-byte pieces
-            *reinterpret_cast<uint4*>(orow + cc * 2 + i * 16) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
       }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->o_free[t]);
+      if ((warp & 3) == 0) DITTO_STAMP(t * 256, k * nkv + nkv - 1, 13);
+      // Written straight from the registers, a warp's store instruction would touch 32 rows (one 16-byte piece
+      // each): 2048 partial-sector requests per tile that back up the load/store path and delay the barrier
+      // operations behind them (measured: the next item's first block ran 6 k clocks late).  Instead every
+      // warp turns its 32 rows x 128 bytes around in 4 KB of shared memory of its own (16-byte pieces swizzled
+      // by row, no bank conflicts either way) and writes 4 rows x 128 contiguous bytes per instruction.
+      uint8_t* stage = smem + SM::kOffStage + warp * 4096;
+      const size_t out_row0 = static_cast<size_t>(it.seq) * p.M + it.m0 + t * kBM + (warp & 3) * 32;
+#pragma unroll
+      for (int pass = 0; pass < D / 64; ++pass) {
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8)
+          *reinterpret_cast<uint4*>(stage + lane * 128 + ((c8 ^ (lane & 7)) << 4)) =
+              make_uint4(w[pass * 32 + 4 * c8], w[pass * 32 + 4 * c8 + 1], w[pass * 32 + 4 * c8 + 2], w[pass * 32 + 4 * c8 + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = 4 * i + (lane >> 3), piece = lane & 7;
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((piece ^ (rr & 7)) << 4));
+          const int col = pass * 64 + piece * 8;        // widths are multiples of 16: whole 16-byte pieces
+          if (it.m0 + t * kBM + (warp & 3) * 32 + rr < p.M && col < p.dv)
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.out) + ((out_row0 + rr) * p.out_ld + it.head_col + col) * 2) = v;
+        }
+        __syncwarp();
+      }
+      if ((warp & 3) == 0) DITTO_STAMP(t * 256, k * nkv + nkv - 1, 14);
+    }
     }
   }
 
@@ -567,6 +684,7 @@ static cudaError_t launch_one(const AttnParams& p, int batch, cudaStream_t strea
   auto kern = attention_kernel<BF16, D, NT, PSMEM, MODE>;
   // the function attributes are set once per device (this instantiation's static)
   static std::atomic<unsigned long long> configured{0};
+  static std::atomic<int> places[64];      // CTAs of this kernel the device holds at once
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
@@ -576,10 +694,26 @@ static cudaError_t launch_one(const AttnParams& p, int batch, cudaStream_t strea
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
+    int per_sm = 0, sms = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads_for(NT), SM::kBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    // the looped variants allocate all 512 tensor-memory columns: one CTA per SM whatever shared memory allows
+    if (!kSeparateP<D, NT, PSMEM>) per_sm = std::min(per_sm, 1);
+    places[dev].store(std::max(1, per_sm * sms), std::memory_order_relaxed);
     configured.fetch_or(1ull << dev, std::memory_order_release);
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>((p.M + NT * kBM - 1) / (NT * kBM)) * static_cast<unsigned>(batch), 1, 1);
+  // one CTA per place the device has (or per item, if there are fewer), or one CTA per item
+  AttnParams q = p;
+  q.items = ((p.M + NT * kBM - 1) / (NT * kBM)) * batch;
+  // The work loop pays where an item is long enough for its fixed cost to show and short enough for it to
+  // matter: measured at head dimension 128 (S = 512: -5 %, 2048: -1 % per item); at 64, where the exponentials
+  // set the pace, one CTA per item was faster (S = 2048: 109 against 119 us), so those launches keep it.
+  constexpr bool loop = kLoopItems<D, NT, PSMEM>;
+  const int grid = loop ? std::min(q.items, places[dev].load(std::memory_order_relaxed)) : q.items;
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
   cfg.blockDim = dim3(threads_for(NT), 1, 1);
   cfg.dynamicSmemBytes = SM::kBytes;
   cfg.stream = stream;
@@ -588,7 +722,7 @@ static cudaError_t launch_one(const AttnParams& p, int batch, cudaStream_t strea
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, p);
+  return cudaLaunchKernelEx(&cfg, kern, q);
 }
 
 cudaError_t launch_attention(const AttnParams& p, int batch, int d, bool bf16, int nt, bool psmem, int mode,

@@ -20,6 +20,7 @@ struct AttnParams {
   int heads;          // 1, or heads folded into the slice index of a packed [sequences, rows, cols] input
   int q_col0, k_col0, v_col0;  // first column of Q / K / V inside the packed row (0 when not packed)
   int out_ld;         // elements between output rows (D when not packed)
+  int items;          // work items of the launch: slices x tiles of NT x 128 query rows (filled in by the launcher)
   float scale_log2;   // softmax scale * log2(e)
   int* status;        // device word receiving a non-zero code if a bounded wait expired; may be null
   long long* trace;   // timeline buffer of -DDITTO_TRACE builds (null otherwise)
