@@ -102,6 +102,7 @@ constexpr int kUnits = DITTO_WIDE_UNITS;
 constexpr int kG1Stages = DITTO_WIDE_G1STAGES;
 constexpr int kW2Stages = DITTO_WIDE_W2STAGES;
 constexpr int kEpiWarps = 8;
+static_assert(kW2Stages <= kUnits, "the W2 producer arms a slot's barrier: it must not run ahead of the slot's previous unit");
 constexpr int kWarpProdG1 = 8, kWarpMmaG1 = 9, kWarpProdW2 = 10, kWarpMmaG2 = 11;
 // Twelve warps: registers are handed out to warps in fours, so a thirteenth would cost every thread 40 of them
 // (65536 / (16 x 32) = 128 against 65536 / (12 x 32) -> 168), and the epilogue warps hold a 128 x 256 tile.
@@ -303,15 +304,19 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       uint32_t pph = 0;
       const int ncol = p.n0 + static_cast<int>(q) * NS;   // W2 / Y column in memory
       bool ok = true;
+      int g = 0;                              // units so far, over all items: slot g % kUnits
       for (int k = 0; k < my_items && ok; ++k) {
         const Item t = decode(k);
-        for (int n = 0; n < units; ++n) {
+        for (int n = 0; n < units; ++n, ++g) {
           const int i = n / (4 * kCluster);
           const int cr = min(kCluster, chunks - kCluster * i);
           const int e = n - 4 * kCluster * i;
           const int hrow = (c0 + i * kCluster + e % cr) * kChunk + (e / cr) * kUnitCols;
           ok = mbar_wait(&bar->w2empty[ps], pph ^ 1, abort_word, 0x200 + i);
           if (!ok) break;
+          // A peer pushes this unit: arm its slot's barrier for the bytes (own units arrive locally).  This thread
+          // is at most kW2Stages units ahead of GEMM2, the slot's previous unit is kUnits back: its phase is over.
+          if (e % cr != static_cast<int>(q)) mbar_arrive_expect_tx(&bar->h_ready[g % kUnits], kUnitBytes);
           uint8_t* dst = smem + kOffW2Ring + ps * kW2StageBytes;
           mbar_arrive_expect_tx(&bar->w2full[ps], static_cast<uint32_t>(64 * NS * 2));
           if (p.w_oi) {
@@ -404,13 +409,10 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       // the Y accumulator is single: the epilogue warps must have read the previous item's out
       if (k > 0) DITTO_TIMED(w_unit, ok = wait(&bar->y_free, (k - 1) & 1, 0x420));
       for (int n = 0; n < units && ok; ++n, ++gn) {
+        // (This warp is the serial resource of GEMM2: no divergent region, no division in its loop.  The W2
+        // producer thread arms h_ready for the units peers push.)
         const int sl = gn % kUnits;
         const int i = n / (4 * kCluster);
-        const int cr = min(kCluster, chunks - kCluster * i);
-        const int src = (n - 4 * kCluster * i) % cr;
-        // a peer pushes this unit: arm the slot's barrier for its bytes (the own units arrive locally)
-        if (src != static_cast<int>(q) && lane == 0) mbar_arrive_expect_tx(&bar->h_ready[sl], kUnitBytes);
-        __syncwarp();
         if (lane == 0 && (n & 15) == 0) DITTO_STAMP(tr + 16 * i + 2);
         DITTO_TIMED(w_unit, ok = wait(&bar->h_ready[sl], (gn / kUnits) & 1, 0x400 + i));
         if (!ok) break;
@@ -426,14 +428,17 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           umma_ss_elected(tmem_y, da + ((s4 * 32) >> 4), db + offb, idesc2, (n | s4) ? 1u : 0u, issuer);
         }
         umma_commit_elected(&bar->w2empty[cs], issuer);
-        if (gn + kUnits < all_units) {
+        {
           // The slot is free once all four CTAs have multiplied the unit: each one's MMA completion arrives
           // directly on the barrier of the CTA that writes the slot next -- the owner of unit gn + kUnits, of
-          // this item or the next (all items of a cluster have the same number of units).
-          const int m = (n + kUnits) % units;
-          const int mi = m / (4 * kCluster);
-          const int mcr = min(kCluster, chunks - kCluster * mi);
-          umma_commit_mcast_elected(&bar->slot_free[sl], 1u << ((m - 4 * kCluster * mi) % mcr), issuer);
+          // this item or the next (all items of a cluster have the same number of units).  The last units of
+          // the CTA have no successor: their commit is predicated off.
+          int m = n + kUnits;
+          m -= m >= units ? units : 0;
+          const int x = m & (4 * kCluster - 1);                      // position in its round
+          const int mcr = min(kCluster, chunks - kCluster * (m / (4 * kCluster)));   // chunks of that round: 1 .. 4
+          const int owner = mcr == 4 ? (x & 3) : mcr == 3 ? x - 3 * ((x * 11) >> 5) : mcr == 2 ? (x & 1) : 0;   // x % mcr, x < 16
+          umma_commit_mcast_elected(&bar->slot_free[sl], 1u << owner, gn + kUnits < all_units ? issuer : 0u);
         }
         if (++cs == kW2Stages) { cs = 0; cph ^= 1; }
         if (lane == 0 && (n & 15) == 15) DITTO_STAMP(tr + 16 * i + 4);
