@@ -181,7 +181,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
   const int lane = threadIdx.x & 31;
   const uint32_t q = cluster_ctarank();   // owns Y columns [q NS, (q+1) NS) and chunks q, q + 4, ... of the item
   const int NS = p.N / kCluster;          // this CTA's Y columns
-  const int all_chunks = p.L / kChunk;
+  const int all_chunks = (p.L + kChunk - 1) / kChunk;   // the last chunk may reach past L: TMA zero-fills W1 columns / W2 rows >= L
   const int ksteps1 = (p.K + 63) / 64;
   // Work items.  Without shared row blocks the launch is persistent: a cluster per place the device has
   // (cudaOccupancyMaxActiveClusters), cluster c taking the (batch entry, row block) items c, c + clusters, ...
@@ -552,7 +552,10 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           uint32_t h[32];
           tmem_ld_x32_wait(tmem_h + lane_base + kk * kUnitCols + grp * 32, h);
           if constexpr (PLAIN) act_pack_fixed<BF16, 1, false>(h, nullptr, v);
-          else act_pack<BF16>(h, bias1 == nullptr ? nullptr : bias1 + kk * (kUnitCols / 2), p.act1, v);
+          // (hidden columns >= L of a last partial chunk: GEMM1 gave zeros, the bias is not read, every
+          // activation maps 0 to 0 and the W2 rows they meet are zero-filled)
+          else act_pack<BF16>(h, (bias1 == nullptr || hcol0 + kk * kUnitCols + grp * 32 >= p.L) ? nullptr : bias1 + kk * (kUnitCols / 2),
+                              p.act1, v);
         };
         auto release_h = [&]() __attribute__((always_inline)) {
           tc_fence_before_sync();
@@ -681,10 +684,11 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
 
 // ------------------------------------------------------------------ host side
 bool mlp_wide_supported(int N, int K, int L) {
-  // 256-wide hidden chunks; K in 16-wide steps (a last partial 64-wide k-step is zero-filled by TMA); a launch
-  // covers up to 1024 Y columns -- N/4 per CTA in whole 64-column groups, at most 256 -- and wider results are
-  // computed as several launches over column groups (see mlp_wide_column_groups)
-  return L % kChunk == 0 && K % 16 == 0 && N % (kCluster * 64) == 0;
+  // 256-wide hidden chunks, the last one possibly partial in whole 64-column groups (TMA zero-fills the rest); K
+  // in 16-wide steps (a last partial 64-wide k-step is zero-filled as well); a launch covers up to 1024 Y columns
+  // -- N/4 per CTA in whole 64-column groups, at most 256 -- and wider results are computed as several launches
+  // over column groups (see mlp_wide_column_groups)
+  return L % 64 == 0 && K % 16 == 0 && N % (kCluster * 64) == 0;
 }
 
 static int mlp_wide_column_groups(int N, int* first, int* width) {
@@ -741,7 +745,7 @@ RowBlockPlan mlp_wide_plan(int batch, int M, int L, int cluster_slots, bool allo
   const int rbs = (M + kRows - 1) / kRows;
   if (!allow_scratch) return {rbs, 1};
   // in units of a 256-wide chunk: an item takes about 14 us + 3.5 us per chunk, sharing adds about 17 us
-  return plan_row_blocks(batch, rbs, L / kChunk, kCluster, kMaxSlabs, cluster_slots, 4.0, 5.0);
+  return plan_row_blocks(batch, rbs, (L + kChunk - 1) / kChunk, kCluster, kMaxSlabs, cluster_slots, 4.0, 5.0);
 }
 
 size_t mlp_wide_workspace_bytes(int batch, int M, int N, const RowBlockPlan& plan) {
@@ -763,7 +767,7 @@ int launch_wide_group(const void* x, const void* w1, const void* w2, void* y, in
   const int NS = N / kCluster;
   const int rbs = (M + kRows - 1) / kRows;
   const int shared_blocks = rbs - plan.whole_blocks;
-  if (plan.whole_blocks < 0 || shared_blocks < 0 || plan.parts < 1 || plan.parts > L / kChunk || plan.parts > kMaxSlabs)
+  if (plan.whole_blocks < 0 || shared_blocks < 0 || plan.parts < 1 || plan.parts > (L + kChunk - 1) / kChunk || plan.parts > kMaxSlabs)
     return DITTO_ERR_INVALID_ARG;
   const bool split = shared_blocks > 0 && plan.parts > 1;
   WideParams p;

@@ -86,7 +86,7 @@ int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M
  *   hidden dimension and the fp32 partials of Y are added through the scratch memory in a fixed order (the
  *   hidden activations still never leave the chip).  NULL or too small: one cluster per row block.
  * Shapes: N <= 128 and K <= 128 (any multiples of 16, [in, out] weights): the reference's own shape family;
- * otherwise L % 128 == 0, K % 64 == 0, N in {256, 512, 768, 1024}, or -- on the default kernel -- L % 256 == 0,
+ * otherwise L % 128 == 0, K % 64 == 0, N in {256, 512, 768, 1024}, or -- on the default kernel -- L % 64 == 0,
  * K % 16 == 0 and N any multiple of 256 up to 16384 (results wider than 1024 columns are computed in column
  * groups of at most 1024, one launch each in stream order, GEMM1 recomputed per group); M any multiple of 16. */
 int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, void* y, int batch, int M, int N,
@@ -124,7 +124,7 @@ int ditto_b200_gemm_relu_gemm_static_scratch(const void* x, const void* w1, cons
  *   b1 [batch, L], b2 [batch, N]: bias vectors in the input type, either may be NULL
  *   act1 / act2: 0 identity, 1 ReLU, 2 GELU (tanh form)
  * Shapes as for the large-N form of ditto_b200_gemm_relu_gemm (L % 128 == 0 with K % 64 == 0 and N in {256, 512,
- * 768, 1024}; L % 256 == 0 with K % 16 == 0 and N any multiple of 256; M any multiple of 16). */
+ * 768, 1024}; L % 64 == 0 with K % 16 == 0 and N any multiple of 256; M any multiple of 16). */
 int ditto_b200_ffn(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, void* y, int batch,
                    int M, int N, int K, int L, int dtype, int w_layout, int act1, int act2, int* status_word,
                    void* stream);

@@ -172,6 +172,38 @@ def test_results_wider_than_1024_columns(cuda, oracle, layout):
     assert_close(out.float().cpu().numpy(), oracle.ffn(x, w1, b1, w2, b2, 1, 1, ODT[dtype]), dtype, f"wide N ffn {layout}")
 
 
+@pytest.mark.parametrize("layout", ["IO", "OI"])
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_hidden_sizes_with_a_partial_last_chunk(cuda, oracle, dtype, layout):
+    """Hidden sizes that are multiples of 64 but not of the 256-wide chunk: the last chunk reaches past L (W1
+    columns / W2 rows beyond it are zero-filled on load, the bias is not read there).  64 and 192: a single
+    partial chunk; 320, 448, 1088: full chunks and a partial one, in the first or a later round; with and
+    without bias / GELU, and inside the work loop (more row blocks than cluster places)."""
+    for (batch, M, N, K, L) in ((1, 128, 256, 64, 64), (2, 208, 512, 80, 192), (1, 256, 1024, 128, 320),
+                                (1, 384, 256, 64, 448), (1, 128, 512, 64, 1088), (1, 128 * 36, 256, 64, 320)):
+        x, w1, w2 = _inputs(41, batch, M, N, K, L, dtype)
+        got = _run(cuda, x, w1, w2, dtype, "relu", layout, "auto", workspace=None)
+        want = oracle.gemm_act_gemm(x, w1, w2, 1, ODT[dtype], wide=False)
+        assert_close(got, want, dtype, f"partial chunk {dtype} {layout} {(batch, M, N, K, L)}")
+    for (M, N, K, L, acts) in ((256, 256, 64, 320, ("gelu", "relu")), (128, 512, 128, 192, ("relu", "identity"))):
+        x, w1, w2 = _inputs(42, 1, M, N, K, L, dtype)
+        rng = np.random.default_rng(43)
+        b1 = W._round(rng.standard_normal((1, L)).astype(np.float32) * 0.5, dtype)
+        b2 = W._round(rng.standard_normal((1, N)).astype(np.float32) * 0.5, dtype)
+        d1, d2 = ((_dev(w1.transpose(0, 2, 1), dtype, cuda), _dev(w2.transpose(0, 2, 1), dtype, cuda)) if layout == "OI"
+                  else (_dev(w1, dtype, cuda), _dev(w2, dtype, cuda)))
+        out = torch.full((1, M, N), float("nan"), dtype=TDT[dtype], device=cuda)
+        # the bias vector sits at the end of an allocation poisoned behind it: a read past L would show
+        pad = torch.full((L + 512,), float("nan"), dtype=TDT[dtype], device=cuda)
+        pad[:L] = _dev(b1, dtype, cuda).view(-1)
+        ops.ffn(_dev(x, dtype, cuda), d1, pad[:L].view(1, L), d2, _dev(b2, dtype, cuda), out=out, act1=acts[0], act2=acts[1],
+                weight_layout=layout)
+        assert ops.device_status(cuda) == 0
+        code = {"identity": 0, "relu": 1, "gelu": 2}
+        assert_close(out.float().cpu().numpy(), oracle.ffn(x, w1, b1, w2, b2, code[acts[0]], code[acts[1]], ODT[dtype]), dtype,
+                     f"partial chunk ffn {dtype} {layout} {(M, N, K, L)}")
+
+
 def test_golden_vector(cuda):
     case = "mlp_bf16_relu"
     w = make_golden.workload(case)
@@ -236,8 +268,8 @@ def test_full_size_properties(cuda):
 
 def test_unsupported_shapes_raise(cuda):
     x = torch.zeros(128, 64, dtype=torch.bfloat16, device=cuda)
-    w1 = torch.zeros(64, 192, dtype=torch.bfloat16, device=cuda)   # hidden 192 is not a multiple of 128
-    w2 = torch.zeros(192, 256, dtype=torch.bfloat16, device=cuda)
+    w1 = torch.zeros(64, 208, dtype=torch.bfloat16, device=cuda)   # hidden 208 is not a multiple of 64
+    w2 = torch.zeros(208, 256, dtype=torch.bfloat16, device=cuda)
     with pytest.raises(_lib.DittoError) as e:
         ops.gemm_relu_gemm(x, w1, w2)
     assert e.value.code == _lib.ERR_UNSUPPORTED
