@@ -174,7 +174,6 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
     // [128, N] fits TMEM next to the intermediate, so the chain runs on the attention kernel with
     // the activation in place of the softmax: A = x, B = w1, C = w2.
     if (static_cast<long long>(batch) * ((M + 127) / 128) > 0x7fffffffLL) return DITTO_ERR_UNSUPPORTED;
-    if (w_layout != 0) return DITTO_ERR_UNSUPPORTED;   // w2 as [N, L] is not an operand form of that kernel
     const bool bf16 = dtype == DITTO_DTYPE_BF16;
     const int dk = (K <= 64 && N <= 64) ? 64 : 128;
     ditto_b200::AttnParams p;
@@ -182,15 +181,24 @@ int ditto_b200_gemm_relu_gemm(const void* x, const void* w1, const void* w2, voi
     const uint64_t uK = K, uM = M, uL = L, ub = batch;
     int rc = make_map_3d(&p.map_q, bf16, x, uK, uM, ub, uK, uM * uK, 64, 128);
     if (rc) return rc;
-    rc = make_map_3d(&p.map_k, bf16, w1, uL, uK, ub, uL, uK * uL, 64, dk);
-    if (rc) return rc;
     const uint64_t uN = N;
-    rc = make_map_3d(&p.map_v, bf16, w2, uN, uL, ub, uN, uL * uN, 64, 128);
+    if (w_layout == 0) {
+      // [in, out] weights: w1 [K, L] is the reference's transposed-K form, w2 [L, N] the usual V
+      rc = make_map_3d(&p.map_k, bf16, w1, uL, uK, ub, uL, uK * uL, 64, dk);
+      if (rc) return rc;
+      rc = make_map_3d(&p.map_v, bf16, w2, uN, uL, ub, uN, uL * uN, 64, 128);
+    } else {
+      // [out, in] weights: w1 [L, K] is K in rows-of-keys form, w2 [N, L] a transposed V (K-major operand of GEMM2)
+      rc = make_map_3d(&p.map_k, bf16, w1, uK, uL, ub, uK, uL * uK, 64, 128);
+      if (rc) return rc;
+      rc = make_map_3d(&p.map_v, bf16, w2, uL, uN, ub, uL, uN * uL, 64, dk);
+    }
     if (rc) return rc;
     p.out = y;
     p.M = M;
     p.L = L;
-    p.k_transposed = 1;
+    p.k_transposed = w_layout == 0;
+    p.v_transposed = w_layout != 0;
     p.d = K;
     p.dv = N;
     p.heads = 1;

@@ -170,7 +170,13 @@ __global__ void __launch_bounds__(kThreads, 2) attention_persistent_kernel(const
           if (!ok) break;
           DITTO_STAMP_T(128, 768 + it * 16 + 8 + j);
           mbar_arrive_expect_tx(&bar->v_full[s], kTileKV);
-          tma_load_3d(smem + kOffV + s * kTileKV, &p.map_v, &bar->v_full[s], p.v_col0 + head_col, j * kBN, seq);
+          if (p.v_transposed) {
+            for (int a = 0; a < kBN / 64; ++a)
+              tma_load_3d(smem + kOffV + s * kTileKV + a * (kD * 128), &p.map_v, &bar->v_full[s], j * kBN + a * 64, 0,
+                          slice);
+          } else {
+            tma_load_3d(smem + kOffV + s * kTileKV, &p.map_v, &bar->v_full[s], p.v_col0 + head_col, j * kBN, seq);
+          }
         }
       }
     }
@@ -179,11 +185,13 @@ __global__ void __launch_bounds__(kThreads, 2) attention_persistent_kernel(const
     const uint32_t issuer = elect_one();
     const bool kt = p.k_transposed != 0;
     const uint32_t idesc_s = umma_idesc_f16(BF16, kBM, kBN, false, kt);
-    const uint32_t idesc_o = umma_idesc_f16(BF16, kBM, kD, false, true);
+    const bool vt = p.v_transposed != 0;           // V stored [slice, dv, L]: K-major operand of P*V
+    const uint32_t idesc_o = umma_idesc_f16(BF16, kBM, kD, false, !vt);
     const uint64_t dq0 = umma_desc_sw128(smem_u32(smem + kOffQ), 16, 1024);
     const uint64_t dk0 = kt ? umma_desc_sw128(smem_u32(smem + kOffK), kD * 128, 1024)
                             : umma_desc_sw128(smem_u32(smem + kOffK), 16, 1024);
-    const uint64_t dv0 = umma_desc_sw128(smem_u32(smem + kOffV), kBN * 128, 1024);
+    const uint64_t dv0 = vt ? umma_desc_sw128(smem_u32(smem + kOffV), 16, 1024)
+                            : umma_desc_sw128(smem_u32(smem + kOffV), kBN * 128, 1024);
     auto wait = [&](uint64_t* b, uint32_t parity, uint32_t code) {
       bool r = mbar_wait(b, parity, abort_word, code);
       r = __all_sync(0xffffffffu, r);
@@ -206,8 +214,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_persistent_kernel(const
       const uint64_t db = dv0 + ((stage * kTileKV) >> 4);
 #pragma unroll
       for (int i = (part == 0 ? 0 : kSplit / 16); i < (part == 0 ? kSplit / 16 : kBN / 16); ++i)
-        umma_ts_elected(tmem_base + kColO, tmem_base + kColP + i * 8, db + ((i * 2048) >> 4), idesc_o,
-                        i > 0 ? 1u : accumulate, issuer);
+        umma_ts_elected(tmem_base + kColO, tmem_base + kColP + i * 8,
+                        db + (vt ? static_cast<uint32_t>(((i / 4) * (kD * 128) + (i % 4) * 32) >> 4)
+                                 : static_cast<uint32_t>((i * 2048) >> 4)),
+                        idesc_o, i > 0 ? 1u : accumulate, issuer);
     };
     bool ok = true;
     int g = 0, it = 0;                             // g: K/V blocks multiplied so far, over all items

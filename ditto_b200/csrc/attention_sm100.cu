@@ -272,9 +272,15 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
             uint8_t* dst = smem + SM::kOffV + s * SM::kTileKV;
             mbar_arrive_expect_tx(&bar->v_full[s], SM::kTileKV);
             armed_v[s] = static_cast<int>(ph);
-            for (int a = 0; a < kAtoms; ++a)
-              tma_load_3d(dst + a * (kBN * 128), &p.map_v, &bar->v_full[s], p.v_col0 + it.head_col + a * 64,
-                          j * kBN, it.seq);
+            if (p.v_transposed) {
+              // V given as [slice, dv, L]: boxes of 64 kv-columns x D rows (K-major operand of P*V)
+              for (int a = 0; a < kBN / 64; ++a)
+                tma_load_3d(dst + a * (D * 128), &p.map_v, &bar->v_full[s], j * kBN + a * 64, 0, it.slice);
+            } else {
+              for (int a = 0; a < kAtoms; ++a)
+                tma_load_3d(dst + a * (kBN * 128), &p.map_v, &bar->v_full[s], p.v_col0 + it.head_col + a * 64,
+                            j * kBN, it.seq);
+            }
           }
         }
       }
@@ -297,11 +303,13 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
     const uint32_t issuer = elect_one();
     const bool kt = p.k_transposed != 0;
     const uint32_t idesc_s = umma_idesc_f16(BF16, kBM, kBN, false, kt);
-    const uint32_t idesc_o = umma_idesc_f16(BF16, kBM, D, false, true);
+    const bool vt = p.v_transposed != 0;
+    const uint32_t idesc_o = umma_idesc_f16(BF16, kBM, D, false, !vt);
     const uint64_t dq0 = umma_desc_sw128(smem_u32(smem + SM::kOffQ), 16, 1024);
     const uint64_t dk0 = kt ? umma_desc_sw128(smem_u32(smem + SM::kOffK), D * 128, 1024)
                             : umma_desc_sw128(smem_u32(smem + SM::kOffK), 16, 1024);
-    const uint64_t dv0 = umma_desc_sw128(smem_u32(smem + SM::kOffV), kBN * 128, 1024);
+    const uint64_t dv0 = vt ? umma_desc_sw128(smem_u32(smem + SM::kOffV), 16, 1024)
+                            : umma_desc_sw128(smem_u32(smem + SM::kOffV), kBN * 128, 1024);
     const uint64_t dp0 = umma_desc_sw128(smem_u32(smem + SM::kOffP), 16, 1024);
 
     auto issue_s = [&](int t, int stage) {
@@ -325,12 +333,16 @@ __global__ void __launch_bounds__(threads_for(NT), kSeparateP<D, NT, PSMEM> ? 2 
 #pragma unroll
       for (int i = (part == 0 ? 0 : kSplit / 16); i < (part == 0 ? kSplit / 16 : kBN / 16); ++i) {
         const uint32_t acc = i > 0 ? 1u : accumulate;
+        // MN-major V: 16 K/V rows of 128 bytes per k-step; K-major (transposed V): 32 bytes per k-step inside a
+        // 64-column atom of D rows, then the next atom
+        const uint32_t off_v = vt ? static_cast<uint32_t>(((i / 4) * (D * 128) + (i % 4) * 32) >> 4)
+                                  : static_cast<uint32_t>((i * 2048) >> 4);
         if constexpr (PSMEM) {
           const uint64_t da = dp0 + ((t * SM::kTileP + (i / 4) * (kBM * 128) + (i % 4) * 32) >> 4);
-          umma_ss_elected(tmem_base + kColO + t * D, da, db + ((i * 2048) >> 4), idesc_o, acc, issuer);
+          umma_ss_elected(tmem_base + kColO + t * D, da, db + off_v, idesc_o, acc, issuer);
         } else {
           umma_ts_elected(tmem_base + kColO + t * D, tmem_base + (kSep ? kColP : t * kBN) + i * 8,
-                          db + ((i * 2048) >> 4), idesc_o, acc, issuer);
+                          db + off_v, idesc_o, acc, issuer);
         }
       }
     };

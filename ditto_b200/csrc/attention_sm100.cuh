@@ -17,6 +17,7 @@ struct AttnParams {
   int d;              // width of Q and K in use: the reduction length of S = Q K^T (multiple of 16, <= the kernel's D)
   int dv;             // width of V and of the output (multiple of 16, <= the kernel's D); columns beyond it are zero-filled / not stored
   int k_transposed;   // 1: K stored [batch, D, L] (the reference's layout)
+  int v_transposed;   // 1: V stored [batch, dv, L] (map_v: box 64 x D x 1; the [out, in] second weight of a small-N chain)
   int heads;          // 1, or heads folded into the slice index of a packed [sequences, rows, cols] input
   int q_col0, k_col0, v_col0;  // first column of Q / K / V inside the packed row (0 when not packed)
   int out_ld;         // elements between output rows (D when not packed)

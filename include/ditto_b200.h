@@ -85,7 +85,7 @@ int ditto_b200_multi_head_attention(const void* qkv, void* out, int batch, int M
  *   undefined on return).  With few row blocks several clusters share a row block, each takes a range of the
  *   hidden dimension and the fp32 partials of Y are added through the scratch memory in a fixed order (the
  *   hidden activations still never leave the chip).  NULL or too small: one cluster per row block.
- * Shapes: N <= 128 and K <= 128 (any multiples of 16, [in, out] weights): the reference's own shape family;
+ * Shapes: N <= 128 and K <= 128 (any multiples of 16, either weight layout): the reference's own shape family;
  * otherwise L % 128 == 0, K % 64 == 0, N in {256, 512, 768, 1024}, or -- on the default kernel -- L % 64 == 0,
  * K % 16 == 0 and N any multiple of 256 up to 16384 (results wider than 1024 columns are computed in column
  * groups of at most 1024, one launch each in stream order, GEMM1 recomputed per group); M any multiple of 16. */

@@ -278,22 +278,25 @@ def test_unsupported_shapes_raise(cuda):
 @pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
 @pytest.mark.parametrize("act", ["relu", "identity"])
 @pytest.mark.parametrize("d", [64, 128])
-def test_small_n_chains(cuda, oracle, dtype, act, d):
+@pytest.mark.parametrize("layout", ["IO", "OI"])
+def test_small_n_chains(cuda, oracle, dtype, act, d, layout):
     """N = K in {64, 128}: the reference's own shape family (benchmark/chimera/cuda/bmm_bmm_cuda.py
-    shapes table, python_test/auto_tensorize/test_hyper_fusion_cpu.py) -- batched, per-slice weights."""
+    shapes table, python_test/auto_tensorize/test_hyper_fusion_cpu.py) -- batched, per-slice weights, as
+    [in, out] (the reference's chain operands) and as [out, in] (its linear layers' weights)."""
     for (batch, M, L) in ((2, 128, 128), (3, 256, 384), (8, 512, 512), (2, 208, 272), (1, 516 // 4 * 4 // 16 * 16 + 16, 512)):
         rng = np.random.default_rng(31)
         a = W._round(rng.uniform(-1, 1, (batch, M, d)).astype(np.float32), dtype)
         b = W._round(rng.uniform(-1, 1, (batch, d, L)).astype(np.float32), dtype)
         c = W._round(rng.uniform(-1, 1, (batch, L, d)).astype(np.float32), dtype)
-        got = _run(cuda, a, b, c, dtype, act, "IO")
+        got = _run(cuda, a, b, c, dtype, act, layout)
         want = oracle.gemm_act_gemm(a, b, c, 1 if act == "relu" else 0, ODT[dtype], wide=False)
         # |result| grows like sqrt(K L) for U(-1,1) operands: scale the absolute floor with it
-        assert_close(got, want, dtype, f"{dtype} {act} d={d} {(batch, M, L)}", scale=float(np.abs(want).max()))
+        assert_close(got, want, dtype, f"{dtype} {act} d={d} {layout} {(batch, M, L)}", scale=float(np.abs(want).max()))
 
 
 @pytest.mark.parametrize("act", ["relu", "identity"])
-def test_small_n_chains_with_different_widths(cuda, oracle, act):
+@pytest.mark.parametrize("layout", ["IO", "OI"])
+def test_small_n_chains_with_different_widths(cuda, oracle, act, layout):
     """N != K, both <= 128: (A B) C with A [M, K], B [K, L], C [L, N] on the attention kernel's chain mode."""
     dtype = "float16"
     for (batch, M, N, K, L) in ((2, 256, 128, 64, 256), (3, 208, 64, 128, 272), (1, 128, 48, 80, 144), (2, 384, 32, 64, 1040)):
@@ -301,9 +304,9 @@ def test_small_n_chains_with_different_widths(cuda, oracle, act):
         a = W._round(rng.uniform(-1, 1, (batch, M, K)).astype(np.float32), dtype)
         b = W._round(rng.uniform(-1, 1, (batch, K, L)).astype(np.float32), dtype)
         c = W._round(rng.uniform(-1, 1, (batch, L, N)).astype(np.float32), dtype)
-        got = _run(cuda, a, b, c, dtype, act, "IO")
+        got = _run(cuda, a, b, c, dtype, act, layout)
         want = oracle.gemm_act_gemm(a, b, c, 1 if act == "relu" else 0, ODT[dtype], wide=False)
-        assert_close(got, want, dtype, f"{act} N != K {(batch, M, N, K, L)}", scale=float(np.abs(want).max()))
+        assert_close(got, want, dtype, f"{act} {layout} N != K {(batch, M, N, K, L)}", scale=float(np.abs(want).max()))
 
 
 def test_small_n_golden_and_cfg1_shape(cuda, oracle):
