@@ -45,13 +45,28 @@ __device__ __forceinline__ float act_apply(float v) {
 // loads) -> activation -> N / 2 packed 16-bit pairs.  The activation and the presence of a bias are
 // compile-time here: a run-time test per element costs a branch per element, which made this loop the
 // longest step of the hidden-chunk hand-over.
-template <bool BF16, int ACT, bool BIAS, int N>
+// VEC: the bias pointer is 16-byte aligned and is read eight values at a time (a load per pair of columns is
+// 64 load instructions per thread and hidden chunk).
+template <bool BF16, int ACT, bool BIAS, int N, bool VEC = false>
 __device__ __forceinline__ void act_pack_fixed(const uint32_t (&acc)[N], const uint32_t* bias, uint32_t (&out)[N / 2]) {
+  uint32_t bw[BIAS ? N / 2 : 1];
+  if constexpr (BIAS) {
+    if constexpr (VEC) {
+#pragma unroll
+      for (int j4 = 0; j4 < N / 8; ++j4) {
+        const uint4 t = __ldg(reinterpret_cast<const uint4*>(bias) + j4);
+        bw[4 * j4] = t.x; bw[4 * j4 + 1] = t.y; bw[4 * j4 + 2] = t.z; bw[4 * j4 + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < N / 2; ++j) bw[j] = __ldg(bias + j);
+    }
+  }
 #pragma unroll
   for (int j = 0; j < N / 2; ++j) {
     float v0 = __uint_as_float(acc[2 * j]), v1 = __uint_as_float(acc[2 * j + 1]);
     if constexpr (BIAS) {
-      const float2 bb = unpack2<BF16>(__ldg(bias + j));
+      const float2 bb = unpack2<BF16>(bw[j]);
       v0 += bb.x;
       v1 += bb.y;
     }

@@ -164,10 +164,19 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
 
 }  // namespace
 
-// PLAIN: ReLU after GEMM1, nothing after GEMM2, no bias -- the chain as the reference defines it.  The general
-// form picks activation and bias at run time (one warp-uniform dispatch per accumulator piece); its six code
-// paths per call site cost registers the plain chain does not have to pay for.
-template <bool BF16, bool PLAIN>
+// EPI names the two epilogues at compile time: 1 = ReLU after GEMM1, nothing after GEMM2, no bias (the chain as
+// the reference defines it); 2 = bias + ReLU after both (the reference's feed-forward block); 3 = bias + GELU,
+// then bias (the same block with the reference's GELU in the usual place); 0 = activations and biases picked at
+// run time (one warp-uniform dispatch per accumulator piece).  The general form's six code paths per call site
+// cost registers (1.5 KB of spills) and time -- config 4 with biases: 878 against 1030 TFLOP/s -- which the
+// named forms do not pay.
+template <int EPI> struct Epilogues;
+template <> struct Epilogues<0> { static constexpr int act1 = 0, act2 = 0; static constexpr bool bias = false; };
+template <> struct Epilogues<1> { static constexpr int act1 = 1, act2 = 0; static constexpr bool bias = false; };
+template <> struct Epilogues<2> { static constexpr int act1 = 1, act2 = 1; static constexpr bool bias = true; };
+template <> struct Epilogues<3> { static constexpr int act1 = 2, act2 = 0; static constexpr bool bias = true; };
+
+template <bool BF16, int EPI>
 __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     mlp_wide_kernel(const __grid_constant__ WideParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -485,7 +494,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           if (c * 16 < NS / 2) {
             uint32_t o[16];
             tmem_ld_x16_wait(tmem_y + lane_base + colg + c * 16, o);
-            if constexpr (PLAIN) act_pack_fixed<BF16, 0, false>(o, nullptr, w[c]);
+            if constexpr (EPI != 0) act_pack_fixed<BF16, Epilogues<EPI>::act2, Epilogues<EPI>::bias, 16, true>(o, bias2 + c * 8, w[c]);
             else act_pack<BF16>(o, bias2 == nullptr ? nullptr : bias2 + c * 8, p.act2, w[c]);
           }
         }
@@ -551,10 +560,16 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         auto load_quarter = [&](int kk, uint32_t (&v)[16]) __attribute__((always_inline)) {
           uint32_t h[32];
           tmem_ld_x32_wait(tmem_h + lane_base + kk * kUnitCols + grp * 32, h);
-          if constexpr (PLAIN) act_pack_fixed<BF16, 1, false>(h, nullptr, v);
           // (hidden columns >= L of a last partial chunk: GEMM1 gave zeros, the bias is not read, every
           // activation maps 0 to 0 and the W2 rows they meet are zero-filled)
-          else act_pack<BF16>(h, (bias1 == nullptr || hcol0 + kk * kUnitCols + grp * 32 >= p.L) ? nullptr : bias1 + kk * (kUnitCols / 2),
+          if constexpr (EPI != 0) {
+            if (Epilogues<EPI>::bias && hcol0 + kk * kUnitCols + grp * 32 >= p.L) {
+#pragma unroll
+              for (int z = 0; z < 16; ++z) v[z] = 0u;
+            } else {
+              act_pack_fixed<BF16, Epilogues<EPI>::act1, Epilogues<EPI>::bias, 32, true>(h, bias1 + kk * (kUnitCols / 2), v);
+            }
+          } else act_pack<BF16>(h, (bias1 == nullptr || hcol0 + kk * kUnitCols + grp * 32 >= p.L) ? nullptr : bias1 + kk * (kUnitCols / 2),
                               p.act1, v);
         };
         auto release_h = [&]() __attribute__((always_inline)) {
@@ -714,10 +729,14 @@ cudaError_t wide_configure(int* slots_out) {
   cudaError_t e = current_device_checked(&dev);
   if (e != cudaSuccess) return e;
   if (!device_configured(configured, dev)) {
-    auto kern = mlp_wide_kernel<BF16, false>;
+    auto kern = mlp_wide_kernel<BF16, 0>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(mlp_wide_kernel<BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    e = cudaFuncSetAttribute(mlp_wide_kernel<BF16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(mlp_wide_kernel<BF16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(mlp_wide_kernel<BF16, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
     // how many clusters of four the device holds at once: the unit row-block sharing is sized against
     cudaLaunchConfig_t cfg = {};
@@ -852,9 +871,21 @@ int launch_wide_group(const void* x, const void* w1, const void* w2, void* y, in
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = split ? 0 : 1;           // a launch with shared row blocks follows its own counter reset: plain stream order
-  const bool plain = act1 == 1 && act2 == 0 && b1 == nullptr && b2 == nullptr;
-  cudaError_t e = plain ? (bf16 ? cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, true>, p) : cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, true>, p))
-                        : (bf16 ? cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, false>, p) : cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, false>, p));
+  // the named forms read their biases 16 bytes at a time
+  const bool both = b1 != nullptr && b2 != nullptr && ((reinterpret_cast<uintptr_t>(b1) | reinterpret_cast<uintptr_t>(b2)) & 15) == 0;
+  const bool none = b1 == nullptr && b2 == nullptr;
+  const int epi = (act1 == 1 && act2 == 0 && none) ? 1 : (act1 == 1 && act2 == 1 && both) ? 2 : (act1 == 2 && act2 == 0 && both) ? 3 : 0;
+  cudaError_t e = cudaErrorInvalidValue;
+  switch (epi * 2 + (bf16 ? 1 : 0)) {
+    case 0: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, 0>, p); break;
+    case 1: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, 0>, p); break;
+    case 2: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, 1>, p); break;
+    case 3: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, 1>, p); break;
+    case 4: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, 2>, p); break;
+    case 5: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, 2>, p); break;
+    case 6: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, 3>, p); break;
+    default: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, 3>, p); break;
+  }
   return e == cudaSuccess ? DITTO_OK : cuda_fail("mlp wide kernel launch", e);
 }
 
