@@ -556,6 +556,40 @@ def unfused_context(run, w, barrier):
             "what": "torch.matmul -> relu -> torch.matmul (cuBLAS), hidden layer through HBM"}
 
 
+def feed_forward_context(run, w):
+    """Beside the plain chain: the reference's feed-forward block on the same shape -- [out, in] weights, biases,
+    ReLU after both GEMMs (nn/model/transformer.py:21-34) -- and its GELU form, through ops.ffn, cold launches."""
+    torch = run.torch
+    from ditto_b200 import ops
+    x, (w1, w2) = run.inputs[0], run.resident
+    w1t, w2t = w1.t().contiguous(), w2.t().contiguous()
+    g = torch.Generator(device=run.device)
+    g.manual_seed(4)
+    b1 = torch.randn(w1t.shape[0], device=run.device, generator=g).to(x.dtype)
+    b2 = torch.randn(w2t.shape[0], device=run.device, generator=g).to(x.dtype)
+    out = torch.empty((x.shape[0], w2t.shape[0]), dtype=x.dtype, device=run.device)
+    result = {}
+    for name, (a1, a2) in (("bias_relu_relu", ("relu", "relu")), ("bias_gelu_identity", ("gelu", "identity"))):
+        def step():
+            ops.ffn(x, w1t, b1, w2t, b2, out=out, act1=a1, act2=a2)
+        for _ in range(3):
+            step()
+            run.flush.zero_()
+        torch.cuda.synchronize(run.device)
+        total = 0.0
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            run.flush.zero_()
+            e1.synchronize()
+            total += e0.elapsed_time(e1)
+        ms = total / 10
+        result[name] = {"ms_per_step": ms, "value": w.flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s"}
+    return result
+
+
 def main():
     args = parse_args()
     if args.shape_table:
@@ -665,6 +699,8 @@ def main():
                 entry["cluster_slots"] = mlp_cluster_slots()
                 if world == 1:
                     entry["context_unfused_torch"] = unfused_context(orun, ow, barrier)
+                    if ow.kind == "relu" and len(orun.resident[0].shape) == 2:
+                        entry["feed_forward_block"] = feed_forward_context(orun, ow)
             others.append(entry)
             del orun
             torch.cuda.empty_cache()
