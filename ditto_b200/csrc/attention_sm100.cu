@@ -10,9 +10,13 @@
 //   O += P * V            tcgen05.mma, P read from TMEM (or swizzled smem)
 //   out = O / rowsum(P)   epilogue, written once as fp16 / bf16
 //
-// The score tile never leaves the SM.  One CTA owns NT (1 or 2) tiles of 128
-// query rows of one slice (batch x head) and streams the slice's K/V in blocks
-// of 128 rows through a TMA-fed ring of 128B-swizzled shared-memory stages.
+// The score tile never leaves the SM.  A work item is NT (1 or 2) tiles of 128
+// query rows of one slice (batch x head); its K/V stream in blocks of 128 rows
+// through a TMA-fed ring of 128B-swizzled shared-memory stages.  At head
+// dimension 128 a CTA per SM walks the items (ring, barrier phases and tensor
+// memory run on across them); the other instances are launched with a CTA per
+// item.  O leaves through 4 KB of shared memory per softmax warp, so that a
+// store instruction writes whole rows.
 //
 // Warp roles (NT = 2: 320 threads):
 //   warps 0-3   softmax + epilogue for query tile 0  (thread i <-> row i, TMEM lane i)
