@@ -416,7 +416,13 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
       const int tr = k < 6 ? 64 * k : 4096;
       (void)tr;
       // the Y accumulator is single: the epilogue warps must have read the previous item's out
+#ifdef DITTO_TRACE
+      if (k == 1 && lane == 0 && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) p.trace[410] = clock64();
+#endif
       if (k > 0) DITTO_TIMED(w_unit, ok = wait(&bar->y_free, (k - 1) & 1, 0x420));
+#ifdef DITTO_TRACE
+      if (k == 1 && lane == 0 && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) p.trace[411] = clock64();
+#endif
       for (int n = 0; n < units && ok; ++n, ++gn) {
         // (This warp is the serial resource of GEMM2: no divergent region, no division in its loop.  The W2
         // producer thread arms h_ready for the units peers push.)
@@ -428,6 +434,9 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         if (lane == 0 && (n & 15) == 0) DITTO_STAMP(tr + 16 * i + 3);
         DITTO_TIMED(w_g2, ok = wait(&bar->w2full[cs], cph, 0x410 + i));
         if (!ok) break;
+#ifdef DITTO_TRACE
+        if (k == 1 && n < 4 && lane == 0 && p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) p.trace[412 + n] = clock64();
+#endif
         const uint32_t sw = ring + cs * kW2StageBytes;
         const uint64_t da = umma_desc_sw128(slots + sl * kUnitBytes, 16, 1024);
         const uint64_t db = p.w_oi ? umma_desc_sw128(sw, 16, 1024) : umma_desc_sw128(sw, 8192, 1024);
@@ -488,14 +497,29 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         uint8_t* yrow = reinterpret_cast<uint8_t*>(p.y) + ((static_cast<size_t>(t.b) * p.M + t.row0 + row) * p.ldn + p.n0 + ycol0) * 2;
         const uint32_t* bias2 = p.b2 == nullptr ? nullptr
                                                 : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(t.b) * p.ldn + p.n0 + ycol0) / 2;
-        uint32_t w[8][8];                       // 16 columns a piece: short live ranges next to the 64 result registers
+        uint32_t w[8][8];                       // 16 columns a piece
+        auto pack_piece = [&](int c, const uint32_t (&o)[16]) __attribute__((always_inline)) {
+          if constexpr (EPI != 0) act_pack_fixed<BF16, Epilogues<EPI>::act2, Epilogues<EPI>::bias, 16, true>(o, bias2 + c * 8, w[c]);
+          else act_pack<BF16>(o, bias2 == nullptr ? nullptr : bias2 + c * 8, p.act2, w[c]);
+        };
+        if (NS == 256) {
+          // the full width: two loads of 64 columns -- the accumulator is handed back (below) two loads'
+          // latencies after the item's last MMA instead of eight (one load of 128 would not fit the registers)
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          if (c * 16 < NS / 2) {
-            uint32_t o[16];
-            tmem_ld_x16_wait(tmem_y + lane_base + colg + c * 16, o);
-            if constexpr (EPI != 0) act_pack_fixed<BF16, Epilogues<EPI>::act2, Epilogues<EPI>::bias, 16, true>(o, bias2 + c * 8, w[c]);
-            else act_pack<BF16>(o, bias2 == nullptr ? nullptr : bias2 + c * 8, p.act2, w[c]);
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t o[64];
+            tmem_ld_x64_wait(tmem_y + lane_base + colg + hf * 64, o);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) pack_piece(4 * hf + c, *reinterpret_cast<const uint32_t(*)[16]>(&o[16 * c]));
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            if (c * 16 < NS / 2) {
+              uint32_t o[16];
+              tmem_ld_x16_wait(tmem_y + lane_base + colg + c * 16, o);
+              pack_piece(c, o);
+            }
           }
         }
         if (release) {
@@ -503,12 +527,47 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
           __syncwarp();
           if (lane == 0) mbar_arrive(&bar->y_free);
         }
-        if (t.row0 + row < p.M) {               // rows >= M of a partial last block were computed on zero-filled X
+        // Stored as they are, a store instruction would touch 32 rows with 16 bytes each, and the 2048 requests of
+        // a CTA back up the load/store path: the barrier operations of every other warp queue behind them (timeline:
+        // the next item's first GEMM2 started when the stores ended, 5 k clocks late).  Shared memory has no room
+        // for staging here, so groups of four lanes transpose 4 x 4 blocks of 16-byte pieces with shuffles: an
+        // instruction then writes 64 contiguous bytes of each of 8 rows, a quarter of the requests.
+        {
+          const int a = lane & 3;
+          (void)yrow;
+          // rows of this lane's group of four: lane_row - a + b, b = 0 .. 3
+          uint8_t* ygrp = reinterpret_cast<uint8_t*>(p.y) +
+                          ((static_cast<size_t>(t.b) * p.M + t.row0 + row - a) * p.ldn + p.n0 + ycol0) * 2;
+          const size_t pitch = static_cast<size_t>(p.ldn) * 2;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            if (c * 16 < NS / 2) {
-              *reinterpret_cast<uint4*>(yrow + c * 32) = make_uint4(w[c][0], w[c][1], w[c][2], w[c][3]);
-              *reinterpret_cast<uint4*>(yrow + c * 32 + 16) = make_uint4(w[c][4], w[c][5], w[c][6], w[c][7]);
+          for (int m = 0; m < 4; ++m) {
+            if (m * 32 < NS / 2) {
+              // v[b][0..3]: piece 4 m + b of this lane's row  ->  piece 4 m + a of row b of the group
+              uint32_t (&v0)[8] = w[2 * m];
+              uint32_t (&v1)[8] = w[2 * m + 1];
+              auto el = [&](int b, int j) -> uint32_t& { return b < 2 ? v0[4 * b + j] : v1[4 * (b - 2) + j]; };
+#pragma unroll
+              for (int b = 0; b < 4; b += 2) {            // lanes a ^ 1 exchange pieces b / b + 1
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint32_t give = (a & 1) ? el(b, j) : el(b + 1, j);
+                  const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 1);
+                  if (a & 1) el(b, j) = got; else el(b + 1, j) = got;
+                }
+              }
+#pragma unroll
+              for (int b = 0; b < 2; ++b) {               // lanes a ^ 2 exchange pieces b / b + 2
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint32_t give = (a & 2) ? el(b, j) : el(b + 2, j);
+                  const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 2);
+                  if (a & 2) el(b, j) = got; else el(b + 2, j) = got;
+                }
+              }
+#pragma unroll
+              for (int b = 0; b < 4; ++b)                 // rows >= M of a partial last block were computed on zero-filled X
+                if (t.row0 + row - a + b < p.M)
+                  *reinterpret_cast<uint4*>(ygrp + b * pitch + (4 * m + a) * 16) = make_uint4(el(b, 0), el(b, 1), el(b, 2), el(b, 3));
             }
           }
         }
