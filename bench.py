@@ -40,7 +40,7 @@ L2_BYTES = 126 * 1024 * 1024
 NCU_TRAFFIC_BYTES_PER_UNIT = {
     "cfg5": (201.488e6 + 47.643e6) / 128,   # capture of the first 128 slices
     "cfg3": (101.050e6 + 11.025e6) / 512,   # capture of a full launch
-    "cfg4": (50.468e6 + 3.526e6) / 128,     # capture of a full launch, 128 row blocks
+    "cfg4": (50.484e6 + 5.570e6) / 128,     # capture of a full launch, 128 row blocks
 }
 
 
