@@ -269,6 +269,35 @@ def test_work_loop_many_items(cuda, dtype):
         assert bool((err <= bound).all()), ((b, M, L, d), err.max().item())
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_work_loop_head_dimension_128(cuda, dtype):
+    """Head dimensions above 64 run the two-tile (one-tile for M <= 128) kernel inside a work loop: one CTA per
+    SM walks the (slice, tile) items, Q is reloaded per item behind the item's last scores, the next item's first
+    scores are issued behind the last P V.  Every output row of launches with more items than SMs is compared with
+    a float32 product: one key block per item (its only scores are also its last), two, three and many; a
+    partial second query tile; a ragged key tail; the reference's transposed-K layout; a narrower value width."""
+    g = torch.Generator(device=cuda).manual_seed(7)
+    cases = ((330, 128, 128, 128, 128, "LK"), (170, 384, 128, 96, 96, "LK"), (160, 256, 256, 128, 128, "KL"),
+             (150, 512, 384, 80, 80, "LK"), (80, 528, 1104, 128, 64, "LK"), (24, 2048, 2048, 128, 128, "LK"))
+    for (b, M, L, d, dv, layout) in cases:
+        q = (torch.rand(b, M, d, device=cuda, generator=g) - 0.5).to(dtype)
+        k = (torch.rand(b, L, d, device=cuda, generator=g) - 0.5).to(dtype)
+        v = (torch.rand(b, L, dv, device=cuda, generator=g) - 0.5).to(dtype)
+        out = torch.full((b, M, dv), float("nan"), dtype=dtype, device=cuda)
+        kk = k.transpose(1, 2).contiguous() if layout == "KL" else k
+        ops.bmm_softmax_bmm(q, kk, v, out=out, scale=1.0, key_layout=layout)
+        assert ops.device_status(cuda) == 0
+        ref = torch.softmax(q.float() @ k.float().transpose(1, 2), -1) @ v.float()
+        tol = 2e-2 if dtype == torch.float16 else 3e-2
+        err = (out.float() - ref).abs()
+        bound = tol * ref.abs() + (1e-3 if dtype == torch.float16 else 4e-3)
+        assert not torch.isnan(out).any(), (b, M, L, d, dv, layout)
+        assert bool((err <= bound).all()), ((b, M, L, d, dv, layout), err.max().item())
+        again = torch.empty_like(out)
+        ops.bmm_softmax_bmm(q, kk, v, out=again, scale=1.0, key_layout=layout)
+        assert torch.equal(out, again), "runs of the work loop differ"
+
+
 def test_unsupported_shapes_raise(cuda):
     q = torch.zeros(1, 128, 144, dtype=torch.float16, device=cuda)     # head dimension above 128
     kv = torch.zeros(1, 128, 64, dtype=torch.float16, device=cuda)
