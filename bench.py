@@ -133,7 +133,7 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------- the GPU arm
-class GpuRun:
+class DeviceRun:
     """This rank's shard of a workload on its GPU: device inputs, pinned host copies, timed passes."""
 
     def __init__(self, w, rank, world, device):
@@ -630,7 +630,7 @@ def main():
     barrier = D.barrier
     peaks = measured_peaks()
 
-    run = GpuRun(w, rank, world, device)
+    run = DeviceRun(w, rank, world, device)
     err = run.sanity()
     warm = max(args.warmup, 3)
     # Both methods at every GPU count; `value` takes the cold one everywhere (see headline_method).
@@ -677,7 +677,7 @@ def main():
             ow = W.WORKLOADS[name]
             if ow.dtype == "float32" or (world > 1 and ow.units < 8 * world):
                 continue                      # config 2's twelve slices are a one-GPU case
-            orun = GpuRun(ow, rank, world, device)
+            orun = DeviceRun(ow, rank, world, device)
             oerr = D.max_over_ranks(orun.sanity(), device)
             with ClockSampler(local) as oclk:
                 oms_cold, _ = orun.time_cold(10, 3, barrier)
