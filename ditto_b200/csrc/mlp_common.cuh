@@ -90,6 +90,30 @@ __device__ __forceinline__ float act_apply_rt(float v, int act) {
   return act == 1 ? act_apply<1>(v) : act == 2 ? act_apply<2>(v) : v;
 }
 
+// Four consecutive lanes (a = lane & 3) each hold four 16-byte pieces v[b][0..3], b = 0 .. 3, of their own row:
+// afterwards lane a holds piece a of row b of the group in v[b] -- a 4 x 4 transpose by two rounds of pairwise
+// exchanges -- so that one store instruction writes 64 contiguous bytes of a row instead of 16.
+__device__ __forceinline__ void quad_transpose(uint32_t (&v)[4][4], int a) {
+#pragma unroll
+  for (int b = 0; b < 4; b += 2) {              // lanes a ^ 1 exchange pieces b / b + 1
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t give = (a & 1) ? v[b][j] : v[b + 1][j];
+      const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 1);
+      if (a & 1) v[b][j] = got; else v[b + 1][j] = got;
+    }
+  }
+#pragma unroll
+  for (int b = 0; b < 2; ++b) {                 // lanes a ^ 2 exchange pieces b / b + 2
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t give = (a & 2) ? v[b][j] : v[b + 2][j];
+      const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 2);
+      if (a & 2) v[b][j] = got; else v[b + 2][j] = got;
+    }
+  }
+}
+
 // Last step of a row block that several clusters shared: add the clusters' fp32 partials of a
 // rows x cols region of Y (one slab per cluster, `slab_stride` floats apart, row pitch `ld` floats) in
 // slab order, apply bias and activation, write the 16-bit result.  `nthreads` threads of one CTA call it with

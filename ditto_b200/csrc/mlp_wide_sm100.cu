@@ -576,13 +576,24 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         const size_t mpad = static_cast<size_t>(p.row_blocks - p.whole_blocks) * kRows;   // rows of the shared blocks
         const size_t slab = static_cast<size_t>(gridDim.y) * mpad * p.N;
         const int srow0 = t.row0 - p.whole_blocks * kRows;
-        float* prow = p.slabs + static_cast<size_t>(sp) * slab + (static_cast<size_t>(t.b) * mpad + srow0 + row) * p.N + ycol0;
+        // (64-byte runs per row, like Y: groups of four lanes transpose 4 x 4 blocks of 16-byte pieces)
+        const int a = lane & 3;
+        float* pgrp = p.slabs + static_cast<size_t>(sp) * slab + (static_cast<size_t>(t.b) * mpad + srow0 + row - a) * p.N + ycol0;
         for (int cc = 0; cc < NS / 2; cc += 32) {
           uint32_t o[32];
           tmem_ld_x32_wait(tmem_y + lane_base + colg + cc, o);
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            __stcg(reinterpret_cast<uint4*>(prow + cc) + j, make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+          for (int m = 0; m < 2; ++m) {
+            uint32_t v[4][4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[b][j] = o[16 * m + 4 * b + j];
+            quad_transpose(v, a);
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+              __stcg(reinterpret_cast<uint4*>(pgrp + static_cast<size_t>(b) * p.N + cc + 16 * m) + a, make_uint4(v[b][0], v[b][1], v[b][2], v[b][3]));
+          }
         }
         __threadfence();
         mbar_arrive(&bar->y_sync);
