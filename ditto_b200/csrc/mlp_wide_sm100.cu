@@ -166,7 +166,8 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
 
 // EPI names the two epilogues at compile time: 1 = ReLU after GEMM1, nothing after GEMM2, no bias (the chain as
 // the reference defines it); 2 = bias + ReLU after both (the reference's feed-forward block); 3 = bias + GELU,
-// then bias (the same block with the reference's GELU in the usual place); 0 = activations and biases picked at
+// then bias (the same block with the reference's GELU in the usual place); 4 = no activation, no bias (the plain
+// GEMM -> GEMM chain); 0 = activations and biases picked at
 // run time (one warp-uniform dispatch per accumulator piece).  The general form's six code paths per call site
 // cost registers (1.5 KB of spills) and time -- config 4 with biases: 878 against 1030 TFLOP/s -- which the
 // named forms do not pay.
@@ -175,6 +176,7 @@ template <> struct Epilogues<0> { static constexpr int act1 = 0, act2 = 0; stati
 template <> struct Epilogues<1> { static constexpr int act1 = 1, act2 = 0; static constexpr bool bias = false; };
 template <> struct Epilogues<2> { static constexpr int act1 = 1, act2 = 1; static constexpr bool bias = true; };
 template <> struct Epilogues<3> { static constexpr int act1 = 2, act2 = 0; static constexpr bool bias = true; };
+template <> struct Epilogues<4> { static constexpr int act1 = 0, act2 = 0; static constexpr bool bias = false; };
 
 template <bool BF16, int EPI>
 __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
@@ -808,6 +810,8 @@ cudaError_t wide_configure(int* slots_out) {
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(mlp_wide_kernel<BF16, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(mlp_wide_kernel<BF16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
     // how many clusters of four the device holds at once: the unit row-block sharing is sized against
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kCluster * 64, 1, 1);
@@ -944,7 +948,8 @@ int launch_wide_group(const void* x, const void* w1, const void* w2, void* y, in
   // the named forms read their biases 16 bytes at a time
   const bool both = b1 != nullptr && b2 != nullptr && ((reinterpret_cast<uintptr_t>(b1) | reinterpret_cast<uintptr_t>(b2)) & 15) == 0;
   const bool none = b1 == nullptr && b2 == nullptr;
-  const int epi = (act1 == 1 && act2 == 0 && none) ? 1 : (act1 == 1 && act2 == 1 && both) ? 2 : (act1 == 2 && act2 == 0 && both) ? 3 : 0;
+  const int epi = (act1 == 1 && act2 == 0 && none) ? 1 : (act1 == 1 && act2 == 1 && both) ? 2 : (act1 == 2 && act2 == 0 && both) ? 3
+                  : (act1 == 0 && act2 == 0 && none) ? 4 : 0;
   cudaError_t e = cudaErrorInvalidValue;
   switch (epi * 2 + (bf16 ? 1 : 0)) {
     case 0: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, 0>, p); break;
@@ -954,7 +959,9 @@ int launch_wide_group(const void* x, const void* w1, const void* w2, void* y, in
     case 4: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, 2>, p); break;
     case 5: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, 2>, p); break;
     case 6: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, 3>, p); break;
-    default: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, 3>, p); break;
+    case 7: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, 3>, p); break;
+    case 8: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<false, 4>, p); break;
+    default: e = cudaLaunchKernelEx(&cfg, mlp_wide_kernel<true, 4>, p); break;
   }
   return e == cudaSuccess ? DITTO_OK : cuda_fail("mlp wide kernel launch", e);
 }
