@@ -73,6 +73,15 @@ __device__ __forceinline__ void act_pack_fixed(const uint32_t (&acc)[N], const u
     out[j] = pack2<BF16>(act_apply<ACT>(v0), act_apply<ACT>(v1));
   }
 }
+// The same with the bias values already in registers (two 16-bit values per word).
+template <bool BF16, int ACT, int N>
+__device__ __forceinline__ void act_pack_words(const uint32_t (&acc)[N], const uint32_t (&bw)[N / 2], uint32_t (&out)[N / 2]) {
+#pragma unroll
+  for (int j = 0; j < N / 2; ++j) {
+    const float2 bb = unpack2<BF16>(bw[j]);
+    out[j] = pack2<BF16>(act_apply<ACT>(__uint_as_float(acc[2 * j]) + bb.x), act_apply<ACT>(__uint_as_float(acc[2 * j + 1]) + bb.y));
+  }
+}
 // One warp-uniform dispatch per call instead of one per element.
 template <bool BF16, int N>
 __device__ __forceinline__ void act_pack(const uint32_t (&acc)[N], const uint32_t* bias, int act, uint32_t (&out)[N / 2]) {

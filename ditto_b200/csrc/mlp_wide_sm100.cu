@@ -490,6 +490,13 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
     // Y of item t leaves tensor memory.  With `release` the accumulator is handed back to the GEMM2 warp as soon
     // as it is in registers (NS / 2 <= 128 columns per thread, rounded: 64 registers), before the stores.
     auto drain_y = [&](const Item& t, int k, bool release) __attribute__((always_inline)) -> bool {
+      // (named forms with biases: lane l < NS / 16 loads piece l of its warp's NS / 2 bias values ahead of the wait)
+      uint4 bq2 = make_uint4(0u, 0u, 0u, 0u);
+      if constexpr (EPI != 0 && Epilogues<EPI>::bias) {
+        if (!shared && lane * 8 < NS / 2)
+          bq2 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint32_t*>(p.b2) +
+                                                     (static_cast<size_t>(t.b) * p.ldn + p.n0 + ycol0) / 2) + lane);
+      }
       bool good = mbar_wait(&bar->y_done, k & 1, abort_word, 0x800);
       good = __all_sync(0xffffffffu, good);
       if (!good) return false;
@@ -501,7 +508,17 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
                                                 : reinterpret_cast<const uint32_t*>(p.b2) + (static_cast<size_t>(t.b) * p.ldn + p.n0 + ycol0) / 2;
         uint32_t w[8][8];                       // 16 columns a piece
         auto pack_piece = [&](int c, const uint32_t (&o)[16]) __attribute__((always_inline)) {
-          if constexpr (EPI != 0) act_pack_fixed<BF16, Epilogues<EPI>::act2, Epilogues<EPI>::bias, 16, true>(o, bias2 + c * 8, w[c]);
+          if constexpr (EPI != 0 && Epilogues<EPI>::bias) {
+            uint32_t bw[8];
+#pragma unroll
+            for (int pc = 0; pc < 2; ++pc) {
+              bw[4 * pc] = __shfl_sync(0xffffffffu, bq2.x, 2 * c + pc);
+              bw[4 * pc + 1] = __shfl_sync(0xffffffffu, bq2.y, 2 * c + pc);
+              bw[4 * pc + 2] = __shfl_sync(0xffffffffu, bq2.z, 2 * c + pc);
+              bw[4 * pc + 3] = __shfl_sync(0xffffffffu, bq2.w, 2 * c + pc);
+            }
+            act_pack_words<BF16, Epilogues<EPI>::act2>(o, bw, w[c]);
+          } else if constexpr (EPI != 0) act_pack_fixed<BF16, Epilogues<EPI>::act2, false>(o, nullptr, w[c]);
           else act_pack<BF16>(o, bias2 == nullptr ? nullptr : bias2 + c * 8, p.act2, w[c]);
         };
         if (NS == 256) {
@@ -628,19 +645,34 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1)
         const uint32_t* bias1 = p.b1 == nullptr ? nullptr
                                                 : reinterpret_cast<const uint32_t*>(p.b1) +
                                                       (static_cast<size_t>(t.b) * p.L + hcol0 + grp * 32) / 2;
+        // The named forms with biases: a bias value is the same for all rows, so instead of every lane loading all
+        // of its warp's 128 values (16 load instructions of 16 bytes per thread and chunk, each on the path
+        // between "accumulator ready" and "unit pushed"), lane l < 16 loads one 16-byte piece -- piece l % 4 of
+        // quarter l / 4 -- before the wait for the accumulator, and the values are handed round by shuffles.
+        uint4 bq = make_uint4(0u, 0u, 0u, 0u);
+        if constexpr (EPI != 0 && Epilogues<EPI>::bias) {
+          if (lane < 16 && hcol0 + (lane >> 2) * kUnitCols + grp * 32 < p.L)
+            bq = __ldg(reinterpret_cast<const uint4*>(bias1 + (lane >> 2) * (kUnitCols / 2)) + (lane & 3));
+        }
         // quarter kk of the chunk: tensor memory -> bias, activation, rounding -> registers
         auto load_quarter = [&](int kk, uint32_t (&v)[16]) __attribute__((always_inline)) {
           uint32_t h[32];
           tmem_ld_x32_wait(tmem_h + lane_base + kk * kUnitCols + grp * 32, h);
           // (hidden columns >= L of a last partial chunk: GEMM1 gave zeros, the bias is not read, every
           // activation maps 0 to 0 and the W2 rows they meet are zero-filled)
-          if constexpr (EPI != 0) {
-            if (Epilogues<EPI>::bias && hcol0 + kk * kUnitCols + grp * 32 >= p.L) {
+          if constexpr (EPI != 0 && Epilogues<EPI>::bias) {
+            // (pieces past L were loaded as zeros: 0 + 0 stays 0 under every activation)
+            uint32_t bw[16];
 #pragma unroll
-              for (int z = 0; z < 16; ++z) v[z] = 0u;
-            } else {
-              act_pack_fixed<BF16, Epilogues<EPI>::act1, Epilogues<EPI>::bias, 32, true>(h, bias1 + kk * (kUnitCols / 2), v);
+            for (int pc = 0; pc < 4; ++pc) {
+              bw[4 * pc] = __shfl_sync(0xffffffffu, bq.x, kk * 4 + pc);
+              bw[4 * pc + 1] = __shfl_sync(0xffffffffu, bq.y, kk * 4 + pc);
+              bw[4 * pc + 2] = __shfl_sync(0xffffffffu, bq.z, kk * 4 + pc);
+              bw[4 * pc + 3] = __shfl_sync(0xffffffffu, bq.w, kk * 4 + pc);
             }
+            act_pack_words<BF16, Epilogues<EPI>::act1>(h, bw, v);
+          } else if constexpr (EPI != 0) {
+            act_pack_fixed<BF16, Epilogues<EPI>::act1, false>(h, nullptr, v);
           } else act_pack<BF16>(h, (bias1 == nullptr || hcol0 + kk * kUnitCols + grp * 32 >= p.L) ? nullptr : bias1 + kk * (kUnitCols / 2),
                               p.act1, v);
         };
